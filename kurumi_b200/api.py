@@ -1,0 +1,356 @@
+"""ctypes binding of the kurumi C ABI (include/kurumi.h, include/kurumi_cuda.h).
+
+The classes mirror the reference's Rust surface so tests read like the reference's own:
+``Graph`` has the builder methods of kurumi_core/src/graph/ops/** (same names, same argument
+order, an ``Error`` on a failed build instead of ``Err``), ``Backend.eval(g, node)`` /
+``eval_with`` / ``eval_many_with`` are the trait methods of kurumi_core/src/backend.rs:14-31.
+
+``Library(path)`` binds any shared library that exports the ABI, so the same Python code drives
+the CUDA library and, in the tests, the CPU oracle.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Iterable, Sequence
+
+import numpy as np
+
+KU_ERR = 0xFFFFFFFF
+KU_CPU, KU_METAL, KU_CUDA = 0, 1, 2
+
+DTYPES = ["BOOL", "U8", "U16", "U32", "U64", "I8", "I16", "I32", "I64", "F8E4M3", "F8E5M2", "F16", "BF16", "F32",
+          "F64", "C64", "C128"]
+(BOOL, U8, U16, U32, U64, I8, I16, I32, I64, F8E4M3, F8E5M2, F16, BF16, F32, F64, C64, C128) = range(17)
+WIDTH = [1, 1, 2, 4, 8, 1, 2, 4, 8, 1, 1, 2, 2, 4, 8, 8, 16]
+# numpy carrier per dtype: narrow floats travel as their raw bit patterns
+_NP = {BOOL: np.uint8, U8: np.uint8, U16: np.uint16, U32: np.uint32, U64: np.uint64, I8: np.int8, I16: np.int16,
+       I32: np.int32, I64: np.int64, F8E4M3: np.uint8, F8E5M2: np.uint8, F16: np.float16, BF16: np.uint16,
+       F32: np.float32, F64: np.float64}
+
+
+class Error(RuntimeError):
+    pass
+
+
+def _sz(seq: Iterable[int]):
+    seq = list(seq)
+    return (C.c_size_t * max(len(seq), 1))(*seq), len(seq)
+
+
+class Library:
+    """One loaded shared library exporting the kurumi C ABI."""
+
+    def __init__(self, path: str):
+        if not os.path.exists(path):
+            raise Error(f"{path} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()')")
+        self.path = path
+        self.lib = C.CDLL(path)
+        L = self.lib
+        L.ku_last_error.restype = C.c_char_p
+        for name in ("ku_graph_new", "ku_backend_new", "ku_eval", "ku_eval_with", "ku_feeds_new", "ku_tensor_f32",
+                     "ku_tensor_new"):
+            getattr(L, name).restype = C.c_void_p
+        for name in ("ku_tensor_rank", "ku_tensor_len", "ku_tensor_nbytes", "ku_node_rank", "ku_node_count", "ku_dump"):
+            getattr(L, name).restype = C.c_size_t
+        L.ku_tensor_data_f32.restype = C.c_ssize_t
+        L.ku_eval_many.restype = C.c_int32
+        self._node_fns = {}
+
+    def last_error(self) -> str:
+        e = self.lib.ku_last_error()
+        return e.decode() if e else ""
+
+    def node_fn(self, name: str):
+        f = self._node_fns.get(name)
+        if f is None:
+            f = getattr(self.lib, name)
+            f.restype = C.c_uint32
+            self._node_fns[name] = f
+        return f
+
+    def has(self, name: str) -> bool:
+        return hasattr(self.lib, name)
+
+
+class Tensor:
+    """Host tensor handle (the reference's TensorVal)."""
+
+    def __init__(self, lib: Library, handle: int):
+        if not handle:
+            raise Error(lib.last_error() or "null tensor")
+        self.lib, self.h = lib, C.c_void_p(handle)
+
+    @staticmethod
+    def from_numpy(lib: Library, arr: np.ndarray, dtype: int | None = None) -> "Tensor":
+        if dtype is None:
+            dtype = {np.dtype(np.float32): F32, np.dtype(np.float64): F64, np.dtype(np.int32): I32,
+                     np.dtype(np.int64): I64, np.dtype(np.uint8): U8, np.dtype(np.bool_): BOOL,
+                     np.dtype(np.float16): F16, np.dtype(np.int8): I8, np.dtype(np.int16): I16,
+                     np.dtype(np.uint16): U16, np.dtype(np.uint32): U32, np.dtype(np.uint64): U64}[arr.dtype]
+        a = np.ascontiguousarray(arr)
+        shape, rank = _sz(a.shape)
+        h = lib.lib.ku_tensor_new(C.c_uint32(dtype), a.ctypes.data_as(C.c_void_p), C.c_size_t(a.nbytes), shape,
+                                  C.c_size_t(rank))
+        return Tensor(lib, h)
+
+    @property
+    def dtype(self) -> int:
+        return int(self.lib.lib.ku_tensor_dtype(self.h))
+
+    @property
+    def shape(self) -> tuple:
+        r = self.lib.lib.ku_tensor_rank(self.h)
+        out = (C.c_size_t * max(r, 1))()
+        self.lib.lib.ku_tensor_shape(self.h, out)
+        return tuple(out[i] for i in range(r))
+
+    def numpy(self) -> np.ndarray:
+        """Values as numpy; bf16 / fp8 come back as raw bit patterns (uint16 / uint8)."""
+        n = self.lib.lib.ku_tensor_nbytes(self.h)
+        buf = np.empty(n, dtype=np.uint8)
+        if n:
+            self.lib.lib.ku_tensor_bytes(self.h, buf.ctypes.data_as(C.c_void_p))
+        return buf.view(_NP[self.dtype]).reshape(self.shape)
+
+    def __del__(self):
+        try:
+            self.lib.lib.ku_tensor_free(self.h)
+        except Exception:
+            pass
+
+
+class Feeds:
+    def __init__(self, lib: Library):
+        self.lib, self.h = lib, C.c_void_p(lib.lib.ku_feeds_new())
+        self._keep = []
+
+    def set(self, node: int, value, dtype: int | None = None):
+        t = value if isinstance(value, Tensor) else Tensor.from_numpy(self.lib, value, dtype)
+        self._keep.append(t)
+        self.lib.lib.ku_feeds_set(self.h, C.c_uint32(node), t.h)
+        return self
+
+    def __del__(self):
+        try:
+            self.lib.lib.ku_feeds_free(self.h)
+        except Exception:
+            pass
+
+
+class Graph:
+    """Graph builder: every method returns a node id or raises Error with ku_last_error()."""
+
+    def __init__(self, lib: Library):
+        self.lib, self.h = lib, C.c_void_p(lib.lib.ku_graph_new())
+
+    def __del__(self):
+        try:
+            self.lib.lib.ku_graph_free(self.h)
+        except Exception:
+            pass
+
+    def _n(self, name: str, *args) -> int:
+        r = self.lib.node_fn(name)(self.h, *args)
+        if r == KU_ERR:
+            raise Error(self.lib.last_error())
+        return r
+
+    # leaves
+    def input(self, shape: Sequence[int], dtype: int) -> int:
+        s, r = _sz(shape)
+        return self._n("ku_input", s, C.c_size_t(r), C.c_uint32(dtype))
+
+    def constant(self, arr: np.ndarray, dtype: int | None = None) -> int:
+        a = np.ascontiguousarray(arr)
+        if dtype is None:
+            dtype = Tensor.from_numpy(self.lib, np.zeros(1, a.dtype)).dtype
+        s, r = _sz(a.shape)
+        return self._n("ku_constant", C.c_uint32(dtype), a.ctypes.data_as(C.c_void_p), C.c_size_t(a.nbytes), s, C.c_size_t(r))
+
+    def scalar(self, like: int, v: float) -> int:
+        return self._n("ku_scalar", C.c_uint32(like), C.c_float(v))
+
+    def iota(self, shape, axis: int, dtype: int) -> int:
+        s, r = _sz(shape)
+        return self._n("ku_iota", s, C.c_size_t(r), C.c_size_t(axis), C.c_uint32(dtype))
+
+    def rand_uniform(self, shape, seed: int) -> int:
+        s, r = _sz(shape)
+        return self._n("ku_rand_uniform", s, C.c_size_t(r), C.c_uint64(seed))
+
+    def rand_uniform_keyed(self, shape, seed_node: int) -> int:
+        s, r = _sz(shape)
+        return self._n("ku_rand_uniform_keyed", s, C.c_size_t(r), C.c_uint32(seed_node))
+
+    def randn(self, shape, seed: int) -> int:
+        s, r = _sz(shape)
+        return self._n("ku_randn", s, C.c_size_t(r), C.c_uint64(seed))
+
+    def rand_range(self, shape, seed: int, lo: float, hi: float) -> int:
+        s, r = _sz(shape)
+        return self._n("ku_rand_range", s, C.c_size_t(r), C.c_uint64(seed), C.c_float(lo), C.c_float(hi))
+
+    def cast(self, x: int, dtype: int) -> int:
+        return self._n("ku_cast", C.c_uint32(x), C.c_uint32(dtype))
+
+    def bitcast(self, x: int, dtype: int) -> int:
+        return self._n("ku_bitcast", C.c_uint32(x), C.c_uint32(dtype))
+
+    # axis ops
+    def sum(self, x, axis): return self._n("ku_sum", C.c_uint32(x), C.c_size_t(axis))
+    def prod(self, x, axis): return self._n("ku_prod", C.c_uint32(x), C.c_size_t(axis))
+    def mean(self, x, axis): return self._n("ku_mean", C.c_uint32(x), C.c_size_t(axis))
+    def reduce_max(self, x, axis): return self._n("ku_reduce_max", C.c_uint32(x), C.c_size_t(axis))
+    def reduce_min(self, x, axis): return self._n("ku_reduce_min", C.c_uint32(x), C.c_size_t(axis))
+    def softmax(self, x, axis): return self._n("ku_softmax", C.c_uint32(x), C.c_size_t(axis))
+    def rmsnorm(self, x, axis, eps): return self._n("ku_rmsnorm", C.c_uint32(x), C.c_size_t(axis), C.c_float(eps))
+    def clamp_min(self, x, v): return self._n("ku_clamp_min", C.c_uint32(x), C.c_float(v))
+
+    # contraction
+    def matmul(self, a, b): return self._n("ku_matmul", C.c_uint32(a), C.c_uint32(b))
+
+    def dot_general(self, a, b, lc, rc, lb=(), rb=()):
+        lc_, nlc = _sz(lc); rc_, nrc = _sz(rc); lb_, nlb = _sz(lb); rb_, nrb = _sz(rb)
+        return self._n("ku_dot_general", C.c_uint32(a), C.c_uint32(b), lc_, C.c_size_t(nlc), rc_, C.c_size_t(nrc), lb_,
+                       C.c_size_t(nlb), rb_, C.c_size_t(nrb))
+
+    def where(self, c, a, b): return self._n("ku_where", C.c_uint32(c), C.c_uint32(a), C.c_uint32(b))
+    select = where
+
+    def sdpa(self, q, k, v, causal: bool):
+        return self._n("ku_sdpa", C.c_uint32(q), C.c_uint32(k), C.c_uint32(v), C.c_uint32(1 if causal else 0))
+
+    # movement
+    def reshape(self, x, shape):
+        s, r = _sz(shape); return self._n("ku_reshape", C.c_uint32(x), s, C.c_size_t(r))
+
+    def expand(self, x, shape):
+        s, r = _sz(shape); return self._n("ku_expand", C.c_uint32(x), s, C.c_size_t(r))
+
+    def permute(self, x, perm):
+        s, r = _sz(perm); return self._n("ku_permute", C.c_uint32(x), s, C.c_size_t(r))
+
+    def transpose(self, x, i, j): return self._n("ku_transpose", C.c_uint32(x), C.c_size_t(i), C.c_size_t(j))
+
+    def flip(self, x, axes):
+        s, r = _sz(axes); return self._n("ku_flip", C.c_uint32(x), s, C.c_size_t(r))
+
+    def slice(self, x, ranges):
+        flat = [v for r in ranges for v in r]; s, _ = _sz(flat)
+        return self._n("ku_slice", C.c_uint32(x), s, C.c_size_t(len(ranges)))
+
+    def slice_step(self, x, ranges):
+        flat = [v for r in ranges for v in r]; s, _ = _sz(flat)
+        return self._n("ku_slice_step", C.c_uint32(x), s, C.c_size_t(len(ranges)))
+
+    def pad(self, x, pads):
+        flat = [v for r in pads for v in r]; s, _ = _sz(flat)
+        return self._n("ku_pad", C.c_uint32(x), s, C.c_size_t(len(pads)))
+
+    def broadcast_to(self, x, shape):
+        s, r = _sz(shape); return self._n("ku_broadcast_to", C.c_uint32(x), s, C.c_size_t(r))
+
+    # passes / inspection
+    def amp(self, root): return self._n("ku_amp", C.c_uint32(root))
+
+    def amp_to(self, root, dtype):
+        name = "ku_cuda_amp_to" if self.lib.has("ku_cuda_amp_to") else "ko_amp_to"
+        return self._n(name, C.c_uint32(root), C.c_uint32(dtype))
+
+    def shape(self, node) -> tuple:
+        r = self.lib.lib.ku_node_rank(self.h, C.c_uint32(node))
+        if r == C.c_size_t(-1).value:
+            raise Error(self.lib.last_error())
+        out = (C.c_size_t * max(r, 1))()
+        self.lib.lib.ku_node_shape(self.h, C.c_uint32(node), out)
+        return tuple(out[i] for i in range(r))
+
+    def dtype(self, node) -> int:
+        d = self.lib.lib.ku_node_dtype(self.h, C.c_uint32(node))
+        if d == KU_ERR:
+            raise Error(self.lib.last_error())
+        return d
+
+    def node_count(self, root) -> int:
+        return self.lib.lib.ku_node_count(self.h, C.c_uint32(root))
+
+    def dump(self, root) -> str:
+        n = self.lib.lib.ku_dump(self.h, C.c_uint32(root), None, C.c_size_t(0))
+        buf = (C.c_uint8 * max(n, 1))()
+        self.lib.lib.ku_dump(self.h, C.c_uint32(root), buf, C.c_size_t(n))
+        return bytes(buf[:n]).decode()
+
+
+def _bin(name):
+    def f(self, a, b): return self._n("ku_" + name, C.c_uint32(a), C.c_uint32(b))
+    return f
+
+
+def _un(name):
+    def f(self, x): return self._n("ku_" + name, C.c_uint32(x))
+    return f
+
+
+for _m in ("add", "sub", "mul", "div", "max", "min", "idiv", "and", "or", "xor", "shl", "shr", "lt", "eq", "le", "gt",
+           "ge", "ne"):
+    setattr(Graph, {"and": "and_", "or": "or_"}.get(_m, _m), _bin(_m))
+Graph.cmp_lt, Graph.cmp_eq = Graph.lt, Graph.eq
+for _m in ("neg", "recip", "sqrt", "square", "abs", "floor", "exp", "exp2", "ln", "log2", "sin", "cos", "relu", "gelu",
+           "silu", "sigmoid", "tanh", "logical_not", "detach"):
+    setattr(Graph, _m, _un(_m))
+
+
+class Backend:
+    """Evaluation seam (kurumi_core/src/backend.rs:14-31) over ku_backend_new / ku_eval*."""
+
+    def __init__(self, lib: Library, kind: int):
+        self.lib = lib
+        h = lib.lib.ku_backend_new(C.c_uint32(kind))
+        if not h:
+            raise Error(lib.last_error() or f"backend kind {kind} unavailable")
+        self.h = C.c_void_p(h)
+
+    def __del__(self):
+        try:
+            self.lib.lib.ku_backend_free(self.h)
+        except Exception:
+            pass
+
+    def eval(self, g: Graph, node: int) -> Tensor:
+        return Tensor(self.lib, self.lib.lib.ku_eval(g.h, C.c_uint32(node), self.h))
+
+    def eval_with(self, g: Graph, node: int, feeds: Feeds) -> Tensor:
+        return Tensor(self.lib, self.lib.lib.ku_eval_with(g.h, C.c_uint32(node), self.h, feeds.h))
+
+    def eval_many_with(self, g: Graph, nodes: Sequence[int], feeds: Feeds | None = None) -> list:
+        feeds = feeds or Feeds(self.lib)
+        ids = (C.c_uint32 * max(len(nodes), 1))(*nodes)
+        out = (C.c_void_p * max(len(nodes), 1))()
+        rc = self.lib.lib.ku_eval_many(g.h, ids, C.c_size_t(len(nodes)), self.h, feeds.h, out)
+        if rc != 0:
+            raise Error(self.lib.last_error())
+        return [Tensor(self.lib, out[i]) for i in range(len(nodes))]
+
+
+# ---- helpers for the narrow float formats (numpy has no bf16 / fp8) -------------------------------
+def bf16_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even f32 -> bf16 bit patterns (NaN kept quiet)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    nan = np.isnan(x)
+    if nan.any():
+        r = np.where(nan, ((u >> 16) | 0x40).astype(np.uint16), r)
+    return r
+
+
+def e4m3_to_f32(bits: np.ndarray) -> np.ndarray:
+    b = bits.astype(np.uint32)
+    e, m, s = (b >> 3) & 0xF, b & 7, (b >> 7) & 1
+    v = np.where(e == 0, m.astype(np.float64) * 2.0 ** -9, (8 + m).astype(np.float64) * np.exp2(e.astype(np.float64) - 10))
+    v = np.where((b & 0x7F) == 0x7F, np.nan, v)
+    return np.where(s == 1, -v, v).astype(np.float32)

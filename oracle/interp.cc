@@ -1,0 +1,707 @@
+// TEST INFRASTRUCTURE, NOT PRODUCT CODE. Nothing under kurumi_b200/ may call into this file.
+//
+// CPU restatement of kurumi_core's reference interpreter (the correctness oracle of the
+// reference) for the primitives the CUDA backend evaluates. Each function cites the reference
+// file:line it follows. Two modes:
+//   * native: every tensor is held in its own dtype and every primitive rounds like the
+//     reference does (f32 arithmetic without FMA contraction, low-precision floats computed
+//     in f32 and rounded after every primitive, integers wrapping).
+//   * wide ("f64 interpreter run"): every float tensor is held in f64 and all float arithmetic
+//     is f64; only an explicit Cast to a narrower float dtype rounds (to that format). This is
+//     the yardstick the bf16 / fp8 GEMM and attention tolerances are stated against.
+//
+// Arithmetic that lives in third-party crates absent from the reference tree:
+//   half 2.7.1 (bf16/f16 conversions)  -> restated as IEEE round-to-nearest-even
+//   float8 0.7.0 (fp8 conversions)     -> restated as RNE + saturate-to-finite (e4m3 "fn")
+//   gemm 0.19.0 (f32 sgemm)            -> stand-in: plain f32 loop, k ascending
+// The reference's own tests pin those only at exactly representable values and through
+// tolerances, so for rounding mode / summation order: parity unpinned.
+#include "interp.h"
+
+#include <algorithm>
+#include <cmath>
+#include <limits>
+#include <unordered_map>
+
+namespace ko {
+using namespace ku;
+
+// kurumi_core/src/rng.rs:10-26 (threefry2x32, 20 rounds, key injection every 4)
+uint64_t threefry2x32(uint64_t key, uint64_t counter) {
+  static const uint32_t ROT[8] = {13, 15, 26, 6, 17, 29, 16, 24};
+  uint32_t k0 = static_cast<uint32_t>(key), k1 = static_cast<uint32_t>(key >> 32);
+  uint32_t ks[3] = {k0, k1, 0x1BD11BDAu ^ k0 ^ k1};
+  uint32_t x0 = static_cast<uint32_t>(counter) + ks[0], x1 = static_cast<uint32_t>(counter >> 32) + ks[1];
+  for (uint32_t r = 0; r < 20; ++r) {
+    x0 += x1;
+    uint32_t s = ROT[r % 8];
+    x1 = (x1 << s) | (x1 >> (32 - s));
+    x1 ^= x0;
+    if (r % 4 == 3) {
+      uint32_t inj = r / 4 + 1;
+      x0 += ks[inj % 3];
+      x1 += ks[(inj + 1) % 3] + inj;
+    }
+  }
+  return static_cast<uint64_t>(x0) | (static_cast<uint64_t>(x1) << 32);
+}
+// kurumi_core/src/rng.rs:29-31
+float uniform_f32(uint64_t bits) { return static_cast<float>(static_cast<uint32_t>(bits) >> 8) / 16777216.0f; }
+
+namespace {
+
+// kurumi_core/src/layout.rs:18-27
+inline void inc(std::vector<size_t>& coord, const Shape& shape) {
+  for (size_t i = coord.size(); i-- > 0;) {
+    if (++coord[i] < shape[i]) return;
+    coord[i] = 0;
+  }
+}
+
+size_t esize(const Val& v) { return v.wide ? 8 : dtype_width(v.dtype); }
+
+Val make_val(DType dt, Shape shape, bool wide) {
+  Val v;
+  v.dtype = dt;
+  v.wide = wide;
+  v.shape = std::move(shape);
+  v.bytes.assign(std::max<size_t>(numel(v.shape), 0) * (wide ? 8 : dtype_width(dt)), 0);
+  return v;
+}
+
+// ---- per-dtype element traits: S = storage type, C = compute type -----------------------------
+template <DType D> struct E;
+#define KO_PLAIN(D, T) \
+  template <> struct E<DType::D> { using S = T; using C = T; static C ld(S s) { return s; } static S st(C c) { return c; } };
+KO_PLAIN(U8, uint8_t) KO_PLAIN(U16, uint16_t) KO_PLAIN(U32, uint32_t) KO_PLAIN(U64, uint64_t)
+KO_PLAIN(I8, int8_t) KO_PLAIN(I16, int16_t) KO_PLAIN(I32, int32_t) KO_PLAIN(I64, int64_t)
+KO_PLAIN(F32, float) KO_PLAIN(F64, double)
+template <> struct E<DType::BOOL> { using S = uint8_t; using C = uint8_t; static C ld(S s) { return s; } static S st(C c) { return c; } };
+// kurumi_core/src/dtype/traits/float.rs:134-161: upcast to f32, compute, round back
+template <> struct E<DType::BF16> { using S = uint16_t; using C = float; static C ld(S s) { return bf16_to_f32(s); } static S st(C c) { return f32_to_bf16(c); } };
+template <> struct E<DType::F16> { using S = uint16_t; using C = float; static C ld(S s) { return f16_to_f32(s); } static S st(C c) { return f32_to_f16(c); } };
+template <> struct E<DType::F8E4M3> { using S = uint8_t; using C = float; static C ld(S s) { return e4m3_to_f32(s); } static S st(C c) { return f32_to_e4m3(c); } };
+template <> struct E<DType::F8E5M2> { using S = uint8_t; using C = float; static C ld(S s) { return e5m2_to_f32(s); } static S st(C c) { return f32_to_e5m2(c); } };
+
+#define KO_CASE(D, ...) case DType::D: { constexpr DType DT = DType::D; (void)DT; __VA_ARGS__; break; }
+#define KO_FLOATS(dt, ...) \
+  switch (dt) { KO_CASE(F8E4M3, __VA_ARGS__) KO_CASE(F8E5M2, __VA_ARGS__) KO_CASE(F16, __VA_ARGS__) KO_CASE(BF16, __VA_ARGS__) \
+    KO_CASE(F32, __VA_ARGS__) KO_CASE(F64, __VA_ARGS__) default: throw Error("oracle: float dtype required"); }
+#define KO_INTS(dt, ...) \
+  switch (dt) { KO_CASE(U8, __VA_ARGS__) KO_CASE(U16, __VA_ARGS__) KO_CASE(U32, __VA_ARGS__) KO_CASE(U64, __VA_ARGS__) \
+    KO_CASE(I8, __VA_ARGS__) KO_CASE(I16, __VA_ARGS__) KO_CASE(I32, __VA_ARGS__) KO_CASE(I64, __VA_ARGS__) \
+    default: throw Error("oracle: integer dtype required"); }
+#define KO_NUMERIC(dt, ...) \
+  switch (dt) { KO_CASE(U8, __VA_ARGS__) KO_CASE(U16, __VA_ARGS__) KO_CASE(U32, __VA_ARGS__) KO_CASE(U64, __VA_ARGS__) \
+    KO_CASE(I8, __VA_ARGS__) KO_CASE(I16, __VA_ARGS__) KO_CASE(I32, __VA_ARGS__) KO_CASE(I64, __VA_ARGS__) \
+    KO_CASE(F8E4M3, __VA_ARGS__) KO_CASE(F8E5M2, __VA_ARGS__) KO_CASE(F16, __VA_ARGS__) KO_CASE(BF16, __VA_ARGS__) \
+    KO_CASE(F32, __VA_ARGS__) KO_CASE(F64, __VA_ARGS__) default: throw Error("oracle: numeric dtype required"); }
+#define KO_ALL(dt, ...) \
+  switch (dt) { KO_CASE(BOOL, __VA_ARGS__) KO_CASE(U8, __VA_ARGS__) KO_CASE(U16, __VA_ARGS__) KO_CASE(U32, __VA_ARGS__) KO_CASE(U64, __VA_ARGS__) \
+    KO_CASE(I8, __VA_ARGS__) KO_CASE(I16, __VA_ARGS__) KO_CASE(I32, __VA_ARGS__) KO_CASE(I64, __VA_ARGS__) \
+    KO_CASE(F8E4M3, __VA_ARGS__) KO_CASE(F8E5M2, __VA_ARGS__) KO_CASE(F16, __VA_ARGS__) KO_CASE(BF16, __VA_ARGS__) \
+    KO_CASE(F32, __VA_ARGS__) KO_CASE(F64, __VA_ARGS__) default: throw Error("oracle: complex dtypes are outside this oracle"); }
+
+// ---- scalar semantics ---------------------------------------------------------------------------
+// kurumi_core/src/dtype/traits/float.rs:10-37 (f32::max = IEEE maxNum), int.rs:10-42
+template <typename C> C op_add(C a, C b) {
+  if constexpr (std::is_integral_v<C>) { using U = std::make_unsigned_t<C>; return static_cast<C>(static_cast<U>(static_cast<U>(a) + static_cast<U>(b))); }
+  else return a + b;
+}
+template <typename C> C op_mul(C a, C b) {
+  if constexpr (std::is_integral_v<C>) { using U = std::make_unsigned_t<C>; return static_cast<C>(static_cast<U>(static_cast<U>(a) * static_cast<U>(b))); }
+  else return a * b;
+}
+template <typename C> C op_max(C a, C b) {
+  if constexpr (std::is_same_v<C, float>) return std::fmax(a, b);
+  else if constexpr (std::is_same_v<C, double>) return std::fmax(a, b);
+  else return a > b ? a : b;
+}
+template <typename C> C op_neg(C a) {
+  if constexpr (std::is_integral_v<C>) { using U = std::make_unsigned_t<C>; return static_cast<C>(static_cast<U>(0) - static_cast<U>(a)); }
+  else return -a;
+}
+template <typename C> C op_idiv(C a, C b) {
+  if (b == 0) return 0;
+  if constexpr (std::is_signed_v<C>) { if (a == std::numeric_limits<C>::min() && b == static_cast<C>(-1)) return a; }
+  return static_cast<C>(a / b);
+}
+template <typename C> C op_shl(C a, C b) {
+  using U = std::make_unsigned_t<C>;
+  unsigned s = static_cast<unsigned>(static_cast<uint32_t>(b)) & (sizeof(C) * 8 - 1);
+  return static_cast<C>(static_cast<U>(static_cast<U>(a) << s));
+}
+template <typename C> C op_shr(C a, C b) {
+  unsigned s = static_cast<unsigned>(static_cast<uint32_t>(b)) & (sizeof(C) * 8 - 1);
+  return static_cast<C>(a >> s);  // arithmetic for signed, logical for unsigned
+}
+template <typename C> C op_float1(OpKind k, C x) {
+  switch (k) {
+    case OpKind::Recip: return static_cast<C>(1) / x;
+    case OpKind::Sqrt: return std::sqrt(x);
+    case OpKind::Exp2: return std::exp2(x);
+    case OpKind::Log2: return std::log2(x);
+    case OpKind::Sin: return std::sin(x);
+    case OpKind::Floor: return std::floor(x);
+    default: throw Error("oracle: not a float unary");
+  }
+}
+
+const double* wd(const Val& v) { return reinterpret_cast<const double*>(v.bytes.data()); }
+double* wd(Val& v) { return reinterpret_cast<double*>(v.bytes.data()); }
+
+// ---- elementwise (kurumi_core/src/interp/elementwise.rs:7-118) -----------------------------------
+Val ew_binary(OpKind k, const Val& a, const Val& b) {
+  const size_t n = numel(a.shape);
+  if (a.wide) {  // wide float arithmetic
+    const double *x = wd(a), *y = wd(b);
+    if (k == OpKind::CmpLt || k == OpKind::CmpEq) {
+      Val o = make_val(DType::BOOL, a.shape, false);
+      for (size_t i = 0; i < n; ++i) o.bytes[i] = k == OpKind::CmpLt ? (x[i] < y[i]) : (x[i] == y[i]);
+      return o;
+    }
+    Val o = make_val(a.dtype, a.shape, true);
+    double* z = wd(o);
+    for (size_t i = 0; i < n; ++i) z[i] = k == OpKind::Add ? x[i] + y[i] : k == OpKind::Mul ? x[i] * y[i] : std::fmax(x[i], y[i]);
+    return o;
+  }
+  if (k == OpKind::CmpLt || k == OpKind::CmpEq) {
+    Val o = make_val(DType::BOOL, a.shape, false);
+    KO_ALL(a.dtype, {
+      using T = E<DT>;
+      auto* x = reinterpret_cast<const typename T::S*>(a.bytes.data());
+      auto* y = reinterpret_cast<const typename T::S*>(b.bytes.data());
+      for (size_t i = 0; i < n; ++i) { auto p = T::ld(x[i]); auto q = T::ld(y[i]); o.bytes[i] = k == OpKind::CmpLt ? (p < q) : (p == q); }
+    })
+    return o;
+  }
+  Val o = make_val(a.dtype, a.shape, false);
+  if (k == OpKind::And || k == OpKind::Or || k == OpKind::Xor) {
+    if (a.dtype == DType::BOOL) {
+      for (size_t i = 0; i < n; ++i) {
+        bool p = a.bytes[i], q = b.bytes[i];
+        o.bytes[i] = k == OpKind::And ? (p && q) : k == OpKind::Or ? (p || q) : (p != q);
+      }
+      return o;
+    }
+    for (size_t i = 0; i < a.bytes.size(); ++i)
+      o.bytes[i] = k == OpKind::And ? (a.bytes[i] & b.bytes[i]) : k == OpKind::Or ? (a.bytes[i] | b.bytes[i]) : (a.bytes[i] ^ b.bytes[i]);
+    return o;
+  }
+  if (k == OpKind::IDiv || k == OpKind::Shl || k == OpKind::Shr) {
+    KO_INTS(a.dtype, {
+      using T = E<DT>;
+      auto* x = reinterpret_cast<const typename T::S*>(a.bytes.data());
+      auto* y = reinterpret_cast<const typename T::S*>(b.bytes.data());
+      auto* z = reinterpret_cast<typename T::S*>(o.bytes.data());
+      for (size_t i = 0; i < n; ++i) z[i] = k == OpKind::IDiv ? op_idiv(x[i], y[i]) : k == OpKind::Shl ? op_shl(x[i], y[i]) : op_shr(x[i], y[i]);
+    })
+    return o;
+  }
+  KO_NUMERIC(a.dtype, {
+    using T = E<DT>;
+    auto* x = reinterpret_cast<const typename T::S*>(a.bytes.data());
+    auto* y = reinterpret_cast<const typename T::S*>(b.bytes.data());
+    auto* z = reinterpret_cast<typename T::S*>(o.bytes.data());
+    if (k == OpKind::Add) for (size_t i = 0; i < n; ++i) z[i] = T::st(op_add(T::ld(x[i]), T::ld(y[i])));
+    else if (k == OpKind::Mul) for (size_t i = 0; i < n; ++i) z[i] = T::st(op_mul(T::ld(x[i]), T::ld(y[i])));
+    else for (size_t i = 0; i < n; ++i) z[i] = T::st(op_max(T::ld(x[i]), T::ld(y[i])));
+  })
+  return o;
+}
+
+Val ew_unary(OpKind k, const Val& a) {
+  const size_t n = numel(a.shape);
+  Val o = make_val(a.dtype, a.shape, a.wide);
+  if (a.wide) {
+    const double* x = wd(a);
+    double* z = wd(o);
+    for (size_t i = 0; i < n; ++i) z[i] = k == OpKind::Neg ? -x[i] : op_float1(k, x[i]);
+    return o;
+  }
+  if (k == OpKind::Neg) {
+    KO_NUMERIC(a.dtype, {
+      using T = E<DT>;
+      auto* x = reinterpret_cast<const typename T::S*>(a.bytes.data());
+      auto* z = reinterpret_cast<typename T::S*>(o.bytes.data());
+      for (size_t i = 0; i < n; ++i) z[i] = T::st(op_neg(T::ld(x[i])));
+    })
+    return o;
+  }
+  KO_FLOATS(a.dtype, {
+    using T = E<DT>;
+    auto* x = reinterpret_cast<const typename T::S*>(a.bytes.data());
+    auto* z = reinterpret_cast<typename T::S*>(o.bytes.data());
+    for (size_t i = 0; i < n; ++i) z[i] = T::st(op_float1(k, T::ld(x[i])));
+  })
+  return o;
+}
+
+Val ew_where(const Val& c, const Val& a, const Val& b) {
+  Val o = make_val(a.dtype, a.shape, a.wide);
+  const size_t n = numel(a.shape), w = esize(a);
+  for (size_t i = 0; i < n; ++i) std::memcpy(o.bytes.data() + i * w, (c.bytes[i] ? a.bytes.data() : b.bytes.data()) + i * w, w);
+  return o;
+}
+
+// Round a wide value to a float format and widen it again.
+double round_to(DType dt, double x) {
+  if (dt == DType::F64) return x;
+  uint8_t tmp[8];
+  f64_to_elem(dt, x, tmp);
+  return elem_to_f64(dt, tmp);
+}
+
+// kurumi_core/src/dtype/convert.rs:14-47: every cast goes through f64
+Val cast_val(const Val& a, DType to, bool wide_mode) {
+  const size_t n = numel(a.shape);
+  const bool out_wide = wide_mode && is_float(to);
+  Val o = make_val(to, a.shape, out_wide);
+  const size_t ws = esize(a), wo = esize(o);
+  if (!a.wide && !out_wide && a.dtype == to) { o.bytes = a.bytes; return o; }
+  for (size_t i = 0; i < n; ++i) {
+    double x = a.wide ? wd(a)[i] : elem_to_f64(a.dtype, a.bytes.data() + i * ws);
+    if (out_wide) wd(o)[i] = round_to(to, x);
+    else f64_to_elem(to, x, o.bytes.data() + i * wo);
+  }
+  return o;
+}
+
+Val narrow(const Val& a) {  // wide -> the logical dtype's own bytes
+  if (!a.wide) return a;
+  Val o = make_val(a.dtype, a.shape, false);
+  const size_t n = numel(a.shape), w = dtype_width(a.dtype);
+  for (size_t i = 0; i < n; ++i) f64_to_elem(a.dtype, wd(a)[i], o.bytes.data() + i * w);
+  return o;
+}
+Val widen(const Val& a) {
+  if (a.wide || !is_float(a.dtype)) return a;
+  Val o = make_val(a.dtype, a.shape, true);
+  const size_t n = numel(a.shape), w = dtype_width(a.dtype);
+  for (size_t i = 0; i < n; ++i) wd(o)[i] = elem_to_f64(a.dtype, a.bytes.data() + i * w);
+  return o;
+}
+
+// kurumi_core/src/dtype/convert.rs:150-152
+Val bitcast_val(const Val& a0, DType to, bool wide_mode) {
+  Val a = narrow(a0);
+  Val o = make_val(to, a.shape, false);
+  o.bytes = a.bytes;
+  if (to == DType::BOOL) for (auto& b : o.bytes) b = b ? 1 : 0;
+  return (wide_mode && is_float(to)) ? widen(o) : o;
+}
+
+// ---- reductions (kurumi_core/src/interp/reduce.rs:67-106) ---------------------------------------
+template <typename T, typename F>
+void reduce_fold(const T* data, const Shape& shape, size_t axis, T init, F f, T* out) {
+  auto st = row_major_strides(shape);
+  const size_t axis_len = shape[axis], axis_stride = st[axis];
+  Shape out_shape;
+  std::vector<size_t> base_strides;
+  for (size_t i = 0; i < shape.size(); ++i)
+    if (i != axis) { out_shape.push_back(shape[i]); base_strides.push_back(st[i]); }
+  const size_t out_len = std::max<size_t>(numel(out_shape), 1);
+  std::vector<size_t> coord(out_shape.size(), 0);
+  for (size_t o = 0; o < out_len; ++o) {
+    size_t base = 0;
+    for (size_t i = 0; i < coord.size(); ++i) base += coord[i] * base_strides[i];
+    T acc = init;
+    for (size_t k = 0; k < axis_len; ++k) acc = f(acc, data[base + k * axis_stride]);  // strict left fold
+    out[o] = acc;
+    inc(coord, out_shape);
+  }
+}
+
+Val reduce_val(OpKind k, const Val& a, size_t axis, bool wide_mode) {
+  Shape out_shape = a.shape;
+  out_shape.erase(out_shape.begin() + static_cast<long>(axis));
+  if (a.wide) {
+    Val o = make_val(a.dtype, out_shape, true);
+    if (k == OpKind::Sum) reduce_fold<double>(wd(a), a.shape, axis, 0.0, [](double p, double q) { return p + q; }, wd(o));
+    else if (k == OpKind::Prod) reduce_fold<double>(wd(a), a.shape, axis, 1.0, [](double p, double q) { return p * q; }, wd(o));
+    else reduce_fold<double>(wd(a), a.shape, axis, -std::numeric_limits<double>::infinity(), [](double p, double q) { return std::fmax(p, q); }, wd(o));
+    return o;
+  }
+  (void)wide_mode;
+  if (is_low_float(a.dtype) && k != OpKind::ReduceMax) {  // promote to f32, fold, round once
+    Val f = cast_val(a, DType::F32, false);
+    Val r = reduce_val(k, f, axis, false);
+    return cast_val(r, a.dtype, false);
+  }
+  Val o = make_val(a.dtype, out_shape, false);
+  KO_NUMERIC(a.dtype, {
+    using T = E<DT>;
+    using C = typename T::C;
+    if constexpr (std::is_same_v<typename T::S, C>) {
+      auto* x = reinterpret_cast<const C*>(a.bytes.data());
+      auto* z = reinterpret_cast<C*>(o.bytes.data());
+      if (k == OpKind::Sum) reduce_fold<C>(x, a.shape, axis, C(0), [](C p, C q) { return op_add(p, q); }, z);
+      else if (k == OpKind::Prod) reduce_fold<C>(x, a.shape, axis, C(1), [](C p, C q) { return op_mul(p, q); }, z);
+      else {
+        C lowest = std::is_floating_point_v<C> ? -std::numeric_limits<C>::infinity() : std::numeric_limits<C>::lowest();
+        reduce_fold<C>(x, a.shape, axis, lowest, [](C p, C q) { return op_max(p, q); }, z);
+      }
+    } else {  // low-precision ReduceMax: identity is the format's lowest (float.rs:38-72), max is exact
+      using S = typename T::S;
+      auto* x = reinterpret_cast<const S*>(a.bytes.data());
+      auto* z = reinterpret_cast<S*>(o.bytes.data());
+      S lowest = (DT == DType::F16 || DT == DType::BF16) ? T::st(-std::numeric_limits<float>::infinity()) : T::st(std::numeric_limits<float>::lowest());
+      reduce_fold<S>(x, a.shape, axis, lowest, [](S p, S q) { return T::st(std::fmax(T::ld(p), T::ld(q))); }, z);
+    }
+  })
+  return o;
+}
+
+}  // namespace
+void reduce_f32(OpKind k, const float* data, const Shape& shape, size_t axis, float* out) {
+  if (k == OpKind::Sum) reduce_fold<float>(data, shape, axis, 0.0f, [](float p, float q) { return p + q; }, out);
+  else reduce_fold<float>(data, shape, axis, -std::numeric_limits<float>::infinity(), [](float p, float q) { return std::fmax(p, q); }, out);
+}
+namespace {
+// ---- movement (kurumi_core/src/interp/movement.rs:37-118): per-output-element gathers -----------
+Val movement_val(const Op& op, const Val& a) {
+  const size_t w = esize(a);
+  const Shape& in_shape = a.shape;
+  auto in_st = row_major_strides(in_shape);
+  if (op.kind == OpKind::Reshape) { Val o = a; o.shape = op.shape; return o; }
+  Shape out_shape;
+  switch (op.kind) {
+    case OpKind::Permute: for (size_t p : op.perm) out_shape.push_back(in_shape[p]); break;
+    case OpKind::Expand: out_shape = op.shape; break;
+    case OpKind::Slice: for (auto& r : op.ranges) out_shape.push_back((r[1] - r[0] + r[2] - 1) / r[2]); break;
+    case OpKind::Flip: out_shape = in_shape; break;
+    case OpKind::Pad: for (size_t d = 0; d < in_shape.size(); ++d) out_shape.push_back(op.ranges[d][0] + in_shape[d] + op.ranges[d][1]); break;
+    default: throw Error("oracle: not a movement op");
+  }
+  Val o = make_val(a.dtype, out_shape, a.wide);
+  const size_t out_len = numel(out_shape) == 0 && out_shape.empty() ? 1 : numel(out_shape);
+  std::vector<size_t> coord(out_shape.size(), 0);
+  std::vector<bool> flipped(in_shape.size(), false);
+  if (op.kind == OpKind::Flip) for (size_t ax : op.perm) flipped[ax] = true;
+  for (size_t idx = 0; idx < out_len; ++idx) {
+    size_t in_flat = 0;
+    bool valid = true;
+    switch (op.kind) {
+      case OpKind::Permute: for (size_t i = 0; i < coord.size(); ++i) in_flat += coord[i] * in_st[op.perm[i]]; break;
+      case OpKind::Expand: for (size_t d = 0; d < coord.size(); ++d) in_flat += in_shape[d] == 1 ? 0 : coord[d] * in_st[d]; break;
+      case OpKind::Slice: for (size_t d = 0; d < coord.size(); ++d) in_flat += (op.ranges[d][0] + coord[d] * op.ranges[d][2]) * in_st[d]; break;
+      case OpKind::Flip: for (size_t d = 0; d < coord.size(); ++d) in_flat += (flipped[d] ? in_shape[d] - 1 - coord[d] : coord[d]) * in_st[d]; break;
+      case OpKind::Pad:
+        for (size_t d = 0; d < coord.size(); ++d) {
+          size_t lo = op.ranges[d][0];
+          if (coord[d] < lo || coord[d] >= lo + in_shape[d]) { valid = false; break; }
+          in_flat += (coord[d] - lo) * in_st[d];
+        }
+        break;
+      default: break;
+    }
+    if (valid) std::memcpy(o.bytes.data() + idx * w, a.bytes.data() + in_flat * w, w);  // else stays 0
+    inc(coord, out_shape);
+  }
+  return o;
+}
+
+// ---- contraction (kurumi_core/src/interp/contract.rs:26-166, contract/gemm.rs:8-113) -----------
+template <typename T>
+void dot_num(const T* a, const Shape& as, const T* b, const Shape& bs, const Op& op, T* out) {
+  auto a_st = row_major_strides(as), b_st = row_major_strides(bs);
+  auto a_free = free_axes(as.size(), op.lb, op.lc), b_free = free_axes(bs.size(), op.rb, op.rc);
+  Shape out_shape, c_sizes;
+  for (size_t i : op.lb) out_shape.push_back(as[i]);
+  for (size_t i : a_free) out_shape.push_back(as[i]);
+  for (size_t i : b_free) out_shape.push_back(bs[i]);
+  for (size_t i : op.lc) c_sizes.push_back(as[i]);
+  const size_t nb = op.lb.size(), nlf = a_free.size();
+  const size_t out_len = std::max<size_t>(numel(out_shape), out_shape.empty() ? 1 : 0);
+  const size_t c_len = c_sizes.empty() ? 1 : numel(c_sizes);
+  std::vector<size_t> oc(out_shape.size(), 0), cc(c_sizes.size(), 0);
+  for (size_t o = 0; o < out_len; ++o) {
+    size_t abase = 0, bbase = 0;
+    for (size_t i = 0; i < nb; ++i) { abase += oc[i] * a_st[op.lb[i]]; bbase += oc[i] * b_st[op.rb[i]]; }
+    for (size_t i = 0; i < a_free.size(); ++i) abase += oc[nb + i] * a_st[a_free[i]];
+    for (size_t i = 0; i < b_free.size(); ++i) bbase += oc[nb + nlf + i] * b_st[b_free[i]];
+    T acc = T(0);
+    std::fill(cc.begin(), cc.end(), 0);
+    for (size_t c = 0; c < c_len; ++c) {
+      size_t ai = abase, bi = bbase;
+      for (size_t j = 0; j < cc.size(); ++j) { ai += cc[j] * a_st[op.lc[j]]; bi += cc[j] * b_st[op.rc[j]]; }
+      acc = op_add(acc, op_mul(a[ai], b[bi]));
+      inc(cc, c_sizes);
+    }
+    out[o] = acc;
+    inc(oc, out_shape);
+  }
+}
+
+// f32 2-D single-contract fast path. Stand-in for the un-vendored `gemm` crate: f32 multiply,
+// f32 add, k ascending per output element (row-panel order so it vectorises over n).
+void sgemm_2d(size_t m, size_t n, size_t k, float* out, const float* a, size_t a_fs, size_t a_cs, const float* b, size_t b_fs, size_t b_cs) {
+  std::fill(out, out + m * n, 0.0f);
+  if (b_fs == 1) {
+    for (size_t i = 0; i < m; ++i)
+      for (size_t kk = 0; kk < k; ++kk) {
+        const float av = a[i * a_fs + kk * a_cs];
+        const float* brow = b + kk * b_cs;
+        float* orow = out + i * n;
+        for (size_t j = 0; j < n; ++j) orow[j] += av * brow[j];
+      }
+  } else {
+    for (size_t i = 0; i < m; ++i)
+      for (size_t j = 0; j < n; ++j) {
+        float acc = 0.0f;
+        for (size_t kk = 0; kk < k; ++kk) acc += a[i * a_fs + kk * a_cs] * b[j * b_fs + kk * b_cs];
+        out[i * n + j] = acc;
+      }
+  }
+}
+
+Shape dot_out_shape(const Shape& as, const Shape& bs, const Op& op) {
+  Shape o;
+  for (size_t i : op.lb) o.push_back(as[i]);
+  for (size_t i : free_axes(as.size(), op.lb, op.lc)) o.push_back(as[i]);
+  for (size_t i : free_axes(bs.size(), op.rb, op.rc)) o.push_back(bs[i]);
+  return o;
+}
+
+Val dot_f32(const Val& a, const Val& b, const Op& op) {
+  Val o = make_val(DType::F32, dot_out_shape(a.shape, b.shape, op), false);
+  auto* x = reinterpret_cast<const float*>(a.bytes.data());
+  auto* y = reinterpret_cast<const float*>(b.bytes.data());
+  auto* z = reinterpret_cast<float*>(o.bytes.data());
+  if (a.shape.size() == 2 && b.shape.size() == 2 && op.lb.empty() && op.lc.size() == 1) {
+    size_t lc = op.lc[0], rc = op.rc[0], lf = 1 - lc, rf = 1 - rc;
+    size_t m = a.shape[lf], k = a.shape[lc], n = b.shape[rf];
+    auto a_st = row_major_strides(a.shape), b_st = row_major_strides(b.shape);
+    if (m && n && k) sgemm_2d(m, n, k, z, x, a_st[lf], a_st[lc], y, b_st[rf], b_st[rc]);
+    return o;
+  }
+  dot_num<float>(x, a.shape, y, b.shape, op, z);
+  return o;
+}
+
+Val dot_val(const Val& a, const Val& b, const Op& op) {
+  if (a.wide) {
+    Val o = make_val(a.dtype, dot_out_shape(a.shape, b.shape, op), true);
+    dot_num<double>(wd(a), a.shape, wd(b), b.shape, op, wd(o));
+    return o;
+  }
+  if (a.dtype == DType::F32) return dot_f32(a, b, op);
+  if (is_low_float(a.dtype)) {  // dot_promoted: f32 GEMM, one rounding of the result
+    Val r = dot_f32(cast_val(a, DType::F32, false), cast_val(b, DType::F32, false), op);
+    return cast_val(r, a.dtype, false);
+  }
+  Val o = make_val(a.dtype, dot_out_shape(a.shape, b.shape, op), false);
+  KO_NUMERIC(a.dtype, {
+    using T = E<DT>;
+    if constexpr (std::is_same_v<typename T::S, typename T::C>) {
+      using C = typename T::C;
+      dot_num<C>(reinterpret_cast<const C*>(a.bytes.data()), a.shape, reinterpret_cast<const C*>(b.bytes.data()), b.shape, op, reinterpret_cast<C*>(o.bytes.data()));
+    }
+  })
+  return o;
+}
+
+// ---- nn oracles (kurumi_core/src/interp/nn.rs:18-172) -------------------------------------------
+template <typename T>
+void softmax_lines(const T* data, const Shape& shape, size_t axis, T* out) {
+  auto st = row_major_strides(shape);
+  const size_t axis_len = shape[axis], axis_stride = st[axis];
+  Shape out_shape;
+  std::vector<size_t> base_strides;
+  for (size_t i = 0; i < shape.size(); ++i)
+    if (i != axis) { out_shape.push_back(shape[i]); base_strides.push_back(st[i]); }
+  const size_t out_len = std::max<size_t>(numel(out_shape), out_shape.empty() ? 1 : 0);
+  std::vector<size_t> coord(out_shape.size(), 0);
+  for (size_t o = 0; o < out_len; ++o) {
+    size_t base = 0;
+    for (size_t i = 0; i < coord.size(); ++i) base += coord[i] * base_strides[i];
+    T m = -std::numeric_limits<T>::infinity();
+    for (size_t k = 0; k < axis_len; ++k) m = std::fmax(m, data[base + k * axis_stride]);
+    T sum = 0;
+    for (size_t k = 0; k < axis_len; ++k) {
+      T e = std::exp(data[base + k * axis_stride] - m);
+      out[base + k * axis_stride] = e;
+      sum += e;
+    }
+    for (size_t k = 0; k < axis_len; ++k) out[base + k * axis_stride] /= sum;
+    inc(coord, out_shape);
+  }
+}
+
+Val softmax_val(const Val& a, size_t axis) {
+  if (a.wide || a.dtype == DType::F64) {
+    Val o = make_val(a.dtype, a.shape, a.wide);
+    softmax_lines<double>(reinterpret_cast<const double*>(a.bytes.data()), a.shape, axis, reinterpret_cast<double*>(o.bytes.data()));
+    return o;
+  }
+  Val f = cast_val(a, DType::F32, false);
+  Val r = make_val(DType::F32, a.shape, false);
+  softmax_lines<float>(reinterpret_cast<const float*>(f.bytes.data()), a.shape, axis, reinterpret_cast<float*>(r.bytes.data()));
+  return a.dtype == DType::F32 ? r : cast_val(r, a.dtype, false);
+}
+
+template <typename T>
+void rmsnorm_lines(const T* data, const Shape& shape, size_t axis, T eps, T* out) {
+  auto st = row_major_strides(shape);
+  const size_t axis_len = shape[axis], axis_stride = st[axis];
+  Shape out_shape;
+  std::vector<size_t> base_strides;
+  for (size_t i = 0; i < shape.size(); ++i)
+    if (i != axis) { out_shape.push_back(shape[i]); base_strides.push_back(st[i]); }
+  const size_t out_len = std::max<size_t>(numel(out_shape), out_shape.empty() ? 1 : 0);
+  std::vector<size_t> coord(out_shape.size(), 0);
+  for (size_t o = 0; o < out_len; ++o) {
+    size_t base = 0;
+    for (size_t i = 0; i < coord.size(); ++i) base += coord[i] * base_strides[i];
+    T ss = 0;
+    for (size_t k = 0; k < axis_len; ++k) { T x = data[base + k * axis_stride]; ss += x * x; }
+    T rms = std::sqrt(ss / static_cast<T>(axis_len) + eps);
+    for (size_t k = 0; k < axis_len; ++k) out[base + k * axis_stride] = data[base + k * axis_stride] / rms;
+    inc(coord, out_shape);
+  }
+}
+
+Val rmsnorm_val(const Val& a, size_t axis, float eps) {
+  if (a.wide || a.dtype == DType::F64) {
+    Val o = make_val(a.dtype, a.shape, a.wide);
+    rmsnorm_lines<double>(reinterpret_cast<const double*>(a.bytes.data()), a.shape, axis, static_cast<double>(eps), reinterpret_cast<double*>(o.bytes.data()));
+    return o;
+  }
+  Val f = cast_val(a, DType::F32, false);
+  Val r = make_val(DType::F32, a.shape, false);
+  rmsnorm_lines<float>(reinterpret_cast<const float*>(f.bytes.data()), a.shape, axis, eps, reinterpret_cast<float*>(r.bytes.data()));
+  return a.dtype == DType::F32 ? r : cast_val(r, a.dtype, false);
+}
+
+template <typename T>
+void scale_causal(const T* data, size_t total, size_t s, T scale, bool causal, T* out) {
+  const size_t block = s * s;
+  for (size_t base = 0; base < total; base += std::max<size_t>(block, 1))
+    for (size_t i = 0; i < s; ++i)
+      for (size_t j = 0; j < s; ++j) {
+        size_t idx = base + i * s + j;
+        out[idx] = (causal && j > i) ? -std::numeric_limits<T>::infinity() : data[idx] * scale;
+      }
+}
+
+Val sdpa_val(const Val& q, const Val& k, const Val& v, bool causal) {
+  const size_t r = q.shape.size();
+  const size_t s = q.shape[r - 2], dh = q.shape[r - 1];
+  Op qk; qk.kind = OpKind::DotGeneral; qk.lc = {r - 1}; qk.rc = {r - 1};
+  for (size_t i = 0; i + 2 < r; ++i) { qk.lb.push_back(i); qk.rb.push_back(i); }
+  Val raw = dot_val(q, k, qk);
+  const float scale = 1.0f / std::sqrt(static_cast<float>(dh));
+  Val scores;
+  if (raw.wide || raw.dtype == DType::F64) {
+    scores = make_val(raw.dtype, raw.shape, raw.wide);
+    scale_causal<double>(reinterpret_cast<const double*>(raw.bytes.data()), numel(raw.shape), s, static_cast<double>(scale), causal, reinterpret_cast<double*>(scores.bytes.data()));
+  } else {
+    Val f = cast_val(raw, DType::F32, false);
+    Val o = make_val(DType::F32, raw.shape, false);
+    scale_causal<float>(reinterpret_cast<const float*>(f.bytes.data()), numel(raw.shape), s, scale, causal, reinterpret_cast<float*>(o.bytes.data()));
+    scores = raw.dtype == DType::F32 ? o : cast_val(o, raw.dtype, false);
+  }
+  Val attn = softmax_val(scores, r - 1);
+  Op av; av.kind = OpKind::DotGeneral; av.lc = {r - 1}; av.rc = {r - 2}; av.lb = qk.lb; av.rb = qk.rb;
+  return dot_val(attn, v, av);
+}
+
+// ---- generation (kurumi_core/src/interp/random.rs:10-28, dtype/convert.rs:72-80) ----------------
+Val iota_val(const Op& op, bool wide_mode) {
+  const size_t len = numel(op.shape);
+  size_t stride = 1;
+  for (size_t i = op.axis + 1; i < op.shape.size(); ++i) stride *= op.shape[i];
+  const size_t axis_len = op.shape[op.axis];
+  Val o = make_val(op.to, op.shape, false);
+  const size_t w = dtype_width(op.to);
+  for (size_t flat = 0; flat < len; ++flat) f64_to_elem(op.to, static_cast<double>((flat / stride) % axis_len), o.bytes.data() + flat * w);
+  return (wide_mode && is_float(op.to)) ? widen(o) : o;
+}
+
+Val rand_val(const Op& op, const Val& seed_v, bool wide_mode) {
+  Val sv = narrow(seed_v);
+  uint64_t seed = static_cast<uint64_t>(static_cast<int64_t>(0));
+  switch (sv.dtype) {  // read the first element as i64 (sign-extending signed types), then as u64
+    case DType::U8: seed = *reinterpret_cast<const uint8_t*>(sv.bytes.data()); break;
+    case DType::U16: seed = *reinterpret_cast<const uint16_t*>(sv.bytes.data()); break;
+    case DType::U32: seed = *reinterpret_cast<const uint32_t*>(sv.bytes.data()); break;
+    case DType::U64: seed = *reinterpret_cast<const uint64_t*>(sv.bytes.data()); break;
+    case DType::I8: seed = static_cast<uint64_t>(static_cast<int64_t>(*reinterpret_cast<const int8_t*>(sv.bytes.data()))); break;
+    case DType::I16: seed = static_cast<uint64_t>(static_cast<int64_t>(*reinterpret_cast<const int16_t*>(sv.bytes.data()))); break;
+    case DType::I32: seed = static_cast<uint64_t>(static_cast<int64_t>(*reinterpret_cast<const int32_t*>(sv.bytes.data()))); break;
+    case DType::I64: seed = static_cast<uint64_t>(*reinterpret_cast<const int64_t*>(sv.bytes.data())); break;
+    default: throw Error("oracle: rand_uniform seed must be an integer tensor");
+  }
+  const size_t n = std::max<size_t>(numel(op.shape), op.shape.empty() ? 1 : 0);
+  Val o = make_val(DType::F32, op.shape, false);
+  auto* z = reinterpret_cast<float*>(o.bytes.data());
+  for (size_t i = 0; i < n; ++i) z[i] = uniform_f32(threefry2x32(seed, i));
+  return wide_mode ? widen(o) : o;
+}
+
+Val from_tensor(const Tensor& t, bool wide_mode) {
+  Val v;
+  v.shape = t.shape; v.dtype = t.dtype; v.wide = false; v.bytes = t.bytes;
+  return (wide_mode && is_float(t.dtype)) ? widen(v) : v;
+}
+
+}  // namespace
+
+// kurumi_core/src/interp.rs:62-112: one primitive given its materialised inputs
+Val eval_op(const Node& n, const std::vector<const Val*>& in, bool wide_mode) {
+  const Op& op = n.op;
+  switch (op.kind) {
+    case OpKind::Const: return from_tensor(*op.data, wide_mode);
+    case OpKind::Input: throw Error("panic: Input must be resolved from feeds before eval_op");
+    case OpKind::Detach: return *in[0];
+    case OpKind::Iota: return iota_val(op, wide_mode);
+    case OpKind::RandUniform: return rand_val(op, *in[0], wide_mode);
+    case OpKind::Cast: return cast_val(*in[0], op.to, wide_mode);
+    case OpKind::Bitcast: return bitcast_val(*in[0], op.to, wide_mode);
+    case OpKind::Add: case OpKind::Mul: case OpKind::Max: case OpKind::IDiv: case OpKind::And: case OpKind::Or:
+    case OpKind::Xor: case OpKind::Shl: case OpKind::Shr: case OpKind::CmpLt: case OpKind::CmpEq:
+      return ew_binary(op.kind, *in[0], *in[1]);
+    case OpKind::Where: return ew_where(*in[0], *in[1], *in[2]);
+    case OpKind::Neg: case OpKind::Recip: case OpKind::Sqrt: case OpKind::Exp2: case OpKind::Log2: case OpKind::Sin:
+    case OpKind::Floor:
+      return ew_unary(op.kind, *in[0]);
+    case OpKind::Sum: case OpKind::Prod: case OpKind::ReduceMax: return reduce_val(op.kind, *in[0], op.axis, wide_mode);
+    case OpKind::Softmax: return softmax_val(*in[0], op.axis);
+    case OpKind::RmsNorm: return rmsnorm_val(*in[0], op.axis, op.eps);
+    case OpKind::Sdpa: return sdpa_val(*in[0], *in[1], *in[2], op.causal);
+    case OpKind::Reshape: case OpKind::Permute: case OpKind::Expand: case OpKind::Slice: case OpKind::Flip: case OpKind::Pad:
+      return movement_val(op, *in[0]);
+    case OpKind::DotGeneral: return dot_val(*in[0], *in[1], op);
+  }
+  throw Error("oracle: unknown op");
+}
+
+Tensor to_tensor(const Val& v) {
+  Tensor t;
+  t.shape = v.shape;
+  t.dtype = v.wide ? DType::F64 : v.dtype;
+  t.bytes = v.bytes;
+  return t;
+}
+
+// kurumi_core/src/interp.rs:25-56: memoised walk; a missing feed is an error
+std::vector<Tensor> interpret_many(const Graph& g, const std::vector<NodeId>& ids, const Feeds& feeds, bool wide_mode) {
+  std::unordered_map<NodeId, Val> memo;
+  for (NodeId id : reachable(g, ids)) {  // topological order: every source is evaluated first
+    const Node& n = g.node(id);
+    if (n.op.kind == OpKind::Input) {
+      auto it = feeds.find(id);
+      if (it == feeds.end()) throw Error("panic: interpret: missing feed for an Input node");
+      memo.emplace(id, from_tensor(*it->second, wide_mode));
+      continue;
+    }
+    std::vector<const Val*> in;
+    for (NodeId s : n.src) in.push_back(&memo.at(s));
+    memo.emplace(id, eval_op(n, in, wide_mode));
+  }
+  std::vector<Tensor> out;
+  for (NodeId id : ids) out.push_back(to_tensor(memo.at(id)));
+  return out;
+}
+
+}  // namespace ko
