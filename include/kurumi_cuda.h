@@ -1,0 +1,84 @@
+/* Extensions of the kurumi C ABI that only the CUDA library exports: device-resident tensors and
+ * evaluation (so a caller can keep weights and activations in HBM between evals), the backend's
+ * stream, timing and launch statistics, and the mixed-precision pass with a target dtype.
+ * None of these has a counterpart in the reference header kurumi/include/kurumi.h; the closest
+ * reference behaviour is cited per entry. Same conventions as kurumi.h: opaque handles, NULL / -1
+ * / KU_ERR on error with the message in ku_last_error(), not thread-safe per handle. */
+#ifndef KURUMI_CUDA_H
+#define KURUMI_CUDA_H
+
+#include "kurumi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct KuDevTensor KuDevTensor;
+typedef struct KuDevFeeds KuDevFeeds;
+
+/* A CUDA backend on a chosen device of this process (ku_backend_new(KU_CUDA) uses device 0).
+ * Fails (NULL) when no sm_100 device is visible: there is no CPU fallback. */
+KuBackend *ku_cuda_backend_new(int32_t device);
+
+/* Host -> device copy of a tensor into a new device tensor (stream-ordered on the backend's
+ * stream). ku_cuda_upload_bytes reads `nbytes` from the caller's buffer, which must stay valid
+ * until ku_cuda_sync when it is pinned memory. Reference analogue: the Metal backend's const
+ * upload, kurumi_metal/src/backend/eval_walk.rs:99-114. */
+KuDevTensor *ku_cuda_upload(const KuBackend *b, const KuTensor *t);
+KuDevTensor *ku_cuda_upload_bytes(const KuBackend *b, uint32_t dtype, const void *data, size_t nbytes, const size_t *shape, size_t rank);
+/* Device -> host: a new KuTensor, or raw bytes into `out` (>= ku_cuda_dev_nbytes). Both wait for the result. */
+KuTensor *ku_cuda_download(const KuBackend *b, const KuDevTensor *t);
+int32_t ku_cuda_download_bytes(const KuBackend *b, const KuDevTensor *t, void *out, size_t cap);
+void ku_cuda_dev_free(const KuBackend *b, KuDevTensor *t);
+void *ku_cuda_dev_ptr(const KuDevTensor *t);
+size_t ku_cuda_dev_nbytes(const KuDevTensor *t);
+size_t ku_cuda_dev_rank(const KuDevTensor *t);
+void ku_cuda_dev_shape(const KuDevTensor *t, size_t *out);
+uint32_t ku_cuda_dev_dtype(const KuDevTensor *t);
+
+/* Feeds that already live on the device (the tensor is borrowed, not copied). */
+KuDevFeeds *ku_cuda_dev_feeds_new(void);
+void ku_cuda_dev_feeds_free(KuDevFeeds *f);
+void ku_cuda_dev_feeds_set(KuDevFeeds *f, KuNode node, const KuDevTensor *t);
+
+/* ku_eval_many (kurumi.h:387) with device-resident outputs: evaluates ids[0..n] in one shared
+ * pass and writes a new KuDevTensor per id into out. `feeds` and `dev_feeds` may each be NULL.
+ * Asynchronous: returns once the work is queued on the backend's stream. 0 ok, -1 error. */
+int32_t ku_cuda_eval_device(KuGraph *g, const KuNode *ids, size_t n, const KuBackend *b, const KuFeeds *feeds,
+                            const KuDevFeeds *dev_feeds, KuDevTensor **out);
+
+int32_t ku_cuda_sync(const KuBackend *b);        /* wait for the backend's stream */
+void *ku_cuda_stream(const KuBackend *b);        /* the cudaStream_t every launch of this backend goes to */
+int32_t ku_cuda_device(const KuBackend *b);
+
+/* Counters since backend creation, in this order: kernel launches, NVRTC compiles, NVRTC cache
+ * hits, host->device bytes, device->host bytes, device allocations, pool hits. Returns how many
+ * were written. Reference analogue: KURUMI_PHASE statistics, kurumi_metal/src/backend.rs:68-90. */
+size_t ku_cuda_stats(const KuBackend *b, uint64_t *out, size_t cap);
+/* Per-kernel-family device time, measured with CUDA events around every launch while enabled.
+ * ku_cuda_profile_take writes a text table ("family launches ms algo_bytes flops" per line) into
+ * out (no NUL), returns its full length, and resets the accumulators. Reference analogue:
+ * KURUMI_GPUTIME, kurumi_metal/src/context/encoder.rs:44-47. */
+void ku_cuda_profile_enable(const KuBackend *b, uint32_t on);
+size_t ku_cuda_profile_take(const KuBackend *b, uint8_t *out, size_t cap);
+
+/* ku_amp (kurumi.h:395) with a target dtype: KU_F16 is the reference pass; KU_BF16 the same
+ * rewrite in bf16; KU_F8E4M3 quantises both operands of every contraction through
+ * cast(cast(x, F8E4M3), dtype) so the backend can feed fp8 to the tensor cores. */
+KuNode ku_cuda_amp_to(KuGraph *g, KuNode root, uint32_t dtype);
+
+/* The explicit forms of ku_sdpa (kurumi.h:343), which picks between them by the size of the score
+ * buffer: the fused primitive Op::Sdpa and the dot + softmax decomposition. They are public in the
+ * Rust API (kurumi_core/src/graph/ops/nn/attention.rs:97-133) but absent from the reference's C header. */
+KuNode ku_sdpa_fused(KuGraph *g, KuNode q, KuNode k, KuNode v, uint32_t causal);
+KuNode ku_sdpa_decomposed(KuGraph *g, KuNode q, KuNode k, KuNode v, uint32_t causal);
+
+/* Compile every kernel the evaluation of ids[0..n] needs to an sm_100a cubin, without a GPU.
+ * Writes the kernel family of each launch, one per line, into out (no NUL); returns the full
+ * length, or (size_t)-1 on error. */
+size_t ku_cuda_compile_check(KuGraph *g, const KuNode *ids, size_t n, uint8_t *out, size_t cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KURUMI_CUDA_H */

@@ -53,6 +53,8 @@ class Library:
             getattr(L, name).restype = C.c_void_p
         for name in ("ku_tensor_rank", "ku_tensor_len", "ku_tensor_nbytes", "ku_node_rank", "ku_node_count", "ku_dump"):
             getattr(L, name).restype = C.c_size_t
+        for name in ("ku_node_dtype", "ku_tensor_dtype"):
+            getattr(L, name).restype = C.c_uint32
         L.ku_tensor_data_f32.restype = C.c_ssize_t
         L.ku_eval_many.restype = C.c_int32
         self._node_fns = {}
@@ -221,6 +223,12 @@ class Graph:
     def sdpa(self, q, k, v, causal: bool):
         return self._n("ku_sdpa", C.c_uint32(q), C.c_uint32(k), C.c_uint32(v), C.c_uint32(1 if causal else 0))
 
+    def sdpa_fused(self, q, k, v, causal: bool):
+        return self._n("ku_sdpa_fused", C.c_uint32(q), C.c_uint32(k), C.c_uint32(v), C.c_uint32(1 if causal else 0))
+
+    def sdpa_decomposed(self, q, k, v, causal: bool):
+        return self._n("ku_sdpa_decomposed", C.c_uint32(q), C.c_uint32(k), C.c_uint32(v), C.c_uint32(1 if causal else 0))
+
     # movement
     def reshape(self, x, shape):
         s, r = _sz(shape); return self._n("ku_reshape", C.c_uint32(x), s, C.c_size_t(r))
@@ -354,3 +362,134 @@ def e4m3_to_f32(bits: np.ndarray) -> np.ndarray:
     v = np.where(e == 0, m.astype(np.float64) * 2.0 ** -9, (8 + m).astype(np.float64) * np.exp2(e.astype(np.float64) - 10))
     v = np.where((b & 0x7F) == 0x7F, np.nan, v)
     return np.where(s == 1, -v, v).astype(np.float32)
+
+
+# ---- device-resident surface of include/kurumi_cuda.h -------------------------------------------
+class DevTensor:
+    def __init__(self, backend: "CudaBackend", handle):
+        if not handle:
+            raise Error(backend.lib.last_error() or "null device tensor")
+        self.backend, self.h = backend, C.c_void_p(handle)
+
+    @property
+    def nbytes(self) -> int:
+        return self.backend.lib.lib.ku_cuda_dev_nbytes(self.h)
+
+    @property
+    def ptr(self) -> int:
+        return self.backend.lib.lib.ku_cuda_dev_ptr(self.h) or 0
+
+    @property
+    def dtype(self) -> int:
+        return int(self.backend.lib.lib.ku_cuda_dev_dtype(self.h))
+
+    @property
+    def shape(self) -> tuple:
+        r = self.backend.lib.lib.ku_cuda_dev_rank(self.h)
+        out = (C.c_size_t * max(r, 1))()
+        self.backend.lib.lib.ku_cuda_dev_shape(self.h, out)
+        return tuple(out[i] for i in range(r))
+
+    def numpy(self) -> np.ndarray:
+        buf = np.empty(self.nbytes, dtype=np.uint8)
+        rc = self.backend.lib.lib.ku_cuda_download_bytes(self.backend.h, self.h, buf.ctypes.data_as(C.c_void_p), C.c_size_t(buf.nbytes))
+        if rc != 0:
+            raise Error(self.backend.lib.last_error())
+        return buf.view(_NP[self.dtype]).reshape(self.shape)
+
+    def download_into(self, ptr: int, cap: int):
+        rc = self.backend.lib.lib.ku_cuda_download_bytes(self.backend.h, self.h, C.c_void_p(ptr), C.c_size_t(cap))
+        if rc != 0:
+            raise Error(self.backend.lib.last_error())
+
+    def free(self):
+        if self.h:
+            self.backend.lib.lib.ku_cuda_dev_free(self.backend.h, self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class CudaBackend(Backend):
+    """ku_cuda_backend_new(device) plus the device-resident calls."""
+
+    def __init__(self, lib: Library, device: int = 0):
+        self.lib = lib
+        L = lib.lib
+        for name in ("ku_cuda_backend_new", "ku_cuda_upload", "ku_cuda_upload_bytes", "ku_cuda_download", "ku_cuda_dev_ptr",
+                     "ku_cuda_stream", "ku_cuda_dev_feeds_new"):
+            getattr(L, name).restype = C.c_void_p
+        for name in ("ku_cuda_dev_nbytes", "ku_cuda_dev_rank", "ku_cuda_stats", "ku_cuda_profile_take"):
+            getattr(L, name).restype = C.c_size_t
+        h = L.ku_cuda_backend_new(C.c_int32(device))
+        if not h:
+            raise Error(lib.last_error() or "CUDA backend unavailable")
+        self.h = C.c_void_p(h)
+
+    def upload(self, arr: np.ndarray, dtype: int | None = None) -> DevTensor:
+        t = Tensor.from_numpy(self.lib, arr, dtype)
+        return DevTensor(self, self.lib.lib.ku_cuda_upload(self.h, t.h))
+
+    def upload_ptr(self, ptr: int, nbytes: int, shape, dtype: int) -> DevTensor:
+        s, r = _sz(shape)
+        return DevTensor(self, self.lib.lib.ku_cuda_upload_bytes(self.h, C.c_uint32(dtype), C.c_void_p(ptr), C.c_size_t(nbytes), s, C.c_size_t(r)))
+
+    def eval_device(self, g: Graph, nodes, feeds: Feeds | None = None, dev_feeds: dict | None = None) -> list:
+        ids = (C.c_uint32 * max(len(nodes), 1))(*nodes)
+        out = (C.c_void_p * max(len(nodes), 1))()
+        df = C.c_void_p(self.lib.lib.ku_cuda_dev_feeds_new())
+        try:
+            for node, t in (dev_feeds or {}).items():
+                self.lib.lib.ku_cuda_dev_feeds_set(df, C.c_uint32(node), t.h)
+            rc = self.lib.lib.ku_cuda_eval_device(g.h, ids, C.c_size_t(len(nodes)), self.h, feeds.h if feeds else None, df, out)
+        finally:
+            self.lib.lib.ku_cuda_dev_feeds_free(df)
+        if rc != 0:
+            raise Error(self.lib.last_error())
+        return [DevTensor(self, out[i]) for i in range(len(nodes))]
+
+    def sync(self):
+        if self.lib.lib.ku_cuda_sync(self.h) != 0:
+            raise Error(self.lib.last_error())
+
+    @property
+    def stream(self) -> int:
+        return self.lib.lib.ku_cuda_stream(self.h) or 0
+
+    def stats(self) -> dict:
+        out = (C.c_uint64 * 7)()
+        self.lib.lib.ku_cuda_stats(self.h, out, C.c_size_t(7))
+        keys = ["launches", "nvrtc_compiles", "nvrtc_hits", "h2d_bytes", "d2h_bytes", "pool_allocs", "pool_hits"]
+        return dict(zip(keys, [int(v) for v in out]))
+
+    def profile(self, on: bool):
+        self.lib.lib.ku_cuda_profile_enable(self.h, C.c_uint32(1 if on else 0))
+
+    def take_profile(self) -> dict:
+        buf = (C.c_uint8 * 65536)()
+        n = self.lib.lib.ku_cuda_profile_take(self.h, buf, C.c_size_t(65536))
+        res = {}
+        for line in bytes(buf[:n]).decode().splitlines():
+            name, launches, ms, nbytes, flops = line.split()
+            res[name] = {"launches": int(launches), "ms": float(ms), "algo_bytes": float(nbytes), "flops": float(flops)}
+        return res
+
+
+def compile_check(lib: Library, g: Graph, nodes) -> list:
+    """NVRTC-compile every kernel the evaluation needs (no GPU). Returns the kernel families."""
+    lib.lib.ku_cuda_compile_check.restype = C.c_size_t
+    ids = (C.c_uint32 * max(len(nodes), 1))(*nodes)
+    buf = (C.c_uint8 * 16384)()
+    n = lib.lib.ku_cuda_compile_check(g.h, ids, C.c_size_t(len(nodes)), buf, C.c_size_t(16384))
+    if n == C.c_size_t(-1).value:
+        raise Error(lib.last_error())
+    return bytes(buf[:n]).decode().split()
+
+
+def load_cuda_library() -> Library:
+    from . import build
+    return Library(build.LIB)

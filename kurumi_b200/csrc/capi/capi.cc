@@ -35,6 +35,8 @@ KuNode build(KuGraph* g, F&& f) {
 }  // namespace
 
 extern "C" {
+KuNode ku_sdpa_fused(KuGraph* g, KuNode q, KuNode k, KuNode v, uint32_t causal);
+KuNode ku_sdpa_decomposed(KuGraph* g, KuNode q, KuNode k, KuNode v, uint32_t causal);
 
 const char* ku_last_error(void) { return g_has_err ? g_last_err.c_str() : nullptr; }
 
@@ -151,6 +153,10 @@ KuNode ku_bitcast(KuGraph* g, KuNode x, uint32_t dtype) {
     return gr.bitcast(x, dt);
   });
 }
+// Graph::sdpa_fused / Graph::sdpa_decomposed of the Rust API (kurumi_core/src/graph/ops/nn/attention.rs:97-133);
+// the reference's C header exposes only the auto-selecting ku_sdpa.
+KuNode ku_sdpa_fused(KuGraph* g, KuNode q, KuNode k, KuNode v, uint32_t causal) { return build(g, [&](Graph& gr) { return gr.sdpa_fused(q, k, v, causal != 0); }); }
+KuNode ku_sdpa_decomposed(KuGraph* g, KuNode q, KuNode k, KuNode v, uint32_t causal) { return build(g, [&](Graph& gr) { return gr.sdpa_decomposed(q, k, v, causal != 0); }); }
 KuNode ku_sdpa(KuGraph* g, KuNode q, KuNode k, KuNode v, uint32_t causal) { return build(g, [&](Graph& gr) { return gr.sdpa(q, k, v, causal != 0); }); }
 
 KuNode ku_rand_uniform(KuGraph* g, const size_t* shape, size_t rank, uint64_t seed) { return build(g, [&](Graph& gr) { return gr.rand_uniform(to_shape(shape, rank), seed); }); }

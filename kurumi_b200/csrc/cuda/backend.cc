@@ -1,0 +1,229 @@
+#include "backend.h"
+
+#include <cstring>
+
+#include "../capi/handles.h"
+
+namespace ku::cu {
+
+CudaBackend::CudaBackend(int device) : rt_(device) {}
+
+CudaBackend::~CudaBackend() {
+  rt_.make_current();
+  cudaStreamSynchronize(rt_.stream());
+  for (auto& e : ev_pool_) { cudaEventDestroy(e.first); cudaEventDestroy(e.second); }
+}
+
+CudaBackend::Compiled& CudaBackend::program_for(const Graph& g, const std::vector<NodeId>& ids) {
+  for (NodeId id : ids) (void)g.node(id);
+  auto key = std::make_pair(g.id(), ids);
+  auto it = programs_.find(key);
+  if (it != programs_.end()) return *it->second;
+  auto c = std::make_unique<Compiled>();
+  c->prog = compile_program(rt_, g, ids);
+  c->temp_ptrs.assign(c->prog.slots.size(), nullptr);
+  Compiled& ref = *c;
+  programs_[key] = std::move(c);
+  return ref;
+}
+
+void* CudaBackend::const_ptr(const Graph& g, NodeId node) {
+  auto key = std::make_pair(g.id(), node);
+  auto it = consts_.find(key);
+  if (it != consts_.end()) return it->second;
+  const Tensor& t = *g.node(node).op.data;
+  void* p = rt_.alloc(std::max<size_t>(t.bytes.size(), 1));
+  if (!t.bytes.empty()) {
+    cuda_check(cudaMemcpyAsync(p, t.bytes.data(), t.bytes.size(), cudaMemcpyHostToDevice, rt_.stream()), "constant upload");
+    rt_.sync();  // the host buffer belongs to the graph; finish before anyone can free it
+    rt_.stats.h2d_bytes += t.bytes.size();
+  }
+  consts_[key] = p;
+  return p;
+}
+
+std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vector<NodeId>& ids, const Feeds& feeds, const DevFeeds& dev_feeds) {
+  rt_.make_current();
+  Compiled& c = program_for(g, ids);
+  Program& P = c.prog;
+  std::vector<void*> ptr(P.slots.size(), nullptr);
+  std::vector<void*> staged;  // host feeds uploaded for this run only
+  for (size_t i = 0; i < P.slots.size(); ++i) {
+    Slot& s = P.slots[i];
+    switch (s.kind) {
+      case Slot::Const: ptr[i] = const_ptr(g, s.node); break;
+      case Slot::Feed: {
+        auto d = dev_feeds.find(s.node);
+        if (d != dev_feeds.end()) {
+          if (d->second->dtype != s.dtype || d->second->shape != s.shape)
+            throw Error::backend("feed for node " + std::to_string(s.node) + " has shape " + shape_str(d->second->shape) + " " + dtype_name(d->second->dtype) +
+                                 ", the Input is " + shape_str(s.shape) + " " + dtype_name(s.dtype));
+          ptr[i] = d->second->ptr;
+          break;
+        }
+        auto h = feeds.find(s.node);
+        if (h == feeds.end()) {
+          for (void* p : staged) rt_.free(p);
+          throw Error("panic: interpret: missing feed for an Input node");
+        }
+        const Tensor& t = *h->second;
+        if (t.dtype != s.dtype || t.shape != s.shape) {
+          for (void* p : staged) rt_.free(p);
+          throw Error::backend("feed for node " + std::to_string(s.node) + " has shape " + shape_str(t.shape) + " " + dtype_name(t.dtype) + ", the Input is " +
+                               shape_str(s.shape) + " " + dtype_name(s.dtype));
+        }
+        void* p = rt_.alloc(std::max<size_t>(s.bytes, 1));
+        if (s.bytes) cuda_check(cudaMemcpyAsync(p, t.bytes.data(), s.bytes, cudaMemcpyHostToDevice, rt_.stream()), "feed upload");
+        rt_.stats.h2d_bytes += s.bytes;
+        staged.push_back(p);
+        ptr[i] = p;
+        break;
+      }
+      case Slot::Temp:
+        if (!c.temp_ptrs[i]) c.temp_ptrs[i] = rt_.alloc(std::max<size_t>(s.bytes, 1));
+        ptr[i] = c.temp_ptrs[i];
+        break;
+      case Slot::Out: ptr[i] = rt_.alloc(std::max<size_t>(s.bytes, 1)); break;
+    }
+  }
+  // issue the cached launches
+  for (const Launch& L : P.launches) {
+    std::vector<void*> vals(L.args.size());
+    std::vector<CUtensorMap> maps(L.args.size());
+    std::vector<void*> argv(L.args.size());
+    for (size_t a = 0; a < L.args.size(); ++a) {
+      const Arg& A = L.args[a];
+      if (A.kind == Arg::SlotPtr) {
+        vals[a] = static_cast<char*>(ptr[static_cast<size_t>(A.slot)]) + A.byte_offset;
+        argv[a] = &vals[a];
+      } else if (A.kind == Arg::Bytes) {
+        argv[a] = const_cast<uint8_t*>(A.bytes.data());
+      } else {
+        const TmapSpec& t = A.tm;
+        maps[a] = rt_.tensor_map(static_cast<char*>(ptr[static_cast<size_t>(t.slot)]) + t.byte_offset, t.dt, t.rank, t.dims, t.strides, t.box, t.swz);
+        argv[a] = &maps[a];
+      }
+    }
+    size_t ev = 0;
+    if (profiling_) {
+      if (ev_used_ == ev_pool_.size()) {
+        cudaEvent_t a, b;
+        cuda_check(cudaEventCreate(&a), "cudaEventCreate");
+        cuda_check(cudaEventCreate(&b), "cudaEventCreate");
+        ev_pool_.push_back({a, b});
+      }
+      ev = ev_used_++;
+      cuda_check(cudaEventRecord(ev_pool_[ev].first, rt_.stream()), "cudaEventRecord");
+    }
+    rt_.launch(L.kernel, L.grid, L.block, L.cluster, L.smem, argv.data());
+    if (profiling_) {
+      cuda_check(cudaEventRecord(ev_pool_[ev].second, rt_.stream()), "cudaEventRecord");
+      pending_.push_back({ev, &L});
+    }
+  }
+  // staged feed buffers return to the pool; stream order keeps them valid until the kernels that read them finish,
+  // because the pool hands memory only to later work on this same stream
+  for (void* p : staged) rt_.free(p);
+  std::vector<DevTensor*> outs;
+  for (int os : P.out_slots) {
+    const Slot& s = P.slots[static_cast<size_t>(os)];
+    auto* t = new DevTensor();
+    t->ptr = ptr[static_cast<size_t>(os)]; t->bytes = s.bytes; t->dtype = s.dtype; t->shape = s.shape;
+    // the same slot requested twice: give the second handle its own copy
+    for (DevTensor* prev : outs)
+      if (prev->ptr == t->ptr) {
+        t->ptr = rt_.alloc(std::max<size_t>(s.bytes, 1));
+        if (s.bytes) cuda_check(cudaMemcpyAsync(t->ptr, prev->ptr, s.bytes, cudaMemcpyDeviceToDevice, rt_.stream()), "output copy");
+        break;
+      }
+    outs.push_back(t);
+  }
+  return outs;
+}
+
+DevTensor* CudaBackend::upload(DType dt, const Shape& shape, const void* host, size_t bytes) {
+  rt_.make_current();
+  if (bytes != numel(shape) * dtype_width(dt)) throw Error::backend("upload: byte count does not match shape " + shape_str(shape));
+  auto* t = new DevTensor();
+  t->ptr = rt_.alloc(std::max<size_t>(bytes, 1)); t->bytes = bytes; t->dtype = dt; t->shape = shape;
+  if (bytes) cuda_check(cudaMemcpyAsync(t->ptr, host, bytes, cudaMemcpyHostToDevice, rt_.stream()), "upload");
+  rt_.stats.h2d_bytes += bytes;
+  return t;
+}
+
+void CudaBackend::download(const DevTensor& t, void* host) {
+  rt_.make_current();
+  if (t.bytes) cuda_check(cudaMemcpyAsync(host, t.ptr, t.bytes, cudaMemcpyDeviceToHost, rt_.stream()), "download");
+  rt_.sync();
+  rt_.stats.d2h_bytes += t.bytes;
+}
+
+void CudaBackend::free_dev(DevTensor* t) {
+  if (!t) return;
+  if (t->owned) rt_.free(t->ptr);
+  delete t;
+}
+
+std::vector<Tensor> CudaBackend::eval_many_with(const Graph& g, const std::vector<NodeId>& ids, const Feeds& feeds) {
+  std::vector<DevTensor*> outs = eval_device(g, ids, feeds, DevFeeds{});
+  std::vector<Tensor> res;
+  try {
+    for (DevTensor* d : outs) {
+      Tensor t = Tensor::make(d->dtype, d->shape);
+      download(*d, t.bytes.data());
+      res.push_back(std::move(t));
+    }
+  } catch (...) {
+    for (DevTensor* d : outs) free_dev(d);
+    throw;
+  }
+  for (DevTensor* d : outs) free_dev(d);
+  return res;
+}
+
+Tensor CudaBackend::eval_with(const Graph& g, NodeId id, const Feeds& feeds) { return std::move(eval_many_with(g, {id}, feeds)[0]); }
+
+void CudaBackend::set_profiling(bool on) {
+  drain_profile();
+  profiling_ = on;
+}
+
+void CudaBackend::drain_profile() {
+  if (pending_.empty()) return;
+  rt_.sync();
+  for (auto& p : pending_) {
+    float ms = 0;
+    cudaEventElapsedTime(&ms, ev_pool_[p.ev].first, ev_pool_[p.ev].second);
+    FamilyTime& f = profile_[p.launch->name];
+    f.name = p.launch->name;
+    ++f.launches;
+    f.ms += ms;
+    f.algo_bytes += p.launch->algo_bytes;
+    f.flops += p.launch->flops;
+  }
+  pending_.clear();
+  ev_used_ = 0;
+}
+
+std::vector<FamilyTime> CudaBackend::take_profile() {
+  drain_profile();
+  std::vector<FamilyTime> v;
+  for (auto& kv : profile_) v.push_back(kv.second);
+  profile_.clear();
+  return v;
+}
+
+}  // namespace ku::cu
+
+namespace ku {
+// The CUDA library creates only the CUDA backend: there is no CPU evaluator to fall back to.
+std::unique_ptr<Backend> make_backend(uint32_t kind) {
+  if (kind == 2) return std::make_unique<cu::CudaBackend>(0);
+  if (kind == 0 || kind == 1) {
+    set_err("ku_backend_new: libkurumi_cuda provides only KU_CUDA (2); kind " + std::to_string(kind) + " is not built into this library");
+    return nullptr;
+  }
+  set_err("ku_backend_new: unknown kind " + std::to_string(kind));
+  return nullptr;
+}
+}  // namespace ku

@@ -1,0 +1,24 @@
+// Hand-written sm_100a kernel templates (sources under kernels/) and the host code that
+// instantiates them: picks tiles, builds TMA tensor maps, fills in the launch.
+#pragma once
+#include "fuse.h"
+
+namespace ku::cu {
+
+// Tensor-core contraction (tcgen05 + TMEM, TMA-fed) with the generated epilogue. Returns false
+// when the operand layout / dtype is outside what the kernel takes (the caller then uses the SIMT
+// kernel). Operand slots in the returned launch are symbolic: -1 = A, -2 = B, -3 = C.
+bool build_gemm_tc(const KernelLoader& load, const GemmDesc& d, const Fused* epi, int sm_count, Launch* out, std::vector<int>* epi_leaf_args);
+
+// Single-pass softmax for lines that are strided in memory while the previous axis is contiguous
+// (a softmax consumed through a transpose view). Returns false when the pattern does not apply.
+bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args);
+
+// Fused causal / full attention with online softmax. Slots are symbolic: -1 q, -2 k, -3 v, -4 out.
+bool attention_supported(DType dt, const Shape& shape);
+bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, bool causal, float scale, int sm_count, Launch* out);
+
+// Every template instantiated once with representative parameters, for the no-GPU build check.
+std::vector<std::pair<std::string, std::string>> representative_kernel_sources();
+
+}  // namespace ku::cu
