@@ -208,13 +208,13 @@ def main():
         if world > 1:
             dist.barrier()
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         step().free()
     barrier()
     launches0 = gpu.stats()["launches"]
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
@@ -222,8 +222,18 @@ def main():
     e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
     launches = gpu.stats()["launches"] - launches0
+    # nvidia-smi needs ~100 ms per sample: when the timed region is shorter than that, keep the same
+    # load running (untimed) so the clock record still describes the kernel under load
+    t_sustain = time.perf_counter()
+    while rank == 0 and ms < 1500 and time.perf_counter() - t_sustain < 1.5:
+        for _ in range(20):
+            step().free()
+        gpu.sync()
+    clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "warm-up + timed steps" + (" + 1.5 s of the same steps, untimed" if ms < 1500 else "")
+    barrier()
     t = torch.tensor([ms], device=f"cuda:{local}")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

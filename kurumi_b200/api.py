@@ -90,7 +90,7 @@ class Tensor:
                      np.dtype(np.int64): I64, np.dtype(np.uint8): U8, np.dtype(np.bool_): BOOL,
                      np.dtype(np.float16): F16, np.dtype(np.int8): I8, np.dtype(np.int16): I16,
                      np.dtype(np.uint16): U16, np.dtype(np.uint32): U32, np.dtype(np.uint64): U64}[arr.dtype]
-        a = np.ascontiguousarray(arr)
+        a = np.ascontiguousarray(arr).reshape(np.shape(arr))   # ascontiguousarray promotes 0-d to 1-d
         shape, rank = _sz(a.shape)
         h = lib.lib.ku_tensor_new(C.c_uint32(dtype), a.ctypes.data_as(C.c_void_p), C.c_size_t(a.nbytes), shape,
                                   C.c_size_t(rank))
@@ -164,7 +164,7 @@ class Graph:
         return self._n("ku_input", s, C.c_size_t(r), C.c_uint32(dtype))
 
     def constant(self, arr: np.ndarray, dtype: int | None = None) -> int:
-        a = np.ascontiguousarray(arr)
+        a = np.ascontiguousarray(arr).reshape(np.shape(arr))
         if dtype is None:
             dtype = Tensor.from_numpy(self.lib, np.zeros(1, a.dtype)).dtype
         s, r = _sz(a.shape)

@@ -72,11 +72,13 @@ __device__ __forceinline__ float ku_d2f_odd(double d) {
   if (d == d && (double)f != d) f = __uint_as_float(__float_as_uint(f) | 1u);
   return f;
 }
-// float -> integer: truncate toward zero, saturate, NaN -> 0
-__device__ __forceinline__ i32 ku_f2i_i32(double d) { return d != d ? 0 : __double2int_rz(d); }
-__device__ __forceinline__ u32 ku_f2i_u32(double d) { return d != d ? 0u : __double2uint_rz(d); }
-__device__ __forceinline__ i64 ku_f2i_i64(double d) { return d != d ? 0ll : __double2ll_rz(d); }
-__device__ __forceinline__ u64 ku_f2i_u64(double d) { return d != d ? 0ull : __double2ull_rz(d); }
+// float -> integer: truncate toward zero, saturate, NaN -> 0. The range tests are explicit: a bare
+// float-to-int conversion of an out-of-range value is undefined to the optimiser, which may fold
+// int -> double -> int round trips into a move.
+__device__ __forceinline__ i32 ku_f2i_i32(double d) { if (!(d == d)) return 0; if (d <= -2147483648.0) return (i32)0x80000000u; if (d >= 2147483647.0) return 2147483647; return (i32)d; }
+__device__ __forceinline__ u32 ku_f2i_u32(double d) { if (!(d == d)) return 0u; if (d <= 0.0) return 0u; if (d >= 4294967295.0) return 0xffffffffu; return (u32)d; }
+__device__ __forceinline__ i64 ku_f2i_i64(double d) { if (!(d == d)) return 0ll; if (d <= -9223372036854775808.0) return (i64)0x8000000000000000ull; if (d >= 9223372036854775808.0) return 0x7fffffffffffffffll; return (i64)d; }
+__device__ __forceinline__ u64 ku_f2i_u64(double d) { if (!(d == d)) return 0ull; if (d <= 0.0) return 0ull; if (d >= 18446744073709551616.0) return 0xffffffffffffffffull; return (u64)d; }
 __device__ __forceinline__ i8 ku_f2i_i8(double d) { i32 v = ku_f2i_i32(d); return (i8)(v < -128 ? -128 : (v > 127 ? 127 : v)); }
 __device__ __forceinline__ u8 ku_f2i_u8(double d) { i32 v = ku_f2i_i32(d); return (u8)(v < 0 ? 0 : (v > 255 ? 255 : v)); }
 __device__ __forceinline__ i16 ku_f2i_i16(double d) { i32 v = ku_f2i_i32(d); return (i16)(v < -32768 ? -32768 : (v > 32767 ? 32767 : v)); }
@@ -314,8 +316,32 @@ struct Gen {
     if (!g.empty()) v = "((" + g + ") ? " + v + " : " + imm_literal(l.dtype, 0) + ")";
     return v;
   }
-  // statements computing every node; the root value is left in `v<root>`
-  std::string body(const std::vector<std::string>& leaf_vals, const std::string& ind) const {
+  // storage bits of a buffer leaf at the coordinates ("" when the leaf has no storage to read)
+  std::string leaf_raw(size_t li, const std::vector<std::string>& c) const {
+    const Leaf& l = f.leaves[li];
+    if (l.kind != LeafKind::Buffer || !is_lowf(l.dtype)) return "";  // wider types hold their own bits in registers
+    std::string v = "((const " + std::string(stype(l.dtype)) + "*)p" + std::to_string(ptr_arg[li]) + ")[" + offset(li, c) + "]";
+    std::string g = guard(li, c);
+    if (!g.empty()) v = "((" + g + ") ? " + v + " : (" + std::string(stype(l.dtype)) + ")0)";
+    return v;
+  }
+  // Is the root a bare load of a buffer leaf (pure movement)? Then the stored element is the loaded
+  // bit pattern itself, so NaN payloads of the narrow float formats survive a copy.
+  bool root_is_copy() const { return f.nodes[static_cast<size_t>(f.root)].op == OpKind::Input && f.leaves[static_cast<size_t>(f.nodes[static_cast<size_t>(f.root)].leaf)].kind == LeafKind::Buffer; }
+  // storage-typed expression to store for the root
+  std::string root_store(const std::vector<std::string>& leaf_raws) const {
+    const FNode& r = f.nodes[static_cast<size_t>(f.root)];
+    if (root_is_copy() && !leaf_raws[static_cast<size_t>(r.leaf)].empty()) return leaf_raws[static_cast<size_t>(r.leaf)];
+    if (r.op == OpKind::Bitcast && is_lowf(r.dtype)) {  // reinterpretation: store the source bits, do not round-trip them through a float
+      const FNode& src = f.nodes[static_cast<size_t>(r.in[0])];
+      const std::string raw = src.op == OpKind::Input ? leaf_raws[static_cast<size_t>(src.leaf)] : std::string();
+      return "(" + std::string(stype(r.dtype)) + ")(" + (raw.empty() ? to_bits(src.dtype, "v" + std::to_string(r.in[0])) : raw) + ")";
+    }
+    return enc(r.dtype, "v" + std::to_string(f.root));
+  }
+  // statements computing every node; the root value is left in `v<root>`. `leaf_raws` (optional)
+  // gives the storage bits of buffer leaves, used by a Bitcast that sits directly on a load.
+  std::string body(const std::vector<std::string>& leaf_vals, const std::string& ind, const std::vector<std::string>* leaf_raws = nullptr) const {
     std::vector<bool> need(f.nodes.size(), false);
     need[static_cast<size_t>(f.root)] = true;
     for (size_t i = f.nodes.size(); i-- > 0;)
@@ -326,7 +352,10 @@ struct Gen {
       const FNode& n = f.nodes[i];
       o << ind << "const " << ctype(n.dtype) << " v" << i << " = ";
       if (n.op == OpKind::Input) o << leaf_vals[static_cast<size_t>(n.leaf)];
-      else {
+      else if (n.op == OpKind::Bitcast && leaf_raws && f.nodes[static_cast<size_t>(n.in[0])].op == OpKind::Input &&
+               !(*leaf_raws)[static_cast<size_t>(f.nodes[static_cast<size_t>(n.in[0])].leaf)].empty()) {
+        o << from_bits(n.dtype, (*leaf_raws)[static_cast<size_t>(f.nodes[static_cast<size_t>(n.in[0])].leaf)]);
+      } else {
         auto nm = [&](int k) { return n.in[k] >= 0 ? "v" + std::to_string(n.in[k]) : std::string(); };
         o << op_expr(n, n.in[0] >= 0 ? f.nodes[static_cast<size_t>(n.in[0])].dtype : n.dtype, nm(0), nm(1), nm(2));
       }
@@ -427,11 +456,13 @@ Emitted emit_pointwise(const Fused& f, int sm_count) {
   o << "#pragma unroll\n    for (int l = 0; l < " << vec << "; ++l) {\n";
   std::vector<std::string> lc = coords;
   lc.back() = "(c" + std::to_string(nd - 1) + " + l)";
-  std::vector<std::string> lv(f.leaves.size());
-  for (size_t li = 0; li < f.leaves.size(); ++li)
+  std::vector<std::string> lv(f.leaves.size()), lr(f.leaves.size());
+  for (size_t li = 0; li < f.leaves.size(); ++li) {
     lv[li] = pre[li] ? dec(f.leaves[li].dtype, "b" + std::to_string(li) + "[l]") : g.leaf_value(li, lc);
-  o << g.body(lv, "      ");
-  o << "      r[l] = " << enc(od, "v" + std::to_string(f.root)) << ";\n    }\n";
+    lr[li] = !is_lowf(f.leaves[li].dtype) ? std::string() : pre[li] ? "b" + std::to_string(li) + "[l]" : g.leaf_raw(li, lc);
+  }
+  o << g.body(lv, "      ", &lr);
+  o << "      r[l] = " << g.root_store(lr) << ";\n    }\n";
   const size_t obytes = dtype_width(od) * static_cast<size_t>(vec);
   const std::string dst = "((" + std::string(stype(od)) + "*)out + e0)";
   if (obytes == 16) o << "    *(uint4*)" << dst << " = *(const uint4*)r;\n";
@@ -597,7 +628,33 @@ Emitted emit_softmax(const Fused& f, OpKind kind, size_t axis, float eps, int sm
   e.leaf_args = g.args;
   const int NT = 256;
   const int64_t per = (len + NT - 1) / NT;
-  if (inner == 1 && !dbl && len >= 64 && per <= 64) {
+  if (inner == 1 && !dbl && len >= 64 && per > 64) {
+    // a line too long for registers: one CTA per line, three passes over the (L2-resident) line with
+    // block-wide reductions in between
+    std::vector<std::string> lv(f.leaves.size());
+    for (size_t li = 0; li < f.leaves.size(); ++li) lv[li] = g.leaf_value(li, coords);
+    const std::string body = g.body(lv, "      ");
+    const std::string X = "v" + std::to_string(f.root);
+    o << "extern \"C\" __global__ void __launch_bounds__(256) ku_line_passes(" << g.params() << "void* __restrict__ out) {\n";
+    o << "  __shared__ float red[32];\n";
+    o << "  for (" << g.idx_t << " row = blockIdx.x; row < " << outer << "; row += gridDim.x) {\n";
+    o << decompose("row", sp.dims, 0, ax, g.idx_t, "c", "    ");
+    if (sm) {
+      o << "    float m = -KU_INF;\n    for (" << g.idx_t << " k = threadIdx.x; k < " << len << "; k += 256) {\n" << body << "      m = fmaxf(m, " << X << ");\n    }\n";
+      o << "    m = ku_block_reduce(m, KuMax(), red);\n";
+      o << "    float s = 0.0f;\n    for (" << g.idx_t << " k = threadIdx.x; k < " << len << "; k += 256) {\n" << body << "      s += expf(" << X << " - m);\n    }\n";
+      o << "    s = ku_block_reduce(s, KuAdd(), red);\n";
+    } else {
+      o << "    float s = 0.0f;\n    for (" << g.idx_t << " k = threadIdx.x; k < " << len << "; k += 256) {\n" << body << "      s += " << X << " * " << X << ";\n    }\n";
+      o << "    s = ku_block_reduce(s, KuAdd(), red);\n    s = sqrtf(s / " << len << ".0f + " << EPS << ");\n";
+    }
+    o << "    for (" << g.idx_t << " k = threadIdx.x; k < " << len << "; k += 256) {\n" << body;
+    o << "      ((" << stype(d) << "*)out)[row * " << len << " + k] = " << enc(d, sm ? "(expf(" + X + " - m) / s)" : "(" + X + " / s)") << ";\n    }\n  }\n}\n";
+    e.entry = "ku_line_passes";
+    e.block = 256;
+    e.grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(outer, static_cast<int64_t>(sm_count) * 8)));
+    e.family = sm ? "softmax_passes" : "rmsnorm_passes";
+  } else if (inner == 1 && !dbl && len >= 64 && per <= 64) {
     // one CTA per line; the line lives in registers between the passes: one read, one write
     int vec = 4;
     while (vec > 1 && (len % vec)) vec >>= 1;
@@ -670,9 +727,11 @@ Emitted emit_softmax(const Fused& f, OpKind kind, size_t axis, float eps, int sm
     const std::string X = "(" + T + ")v" + std::to_string(f.root);
     if (sm) {
       o << "    " << T << " m = " << NEG_INF << ";\n    for (" << g.idx_t << " k = 0; k < " << len << "; ++k) {\n" << body << "      m = " << MAXF << "(m, " << X << ");\n    }\n";
-      o << "    " << T << " s = 0;\n    for (" << g.idx_t << " k = 0; k < " << len << "; ++k) {\n" << body << "      s += " << EXP << "(" << X << " - m);\n    }\n";
+      // compensated (Kahan) running sum: one thread folds the whole line, so plain f32 accumulation
+      // would lose up to len * 2^-24 of relative accuracy
+      o << "    " << T << " s = 0, comp = 0;\n    for (" << g.idx_t << " k = 0; k < " << len << "; ++k) {\n" << body << "      const " << T << " y = " << EXP << "(" << X << " - m) - comp; const " << T << " t = s + y; comp = (t - s) - y; s = t;\n    }\n";
     } else {
-      o << "    " << T << " s = 0;\n    for (" << g.idx_t << " k = 0; k < " << len << "; ++k) {\n" << body << "      s += " << X << " * " << X << ";\n    }\n";
+      o << "    " << T << " s = 0, comp = 0;\n    for (" << g.idx_t << " k = 0; k < " << len << "; ++k) {\n" << body << "      const " << T << " y = " << X << " * " << X << " - comp; const " << T << " t = s + y; comp = (t - s) - y; s = t;\n    }\n";
       o << "    s = " << SQRT << "(s / (" << T << ")" << len << " + " << EPS << ");\n";
     }
     o << "    for (" << g.idx_t << " k = 0; k < " << len << "; ++k) {\n" << body;

@@ -300,7 +300,7 @@ void reduce_fold(const T* data, const Shape& shape, size_t axis, T init, F f, T*
   std::vector<size_t> base_strides;
   for (size_t i = 0; i < shape.size(); ++i)
     if (i != axis) { out_shape.push_back(shape[i]); base_strides.push_back(st[i]); }
-  const size_t out_len = std::max<size_t>(numel(out_shape), 1);
+  const size_t out_len = numel(out_shape);  // 1 for a rank-0 result, 0 when any kept axis is empty
   std::vector<size_t> coord(out_shape.size(), 0);
   for (size_t o = 0; o < out_len; ++o) {
     size_t base = 0;
@@ -374,7 +374,7 @@ Val movement_val(const Op& op, const Val& a) {
     default: throw Error("oracle: not a movement op");
   }
   Val o = make_val(a.dtype, out_shape, a.wide);
-  const size_t out_len = numel(out_shape) == 0 && out_shape.empty() ? 1 : numel(out_shape);
+  const size_t out_len = numel(out_shape);
   std::vector<size_t> coord(out_shape.size(), 0);
   std::vector<bool> flipped(in_shape.size(), false);
   if (op.kind == OpKind::Flip) for (size_t ax : op.perm) flipped[ax] = true;
@@ -412,7 +412,7 @@ void dot_num(const T* a, const Shape& as, const T* b, const Shape& bs, const Op&
   for (size_t i : b_free) out_shape.push_back(bs[i]);
   for (size_t i : op.lc) c_sizes.push_back(as[i]);
   const size_t nb = op.lb.size(), nlf = a_free.size();
-  const size_t out_len = std::max<size_t>(numel(out_shape), out_shape.empty() ? 1 : 0);
+  const size_t out_len = numel(out_shape);
   const size_t c_len = c_sizes.empty() ? 1 : numel(c_sizes);
   std::vector<size_t> oc(out_shape.size(), 0), cc(c_sizes.size(), 0);
   for (size_t o = 0; o < out_len; ++o) {
@@ -510,7 +510,7 @@ void softmax_lines(const T* data, const Shape& shape, size_t axis, T* out) {
   std::vector<size_t> base_strides;
   for (size_t i = 0; i < shape.size(); ++i)
     if (i != axis) { out_shape.push_back(shape[i]); base_strides.push_back(st[i]); }
-  const size_t out_len = std::max<size_t>(numel(out_shape), out_shape.empty() ? 1 : 0);
+  const size_t out_len = numel(out_shape);
   std::vector<size_t> coord(out_shape.size(), 0);
   for (size_t o = 0; o < out_len; ++o) {
     size_t base = 0;
@@ -548,7 +548,7 @@ void rmsnorm_lines(const T* data, const Shape& shape, size_t axis, T eps, T* out
   std::vector<size_t> base_strides;
   for (size_t i = 0; i < shape.size(); ++i)
     if (i != axis) { out_shape.push_back(shape[i]); base_strides.push_back(st[i]); }
-  const size_t out_len = std::max<size_t>(numel(out_shape), out_shape.empty() ? 1 : 0);
+  const size_t out_len = numel(out_shape);
   std::vector<size_t> coord(out_shape.size(), 0);
   for (size_t o = 0; o < out_len; ++o) {
     size_t base = 0;
@@ -632,7 +632,7 @@ Val rand_val(const Op& op, const Val& seed_v, bool wide_mode) {
     case DType::I64: seed = static_cast<uint64_t>(*reinterpret_cast<const int64_t*>(sv.bytes.data())); break;
     default: throw Error("oracle: rand_uniform seed must be an integer tensor");
   }
-  const size_t n = std::max<size_t>(numel(op.shape), op.shape.empty() ? 1 : 0);
+  const size_t n = numel(op.shape);
   Val o = make_val(DType::F32, op.shape, false);
   auto* z = reinterpret_cast<float*>(o.bytes.data());
   for (size_t i = 0; i < n; ++i) z[i] = uniform_f32(threefry2x32(seed, i));
