@@ -87,7 +87,14 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
     }
   }
   // issue the cached launches
-  for (const Launch& L : P.launches) {
+  for (Launch& L : P.launches) {
+    if (L.persistent_clusters < 0) {  // persistent kernel: one wave of co-resident clusters
+      const unsigned cl = L.cluster[0];
+      const int fit = rt_.max_active_clusters(L.kernel, cl, L.block[0], L.smem);
+      if (fit <= 0) throw Error::backend("kernel " + L.name + " cannot be launched with clusters of " + std::to_string(cl));
+      L.persistent_clusters = std::min<int>(fit, static_cast<int>(L.grid[0] / cl));
+      L.grid[0] = static_cast<unsigned>(L.persistent_clusters) * cl;
+    }
     std::vector<void*> vals(L.args.size());
     std::vector<CUtensorMap> maps(L.args.size());
     std::vector<void*> argv(L.args.size());
@@ -96,6 +103,10 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
       if (A.kind == Arg::SlotPtr) {
         vals[a] = static_cast<char*>(ptr[static_cast<size_t>(A.slot)]) + A.byte_offset;
         argv[a] = &vals[a];
+      } else if (A.kind == Arg::Status) {
+        vals[a] = rt_.status_word();
+        argv[a] = &vals[a];
+        uses_status_ = true;
       } else if (A.kind == Arg::Bytes) {
         argv[a] = const_cast<uint8_t*>(A.bytes.data());
       } else {
@@ -154,7 +165,7 @@ DevTensor* CudaBackend::upload(DType dt, const Shape& shape, const void* host, s
 void CudaBackend::download(const DevTensor& t, void* host) {
   rt_.make_current();
   if (t.bytes) cuda_check(cudaMemcpyAsync(host, t.ptr, t.bytes, cudaMemcpyDeviceToHost, rt_.stream()), "download");
-  rt_.sync();
+  if (uses_status_) rt_.check_status(); else rt_.sync();
   rt_.stats.d2h_bytes += t.bytes;
 }
 

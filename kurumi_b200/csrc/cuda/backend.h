@@ -52,6 +52,7 @@ class CudaBackend : public Backend {
   std::map<std::pair<uint64_t, std::vector<NodeId>>, std::unique_ptr<Compiled>> programs_;
   std::map<std::pair<uint64_t, NodeId>, void*> consts_;
   bool profiling_ = false;
+  bool uses_status_ = false;  // some launched kernel reports through the device status word
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev_pool_;
   struct Pending { size_t ev; const Launch* launch; };
   std::vector<Pending> pending_;

@@ -746,6 +746,71 @@ Emitted emit_softmax(const Fused& f, OpKind kind, size_t axis, float eps, int sm
   return e;
 }
 
+// ---- producer function for the hand-written line kernels -------------------------------------------------
+bool emit_line_source_fn(const Fused& f, size_t axis, std::string* src, std::vector<int>* leaf_args, int64_t* R, int64_t* C, bool* transposed, LineLeaf* big) {
+  Space sp = collapse(f, static_cast<int>(axis));
+  if (sp.dims.size() != 2 || sp.special != 1) return false;
+  *R = sp.dims[0];
+  *C = sp.dims[1];
+  Gen g(f, sp);
+  *leaf_args = g.args;
+  // the transposed pattern: the dominant buffers are contiguous along the line index and strided
+  // along the line, and nothing large is contiguous along the line
+  bool has_t = false, has_n = false;
+  for (size_t li = 0; li < f.leaves.size(); ++li) {
+    if (f.leaves[li].kind != LeafKind::Buffer) continue;
+    const int64_t s0 = sp.ls[li][0], s1 = sp.ls[li][1];
+    if ((s0 == 1 || s0 == -1) && s1 != 0 && s1 != 1 && s1 != -1) has_t = true;
+    else if (s0 != 0 && (s1 == 1 || s1 == -1)) has_n = true;
+    else if (s0 != 0 && s1 != 0) has_n = true;
+  }
+  *transposed = has_t && !has_n;
+  // the single dominant leaf a TMA pipeline can stream: plain f32, unit stride across lines, 16-byte aligned rows
+  int big_leaf = -1;
+  if (big) {
+    big->leaf = -1;
+    int count = 0;
+    for (size_t li = 0; li < f.leaves.size(); ++li) {
+      const Leaf& l = f.leaves[li];
+      if (l.kind != LeafKind::Buffer) continue;
+      const int64_t s0 = sp.ls[li][0], s1 = sp.ls[li][1];
+      if (s0 == 1 && s1 > 1) {
+        ++count;
+        if (l.dtype == DType::F32 && l.view.guards.empty() && l.view.base % 4 == 0 && s1 % 4 == 0 && l.view.base >= 0) { big_leaf = static_cast<int>(li); big->ld = s1; big->base = l.view.base; }
+      }
+    }
+    if (count != 1) big_leaf = -1;
+    big->leaf = big_leaf;
+    if (big_leaf >= 0) {
+      const FNode& r = f.nodes[static_cast<size_t>(f.root)];
+      big->identity = r.op == OpKind::Input && r.leaf == big_leaf;
+    }
+  }
+  std::ostringstream o;
+  std::string params, args;
+  for (size_t i = 0; i < g.args.size(); ++i) { params += ", const void* __restrict__ p" + std::to_string(i); args += ", p" + std::to_string(i); }
+  o << "#define KU_SRC_PARAMS " << params << "\n#define KU_SRC_ARGS " << args << "\n";
+  std::string lead;
+  for (size_t i = 0; i < g.args.size(); ++i) lead += "const void* __restrict__ p" + std::to_string(i) + ", ";
+  o << "#define KU_SRC_PARAMS_LEAD " << lead << "\n";
+  o << "typedef " << stype(f.dtype()) << " ku_out_t;\n#define KU_ENC(x) " << enc(f.dtype(), "(x)") << "\n";
+  o << "__device__ __forceinline__ float ku_src(" << g.idx_t << " i, " << g.idx_t << " j" << params << ") {\n";
+  std::vector<std::string> coords = {"i", "j"};
+  std::vector<std::string> lv(f.leaves.size());
+  for (size_t li = 0; li < f.leaves.size(); ++li) lv[li] = g.leaf_value(li, coords);
+  o << g.body(lv, "  ");
+  o << "  return (float)v" << f.root << ";\n}\n";
+  if (big_leaf >= 0) {  // same producer with the dominant leaf's value handed in (it was staged in shared memory)
+    o << "__device__ __forceinline__ float ku_src_t(float lval, " << g.idx_t << " i, " << g.idx_t << " j" << params << ") {\n";
+    std::vector<std::string> lv2 = lv;
+    lv2[static_cast<size_t>(big_leaf)] = "lval";
+    o << g.body(lv2, "  ");
+    o << "  return (float)v" << f.root << ";\n}\n";
+  }
+  *src = o.str();
+  return true;
+}
+
 // ---- GEMM epilogue + SIMT GEMM ----------------------------------------------------------------------
 // Generates `ku_epilogue(acc, b, m, n, pointers...)`: the pointwise chain that consumes the rounded
 // contraction result at output coordinate (b, m, n) and returns the stored element.

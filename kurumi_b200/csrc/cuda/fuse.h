@@ -81,7 +81,7 @@ struct TmapSpec {  // a tensor map over a slot, encoded once the slot's address 
 };
 
 struct Arg {
-  enum Kind : uint8_t { SlotPtr, Bytes, Tmap } kind = SlotPtr;
+  enum Kind : uint8_t { SlotPtr, Bytes, Tmap, Status } kind = SlotPtr;  // Status: the backend's device status word
   int slot = -1;
   int64_t byte_offset = 0;
   std::vector<uint8_t> bytes;
@@ -93,6 +93,8 @@ struct Launch {
   Kernel kernel;
   unsigned grid[3] = {1, 1, 1}, block[3] = {1, 1, 1}, cluster[3] = {1, 1, 1};
   unsigned smem = 0;
+  int persistent_clusters = 0;  // -1: cap grid[0] at the co-resident cluster count (x cluster size) on first launch; > 0: done
+  bool status_arg = false;      // append the backend's device status word as the last kernel parameter
   std::vector<Arg> args;
   double algo_bytes = 0, flops = 0;  // algorithmic traffic / work of this launch
 };
@@ -134,6 +136,14 @@ struct GemmDesc {
 // C[batch, m, n] = epilogue(round_to_dtype(sum_k A*B)); `epi` (may be null) is a Fused over shape
 // [batch, m, n] (collapsed to 3-D) containing one Acc leaf. SIMT kernel, any numeric dtype.
 Emitted emit_gemm_simt(const GemmDesc& g, const Fused* epi, int sm_count);
+
+// For the hand-written line kernels: when `f` collapses to [R lines, C positions] with the softmax axis
+// last, generates `float ku_src(i, j, pointers)` (the fused producer) plus the KU_SRC_* / KU_ENC glue
+// and reports whether the reads are transposed (contiguous across lines, strided along a line).
+// `big` (optional) receives the one dominant f32 leaf that a TMA pipeline can stream (leaf = -1 if
+// there is none); then `ku_src_t(lval, i, j, pointers)` is generated too, taking that leaf's value.
+struct LineLeaf { int leaf = -1; int64_t ld = 0, base = 0; bool identity = false; };
+bool emit_line_source_fn(const Fused& f, size_t axis, std::string* src, std::vector<int>* leaf_args, int64_t* R, int64_t* C, bool* transposed, LineLeaf* big = nullptr);
 
 // Shared pieces the hand-written kernel templates splice in (prelude + the per-element epilogue).
 std::string device_prelude();

@@ -51,12 +51,45 @@ Runtime::Runtime(int device) : device_(device) {
   entry("cuFuncGetAttribute", &cuFuncGetAttribute_);
   entry("cuTensorMapEncodeTiled", &cuTensorMapEncodeTiled_);
   entry("cuGetErrorString", &cuGetErrorString_);
+  entry("cuOccupancyMaxActiveClusters", &cuOccupancyMaxActiveClusters_);
   g_err_string = cuGetErrorString_;
+  cuda_check(cudaMalloc(&status_, 256), "cudaMalloc(status)");
+  cuda_check(cudaMemsetAsync(status_, 0, 256, stream_), "cudaMemset(status)");
+}
+
+void Runtime::check_status() {
+  int v = 0;
+  cuda_check(cudaMemcpyAsync(&v, status_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "status read");
+  sync();
+  if (v != 0) {
+    cudaMemsetAsync(status_, 0, sizeof(int), stream_);
+    throw Error::backend("a kernel gave up a bounded wait (status " + std::to_string(v) + "); its results are invalid");
+  }
+}
+
+int Runtime::max_active_clusters(const Kernel& k, unsigned cluster, unsigned block, unsigned smem) {
+  if (smem > 48 * 1024) drv_check(cuFuncSetAttribute_(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, static_cast<int>(smem)), "cuFuncSetAttribute(smem)");
+  if (cluster > 8) drv_check(cuFuncSetAttribute_(k.fn, CU_FUNC_ATTRIBUTE_NON_PORTABLE_CLUSTER_SIZE_ALLOWED, 1), "cuFuncSetAttribute(cluster)");
+  CUlaunchConfig cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDimX = cluster * 64; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+  cfg.blockDimX = block; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+  cfg.sharedMemBytes = smem;
+  cfg.hStream = stream_;
+  CUlaunchAttribute attr[1];
+  attr[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+  attr[0].value.clusterDim.x = cluster; attr[0].value.clusterDim.y = 1; attr[0].value.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  drv_check(cuOccupancyMaxActiveClusters_(&n, k.fn, &cfg), "cuOccupancyMaxActiveClusters");
+  return n;
 }
 
 Runtime::~Runtime() {
   cudaSetDevice(device_);
   if (stream_) cudaStreamSynchronize(stream_);
+  if (status_) cudaFree(status_);
   for (auto& kv : free_) cudaFree(kv.second);
   for (auto& kv : live_) cudaFree(kv.first);
   for (CUmodule m : modules_) cuModuleUnload_(m);
@@ -114,12 +147,15 @@ std::string Runtime::compile_to_cubin(const std::string& source, bool fmad, std:
     throw Error::backend("nvrtcCreateProgram failed");
   std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo", "--prec-div=true", "--prec-sqrt=true", "--ftz=false"};
   opts.push_back(fmad ? "--fmad=true" : "--fmad=false");
+  const bool verbose = std::getenv("KURUMI_CUDA_VERBOSE") != nullptr;
+  if (verbose) opts.push_back("--ptxas-options=-v");
   nvrtcResult r = nvrtcCompileProgram(prog, static_cast<int>(opts.size()), opts.data());
   size_t log_size = 0;
   nvrtcGetProgramLogSize(prog, &log_size);
   std::string log(log_size, '\0');
   if (log_size > 1) nvrtcGetProgramLog(prog, log.data());
   if (log_out) *log_out = log;
+  if (verbose && log_size > 1) fprintf(stderr, "%s\n", log.c_str());
   if (r != NVRTC_SUCCESS) {
     nvrtcDestroyProgram(&prog);
     throw Error::backend("NVRTC compile failed: " + log);

@@ -53,6 +53,12 @@ class Runtime {
   void launch(const Kernel& k, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3], unsigned smem,
               void** args);
 
+  // Largest number of clusters of this shape that can be resident at once (0 if it cannot launch).
+  int max_active_clusters(const Kernel& k, unsigned cluster, unsigned block, unsigned smem);
+  // A device word kernels set when a bounded wait gives up; check_status() throws and clears it.
+  int* status_word() const { return status_; }
+  void check_status();
+
   CUtensorMap tensor_map(const void* ptr, CUtensorMapDataType dt, unsigned rank, const uint64_t* dims,
                          const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz);
 
@@ -62,6 +68,7 @@ class Runtime {
   int device_;
   int sm_count_ = 0;
   cudaStream_t stream_ = nullptr;
+  int* status_ = nullptr;
   std::unordered_map<std::string, Kernel> kernels_;
   std::vector<CUmodule> modules_;
   std::multimap<size_t, void*> free_;
@@ -77,6 +84,7 @@ class Runtime {
                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
   CUresult (*cuGetErrorString_)(CUresult, const char**) = nullptr;
+  CUresult (*cuOccupancyMaxActiveClusters_)(int*, CUfunction, const CUlaunchConfig*) = nullptr;
   friend void drv_check(CUresult, const char*);
 };
 

@@ -272,6 +272,7 @@ Fused Scheduler::softmax(OpKind k, const Fused& f0, size_t axis, float eps) {
     if (k == OpKind::Softmax && build_softmax_transposed(*load_, f, axis, sm_, &L, &leaf_args)) {
       for (int li : leaf_args) { Arg a; a.kind = Arg::SlotPtr; a.slot = f.leaves[static_cast<size_t>(li)].slot; L.args.push_back(a); }
       Arg o; o.kind = Arg::SlotPtr; o.slot = slot; L.args.push_back(o);
+      if (L.status_arg) { Arg st; st.kind = Arg::Status; L.args.push_back(st); }
       L.algo_bytes = leaf_bytes(f) + static_cast<double>(prog_.slots[static_cast<size_t>(slot)].bytes);
       prog_.launches.push_back(std::move(L));
     } else {
