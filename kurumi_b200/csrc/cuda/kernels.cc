@@ -4,10 +4,6 @@
 
 namespace ku::cu {
 
-bool build_gemm_tc(const KernelLoader&, const GemmDesc&, const Fused*, int, Launch*, std::vector<int>*) { return false; }
-extern const std::string kSrc_softmax_transposed;
-extern const std::string kSrc_softmax_transposed_tma;
-
 namespace {
 std::string defines(std::initializer_list<std::pair<const char*, int64_t>> kv) {
   std::string s;
@@ -15,6 +11,77 @@ std::string defines(std::initializer_list<std::pair<const char*, int64_t>> kv) {
   return s;
 }
 }  // namespace
+
+extern const std::string kSrc_gemm_tc;
+
+static std::string lower(std::string s) { for (auto& c : s) c = static_cast<char>(std::tolower(c)); return s; }
+
+bool build_gemm_tc(const KernelLoader& load, const GemmDesc& d, const Fused* epi, int sm_count, Launch* out, std::vector<int>* epi_leaf_args) {
+  if (std::getenv("KURUMI_NO_TC")) return false;
+  const DType in = d.in_dtype;
+  const bool f8 = in == DType::F8E4M3;
+  if (!(d.dtype == DType::BF16 || d.dtype == DType::F16)) return false;
+  if (!(in == d.dtype || f8)) return false;
+  const int64_t es = f8 ? 1 : 2, al = 16 / es;  // element size, elements per 16 bytes
+  if (d.m < 1 || d.n < 1 || d.k < 1 || d.m >= (int64_t(1) << 31) || d.n >= (int64_t(1) << 31) || d.k >= (int64_t(1) << 31)) return false;
+  // each operand must be K-major or MN-major with 16-byte aligned rows, base and batch stride
+  auto major = [&](int64_t row_stride, int64_t k_stride, int64_t rows, int64_t base, int64_t bs, int* mn) {
+    if (base % al || base < 0 || (d.batch > 1 && (bs % al || bs <= 0))) return false;
+    if (k_stride == 1 && (rows == 1 || (row_stride % al == 0 && row_stride >= d.k))) { *mn = 0; return true; }
+    if (row_stride == 1 && (d.k == 1 || (k_stride % al == 0 && k_stride >= rows))) { *mn = 1; return true; }
+    return false;
+  };
+  int a_mn = 0, b_mn = 0;
+  if (!major(d.a_ms, d.a_ks, d.m, d.a_base, d.a_bs, &a_mn) || !major(d.b_ns, d.b_ks, d.n, d.b_base, d.b_bs, &b_mn)) return false;
+  const int64_t bm = 128, bn = d.n > 128 ? 256 : d.n > 64 ? 128 : 64, bkb = 128, bk = bkb / es;
+  const int64_t stage = (bm + bn) * bkb;
+  const int64_t stages = std::min<int64_t>(8, (200 * 1024) / stage);
+  const int64_t tiles_m = (d.m + bm - 1) / bm, tiles_n = (d.n + bn - 1) / bn;
+  if (d.batch * tiles_m * tiles_n >= (int64_t(1) << 31)) return false;
+  // instruction descriptor: f32 accumulate, operand formats, major-ness, N >> 3, M >> 4
+  const uint32_t fmt = f8 ? 0u : (d.dtype == DType::BF16 ? 1u : 0u);
+  const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
+                         (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(bm >> 4) << 24);
+  std::string src = device_prelude() + emit_epilogue_fn(epi, d.dtype, epi_leaf_args) +
+                    defines({{"M", d.m}, {"N", d.n}, {"K", d.k}, {"BATCH", d.batch}, {"BM", bm}, {"BN", bn}, {"BKB", bkb}, {"ESIZE", es}, {"STAGES", stages},
+                             {"A_MN", a_mn}, {"B_MN", b_mn}, {"IDESC", static_cast<int64_t>(idesc)}, {"TILES_M", tiles_m}, {"TILES_N", tiles_n}}) +
+                    "#define KU_ROUND(x) ku_rnd_" + lower(dtype_name(d.dtype)) + "(x)\n" + kSrc_gemm_tc;
+  out->name = f8 ? "gemm_tc_f8" : "gemm_tc";
+  out->kernel = load(src, "ku_gemm_tc", true);
+  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(d.batch * tiles_m * tiles_n, sm_count));
+  out->block[0] = 192;
+  out->smem = static_cast<unsigned>(std::max<int64_t>(stages * stage + 1024, 120 * 1024));  // > half an SM: one CTA per SM owns all of tensor memory
+  auto tmap = [&](int slot, int mn, int64_t rows, int64_t row_stride, int64_t k_stride, int64_t base, int64_t bs, int64_t tile_rows) {
+    Arg a;
+    a.kind = Arg::Tmap;
+    a.tm.slot = slot;
+    a.tm.byte_offset = base * es;
+    a.tm.dt = f8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : (d.dtype == DType::BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    a.tm.rank = 3;
+    a.tm.swz = CU_TENSOR_MAP_SWIZZLE_128B;
+    const int64_t batch_stride = d.batch > 1 ? bs : std::max<int64_t>(al, ((mn ? d.k * std::max<int64_t>(k_stride, 1) : rows * std::max<int64_t>(row_stride, 1)) + al - 1) / al * al);
+    if (!mn) {  // K-major: dims (K, rows, batch), box (BK, tile rows, 1)
+      a.tm.dims[0] = static_cast<uint64_t>(d.k); a.tm.dims[1] = static_cast<uint64_t>(rows); a.tm.dims[2] = static_cast<uint64_t>(d.batch);
+      a.tm.strides[0] = static_cast<uint64_t>((rows == 1 ? std::max<int64_t>(d.k, al) : row_stride) * es);
+      a.tm.box[0] = static_cast<uint32_t>(bk); a.tm.box[1] = static_cast<uint32_t>(tile_rows); a.tm.box[2] = 1;
+    } else {    // MN-major: dims (rows, K, batch), box (128 bytes of rows, BK, 1)
+      a.tm.dims[0] = static_cast<uint64_t>(rows); a.tm.dims[1] = static_cast<uint64_t>(d.k); a.tm.dims[2] = static_cast<uint64_t>(d.batch);
+      a.tm.strides[0] = static_cast<uint64_t>((d.k == 1 ? std::max<int64_t>(rows, al) : k_stride) * es);
+      a.tm.box[0] = static_cast<uint32_t>(128 / es); a.tm.box[1] = static_cast<uint32_t>(bk); a.tm.box[2] = 1;
+    }
+    a.tm.strides[0] = (a.tm.strides[0] + 15) / 16 * 16;
+    a.tm.strides[1] = static_cast<uint64_t>(batch_stride * es);
+    return a;
+  };
+  out->args.push_back(tmap(-1, a_mn, d.m, d.a_ms, d.a_ks, d.a_base, d.a_bs, bm));
+  out->args.push_back(tmap(-2, b_mn, d.n, d.b_ns, d.b_ks, d.b_base, d.b_bs, bn));
+  Arg c; c.kind = Arg::SlotPtr; c.slot = -3; out->args.push_back(c);
+  Arg st; st.kind = Arg::Status; out->args.push_back(st);
+  return true;
+}
+extern const std::string kSrc_softmax_transposed;
+extern const std::string kSrc_softmax_transposed_tma;
+
 
 bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args) {
   if (f.dtype() == DType::F64 || !is_float(f.dtype())) return false;
@@ -33,7 +100,9 @@ bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t a
     int64_t nbuf = std::min<int64_t>(3, (200 * 1024) / (cj * 128));
     if (const char* e = std::getenv("KURUMI_SMT_NBUF")) nbuf = std::atoi(e);
     if (nbuf >= 2 && R < (int64_t(1) << 30) && C < (int64_t(1) << 30)) {
-      const int64_t nt = 512, slabs = (R + 31) / 32;
+      int64_t nt = 512;
+      if (const char* e = std::getenv("KURUMI_SMT_NT")) nt = std::atoi(e);
+      const int64_t slabs = (R + 31) / 32;
       std::string src = device_prelude() + src_fn +
                         defines({{"R", R}, {"C", C}, {"CL", cl}, {"CJ", cj}, {"BOXJ", boxj}, {"NBUF", nbuf}, {"NT", nt}, {"NSLABS", slabs}, {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
                         kSrc_softmax_transposed_tma;

@@ -1,0 +1,219 @@
+// Tensor-core contraction for sm_100a: C[b, m, n] = epilogue(round(sum_k A[b, m, k] * B[b, k, n])).
+//
+// tcgen05.mma (cta_group::1, M = 128, N = BN, K = 32 bytes per instruction) accumulates in f32 in
+// tensor memory; operands are staged in a ring of shared-memory tiles by cp.async.bulk.tensor (TMA,
+// SWIZZLE_128B, no multicast) completing on mbarriers. One CTA per SM, persistent over the output
+// tiles, warp-specialised:
+//   warp 0      one thread issues the TMA loads
+//   warp 1      allocates tensor memory; one thread issues the MMAs and commits them to mbarriers
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes its id
+//               selects), round it to the contraction's dtype, run the fused pointwise chain that
+//               the graph put behind the contraction, store
+// Tensor memory holds two accumulators (2 x BN of the 512 columns), so the epilogue of tile i overlaps
+// the MMAs of tile i + 1. Tiles are walked in groups of 16 row-blocks so that CTAs running together
+// share operand panels in L2.
+//
+// Either operand may be K-major (rows of 128 contiguous bytes along K) or MN-major (128 contiguous
+// bytes along M / N); the shared-memory descriptors and the instruction descriptor say which.
+// Accumulation is f32 and the result is rounded once to the operand dtype before the epilogue,
+// which is what the interpreter computes (kurumi_core/src/interp/contract.rs:58-64).
+//
+// Every mbarrier wait is bounded; a role that gives up raises *status, stops waiting and runs to
+// the end so that tensor memory is still released.
+//
+// Spliced in by the host: M, N, K, BATCH, BM (=128), BN, BKB (=128 bytes of K per stage), ESIZE,
+// STAGES, A_MN, B_MN (operand major-ness), IDESC, TILES_M, TILES_N, KU_ROUND(x) and
+//   ku_out_t ku_epilogue(float acc, i64 b, i64 m, i64 n KU_EPI_PARAMS).
+#define BK (BKB / ESIZE)                 // K elements per stage
+#define A_STAGE_BYTES (BM * BKB)
+#define B_STAGE_BYTES (BN * BKB)
+#define STAGE_BYTES (A_STAGE_BYTES + B_STAGE_BYTES)
+#define KBLOCKS ((K + BK - 1) / BK)
+#define SPIN_LIMIT (1u << 27)
+
+struct alignas(64) KuTmap { unsigned long long opaque[16]; };
+
+__device__ __forceinline__ unsigned ku_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ku_mbar_init(unsigned a, unsigned n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(n)); }
+__device__ __forceinline__ void ku_mbar_expect(unsigned a, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ku_mbar_arrive(unsigned a) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory"); }
+__device__ __forceinline__ bool ku_mbar_try(unsigned a, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded wait: returns false (and raises the status word once) when the barrier never flips
+__device__ __forceinline__ bool ku_wait(unsigned a, unsigned parity, bool& failed, int* status) {
+  if (failed) return false;
+  unsigned spins = 0;
+  while (!ku_mbar_try(a, parity)) {
+    if (++spins > SPIN_LIMIT) { failed = true; atomicExch(status, 2); return false; }
+  }
+  return true;
+}
+__device__ __forceinline__ void ku_tma_3d(unsigned dst, const KuTmap* map, int x, int y, int z, unsigned mbar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(mbar) : "memory");
+}
+// shared-memory matrix descriptor, SWIZZLE_128B, version 1; offsets in bytes
+__device__ __forceinline__ unsigned long long ku_smem_desc(unsigned addr, unsigned lbo, unsigned sbo) {
+  return (unsigned long long)((addr & 0x3FFFFu) >> 4) | ((unsigned long long)(lbo >> 4) << 16) | ((unsigned long long)(sbo >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void ku_mma(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+#if ESIZE == 1
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#else
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#endif
+}
+__device__ __forceinline__ void ku_mma_commit(unsigned mbar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void ku_tmem_ld32(unsigned taddr, float* v) {
+  unsigned* r = (unsigned*)v;
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+      "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+        "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+        "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// tile index -> (batch, row block, column block): groups of 16 row blocks, column-major inside a group
+__device__ __forceinline__ void ku_tile_coords(int t, int& b, int& mb, int& nb) {
+  const int per_batch = TILES_M * TILES_N;
+  b = t / per_batch;
+  const int r = t - b * per_batch;
+  const int group = r / (16 * TILES_N), in_group = r - group * 16 * TILES_N;
+  const int rows = (TILES_M - group * 16) < 16 ? (TILES_M - group * 16) : 16;
+  mb = group * 16 + in_group % rows;
+  nb = in_group / rows;
+}
+
+extern "C" __global__ void __launch_bounds__(192, 1)
+ku_gemm_tc(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTmap tmap_b, void* __restrict__ Cp, int* __restrict__ status KU_EPI_PARAMS) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], tmem_full[2], tmem_empty[2];
+  __shared__ unsigned tmem_base_slot;
+  unsigned char* smem = smem_raw + ((1024u - (ku_smem(smem_raw) & 1023u)) & 1023u);  // swizzle atoms need 1024-byte alignment
+  const unsigned smem_s = ku_smem(smem);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = BATCH * TILES_M * TILES_N;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { ku_mbar_init(ku_smem(&full_bar[s]), 1); ku_mbar_init(ku_smem(&empty_bar[s]), 1); }
+    for (int a = 0; a < 2; ++a) { ku_mbar_init(ku_smem(&tmem_full[a]), 1); ku_mbar_init(ku_smem(&tmem_empty[a]), 128); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // 512 columns: two BN-wide f32 accumulators
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ku_smem(&tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = tmem_base_slot;
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer ----
+      int it = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        int b, mb, nb;
+        ku_tile_coords(t, b, mb, nb);
+        for (int kb = 0; kb < KBLOCKS; ++kb, ++it) {
+          const int s = it % STAGES;
+          const unsigned ph = (it / STAGES) & 1;
+          ku_wait(ku_smem(&empty_bar[s]), ph ^ 1, failed, status);  // first pass over the ring: passes at once
+          const unsigned fb = ku_smem(&full_bar[s]);
+          ku_mbar_expect(fb, STAGE_BYTES);
+          const unsigned sa = smem_s + s * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+#if A_MN
+          for (int c = 0; c < BM * ESIZE / 128; ++c) ku_tma_3d(sa + c * BK * 128, &tmap_a, mb * BM + c * (128 / ESIZE), kb * BK, b, fb);
+#else
+          ku_tma_3d(sa, &tmap_a, kb * BK, mb * BM, b, fb);
+#endif
+#if B_MN
+          for (int c = 0; c < BN * ESIZE / 128; ++c) ku_tma_3d(sb + c * BK * 128, &tmap_b, nb * BN + c * (128 / ESIZE), kb * BK, b, fb);
+#else
+          ku_tma_3d(sb, &tmap_b, kb * BK, nb * BN, b, fb);
+#endif
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // ---- MMA issuer ----
+      int it = 0, local = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+        const int acc = local & 1;
+        ku_wait(ku_smem(&tmem_empty[acc]), ((local >> 1) & 1) ^ 1, failed, status);  // the epilogue has drained this accumulator
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < KBLOCKS; ++kb, ++it) {
+          const int s = it % STAGES;
+          ku_wait(ku_smem(&full_bar[s]), (it / STAGES) & 1, failed, status);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const unsigned sa = smem_s + s * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BKB / 32; ++k) {  // 32 bytes of K per instruction
+#if A_MN
+            const unsigned long long ad = ku_smem_desc(sa + k * (32 / ESIZE) * 128, BK * 128, 1024);
+#else
+            const unsigned long long ad = ku_smem_desc(sa + k * 32, 16, 1024);
+#endif
+#if B_MN
+            const unsigned long long bd = ku_smem_desc(sb + k * (32 / ESIZE) * 128, BK * 128, 1024);
+#else
+            const unsigned long long bd = ku_smem_desc(sb + k * 32, 16, 1024);
+#endif
+            ku_mma(d_tmem, ad, bd, IDESC, (kb | k) != 0);
+          }
+          ku_mma_commit(ku_smem(&empty_bar[s]));  // the stage is free once these MMAs have read it
+        }
+        ku_mma_commit(ku_smem(&tmem_full[acc]));  // the accumulator is complete once all MMAs of the tile retire
+      }
+    }
+  } else {  // ---- epilogue warps ----
+    const int q = warp & 3;  // the TMEM lane quarter this warp may read
+    int local = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+      int b, mb, nb;
+      ku_tile_coords(t, b, mb, nb);
+      const int acc = local & 1;
+      ku_wait(ku_smem(&tmem_full[acc]), (local >> 1) & 1, failed, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const i64 m = (i64)mb * BM + q * 32 + lane;
+      const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + acc * BN;
+      ku_out_t* crow = (ku_out_t*)Cp + ((i64)b * M + m) * N;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float v[32];
+        ku_tmem_ld32(taddr + c * 32, v);
+        const i64 n0 = (i64)nb * BN + c * 32;
+        if (m < M && n0 < N) {
+          if ((N % (16 / (int)sizeof(ku_out_t))) == 0 && n0 + 32 <= N) {
+            __align__(16) ku_out_t o[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = ku_epilogue(KU_ROUND(v[j]), (i64)b, m, n0 + j KU_EPI_ARGS);
+#pragma unroll
+            for (int w = 0; w < (int)(32 * sizeof(ku_out_t) / 16); ++w) ((uint4*)(crow + n0))[w] = ((const uint4*)o)[w];
+          } else {
+            for (int j = 0; j < 32 && n0 + j < N; ++j) crow[n0 + j] = ku_epilogue(KU_ROUND(v[j]), (i64)b, m, n0 + j KU_EPI_ARGS);
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      ku_mbar_arrive(ku_smem(&tmem_empty[acc]));
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+}

@@ -31,8 +31,15 @@ __device__ __forceinline__ float ku_ld_peer(const float* p, unsigned rank) {
   unsigned a = (unsigned)__cvta_generic_to_shared(p), ra;
   float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
   return v;
+}
+// per-line partials travel between the CTAs of a cluster as asynchronous remote stores that complete
+// on the receiver's mbarrier: no cluster-wide barrier, and no release fence that would have to wait
+// for the drain's global stores
+__device__ __forceinline__ unsigned ku_mapa(unsigned a, unsigned rank) { unsigned ra; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank)); return ra; }
+__device__ __forceinline__ void ku_st_async(unsigned remote_addr, float v, unsigned remote_mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(remote_addr), "r"(__float_as_uint(v)), "r"(remote_mbar) : "memory");
 }
 __device__ __forceinline__ unsigned ku_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ku_mbar_init(unsigned a, unsigned n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(n)); }
@@ -56,7 +63,9 @@ ku_softmax_transposed_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEA
   extern __shared__ __align__(1024) unsigned char tiles_raw[];  // NBUF tiles of [CJ][32] f32, 128-byte swizzled rows
   __shared__ __align__(8) unsigned long long full[NBUF];
   __shared__ float part[NW][32];
-  __shared__ float cta_max[2][32], cta_sum[2][32], line_max[32], line_c[32];
+  __shared__ __align__(8) unsigned long long bar_max[2], bar_sum[2];
+  __shared__ float cta_val[32], line_c[32];
+  __shared__ float gather_max[2][CL][32], gather_sum[2][CL][32];   // [slab parity][sender rank][line]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned rank = ku_cluster_rank();
   const int cid = blockIdx.x / CL, nclusters = gridDim.x / CL;
@@ -67,9 +76,10 @@ ku_softmax_transposed_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEA
 
   if (threadIdx.x == 0) {
     for (int b = 0; b < NBUF; ++b) ku_mbar_init(ku_smem(&full[b]), 1);
+    for (int b = 0; b < 2; ++b) { ku_mbar_init(ku_smem(&bar_max[b]), 1); ku_mbar_init(ku_smem(&bar_sum[b]), 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
+  ku_cluster_sync();   // every CTA's barriers exist before any peer sends to them
   auto issue = [&](int slab, int b) {  // one thread: stream this CTA's share of a slab into tile b
     const unsigned mb = ku_smem(&full[b]);
     ku_mbar_expect(mb, TILE_BYTES);
@@ -108,36 +118,50 @@ ku_softmax_transposed_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEA
 #endif
       m = fmaxf(m, v);
     }
+    bool failed = false;
+    const unsigned xparity = (n >> 1) & 1;   // each exchange barrier is used every second slab
     part[warp][lane] = m;
     __syncthreads();
     if (warp == 0) {
       float r = part[0][lane];
       for (int w = 1; w < NW; ++w) r = fmaxf(r, part[w][lane]);
-      cta_max[pp][lane] = r;
-    }
-    ku_cluster_sync();
-    if (warp == 0) {
-      float r = ku_ld_peer(&cta_max[pp][lane], 0);
-      for (unsigned c = 1; c < CL; ++c) r = fmaxf(r, ku_ld_peer(&cta_max[pp][lane], c));
-      line_max[lane] = r;
+      cta_val[lane] = r;
+      if (lane == 0) ku_mbar_expect(ku_smem(&bar_max[pp]), CL * 128);
     }
     __syncthreads();
+    if (warp < CL)   // warp w delivers this CTA's 32 partial maxima to CTA w
+      ku_st_async(ku_mapa(ku_smem(&gather_max[pp][rank][lane]), warp), cta_val[lane], ku_mapa(ku_smem(&bar_max[pp]), warp));
+    {
+      unsigned sp = 0;
+      while (!failed && !ku_mbar_try(ku_smem(&bar_max[pp]), xparity)) if (++sp > SPIN_LIMIT) { atomicExch(status, 3); failed = true; }
+    }
+    float mx = gather_max[pp][0][lane];
+#pragma unroll
+    for (int c = 1; c < CL; ++c) mx = fmaxf(mx, gather_max[pp][c][lane]);
 
-    const float m2 = line_max[lane] * KU_LOG2E;
+    const float m2 = mx * KU_LOG2E;
     float s = 0.0f;
 #pragma unroll 8
     for (int jj = warp; jj < CJ; jj += NW) s += ku_ex2(__fmaf_rn(*(const float*)(tile + ku_tile_off(jj, lane)), KU_LOG2E, -m2));
+    __syncthreads();   // cta_val and part are free again
     part[warp][lane] = s;
     __syncthreads();
     if (warp == 0) {
       float r = part[0][lane];
       for (int w = 1; w < NW; ++w) r += part[w][lane];
-      cta_sum[pp][lane] = r;
+      cta_val[lane] = r;
+      if (lane == 0) ku_mbar_expect(ku_smem(&bar_sum[pp]), CL * 128);
     }
-    ku_cluster_sync();
+    __syncthreads();
+    if (warp < CL) ku_st_async(ku_mapa(ku_smem(&gather_sum[pp][rank][lane]), warp), cta_val[lane], ku_mapa(ku_smem(&bar_sum[pp]), warp));
+    {
+      unsigned sp = 0;
+      while (!failed && !ku_mbar_try(ku_smem(&bar_sum[pp]), xparity)) if (++sp > SPIN_LIMIT) { atomicExch(status, 4); failed = true; }
+    }
     if (warp == 0) {
-      float r = ku_ld_peer(&cta_sum[pp][lane], 0);
-      for (unsigned c = 1; c < CL; ++c) r += ku_ld_peer(&cta_sum[pp][lane], c);
+      float r = gather_sum[pp][0][lane];
+#pragma unroll
+      for (int c = 1; c < CL; ++c) r += gather_sum[pp][c][lane];
       line_c[lane] = m2 + log2f(r);  // exp(x - max) / sum == exp2(x * log2e - (max * log2e + log2 sum))
     }
     __syncthreads();
