@@ -73,6 +73,13 @@ KuNode ku_cuda_amp_to(KuGraph *g, KuNode root, uint32_t dtype);
 KuNode ku_sdpa_fused(KuGraph *g, KuNode q, KuNode k, KuNode v, uint32_t causal);
 KuNode ku_sdpa_decomposed(KuGraph *g, KuNode q, KuNode k, KuNode v, uint32_t causal);
 
+/* Softmax over strided lines on raw device pointers: out[i * len + j] = softmax over j of
+ * (in[j * ld + i] + bias[j]) for i < lines, j < len, f32; bias may be NULL. It is the kernel the
+ * graph path runs for a softmax consumed through a transpose view (Op::Softmax, kurumi_core/src/
+ * graph/op.rs:48-51, oracle kurumi_core/src/interp/nn.rs:35-69), callable without recording a
+ * graph. Queued on the backend's stream; scratch comes from the backend's device pool. 0 ok, -1 error. */
+int32_t ku_cuda_softmax_lines_f32(const KuBackend *b, const float *in, const float *bias, float *out, size_t lines, size_t len, size_t ld);
+
 /* Compile every kernel the evaluation of ids[0..n] needs to an sm_100a cubin, without a GPU.
  * Writes the kernel family of each launch, one per line, into out (no NUL); returns the full
  * length, or (size_t)-1 on error. */

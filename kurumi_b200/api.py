@@ -452,6 +452,15 @@ class CudaBackend(Backend):
             raise Error(self.lib.last_error())
         return [DevTensor(self, out[i]) for i in range(len(nodes))]
 
+    def softmax_lines(self, x: DevTensor, bias, out: DevTensor, lines: int, length: int, ld: int, entry: str = "ku_cuda_softmax_lines_f32"):
+        """out[i, j] = softmax_j(x[j * ld + i] + bias[j]) on device buffers (ku_cuda_softmax_lines_f32)."""
+        fn = getattr(self.lib.lib, entry)
+        fn.restype = C.c_int32
+        args = [C.c_void_p(x.ptr), C.c_void_p(bias.ptr if bias is not None else None), C.c_void_p(out.ptr), C.c_size_t(lines), C.c_size_t(length), C.c_size_t(ld)]
+        rc = fn(self.h, *args) if entry == "ku_cuda_softmax_lines_f32" else fn(*args, C.c_void_p(self.stream))
+        if rc != 0:
+            raise Error(self.lib.last_error())
+
     def sync(self):
         if self.lib.lib.ku_cuda_sync(self.h) != 0:
             raise Error(self.lib.last_error())

@@ -126,7 +126,12 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
       ev = ev_used_++;
       cuda_check(cudaEventRecord(ev_pool_[ev].first, rt_.stream()), "cudaEventRecord");
     }
-    rt_.launch(L.kernel, L.grid, L.block, L.cluster, L.smem, argv.data());
+    if (L.host_launch) {
+      L.host_launch(vals, rt_.stream());
+      ++rt_.stats.launches;
+    } else {
+      rt_.launch(L.kernel, L.grid, L.block, L.cluster, L.smem, argv.data());
+    }
     if (profiling_) {
       cuda_check(cudaEventRecord(ev_pool_[ev].second, rt_.stream()), "cudaEventRecord");
       pending_.push_back({ev, &L});

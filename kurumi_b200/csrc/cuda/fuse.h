@@ -95,6 +95,9 @@ struct Launch {
   unsigned smem = 0;
   int persistent_clusters = 0;  // -1: cap grid[0] at the co-resident cluster count (x cluster size) on first launch; > 0: done
   bool status_arg = false;      // append the backend's device status word as the last kernel parameter
+  // When set, the step is a precompiled (nvcc-built) kernel sequence: the backend resolves the SlotPtr
+  // arguments and calls this instead of launching `kernel`.
+  std::function<void(const std::vector<void*>& ptrs, cudaStream_t stream)> host_launch;
   std::vector<Arg> args;
   double algo_bytes = 0, flops = 0;  // algorithmic traffic / work of this launch
 };

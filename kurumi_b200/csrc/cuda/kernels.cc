@@ -1,5 +1,6 @@
 #include "kernels.h"
 
+#include <cstdio>
 #include <cstdlib>
 
 namespace ku::cu {
@@ -83,6 +84,54 @@ extern const std::string kSrc_softmax_transposed;
 extern const std::string kSrc_softmax_transposed_tma;
 
 
+size_t softmax_two_pass_scratch_bytes(size_t lines, size_t len);
+void softmax_two_pass_launch(const float* in, const float* bias, float* out, size_t lines, size_t len, size_t ld, void* scratch, cudaStream_t stream);
+
+bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* scratch_bytes) {
+  if (std::getenv("KURUMI_SMT_NO_TWO_PASS")) return false;
+  if (f.dtype() != DType::F32 || f.shape.size() != 2 || axis != 1) return false;
+  const int64_t lines = static_cast<int64_t>(f.shape[0]), len = static_cast<int64_t>(f.shape[1]);
+  // lines of 2048 positions and more go to the single-pass cluster kernel, which measured faster there
+  if (len >= 2048 && !std::getenv("KURUMI_SMT_TWO_PASS")) return false;
+  if (lines < 64 || len < 256 || lines >= (int64_t(1) << 31) || len >= (int64_t(1) << 31)) return false;
+  auto is_big = [&](const Leaf& l) {
+    return l.kind == LeafKind::Buffer && l.dtype == DType::F32 && l.view.guards.empty() && l.view.stride[0] == 1 && l.view.stride[1] >= lines && l.view.base >= 0;
+  };
+  auto is_bias = [&](const Leaf& l) {
+    return l.kind == LeafKind::Buffer && l.dtype == DType::F32 && l.view.guards.empty() && l.view.stride[0] == 0 && l.view.stride[1] == 1 && l.view.base >= 0;
+  };
+  const FNode& r = f.nodes[static_cast<size_t>(f.root)];
+  const Leaf *big = nullptr, *bias = nullptr;
+  if (r.op == OpKind::Input) {
+    big = &f.leaves[static_cast<size_t>(r.leaf)];
+  } else if (r.op == OpKind::Add && r.dtype == DType::F32) {
+    const FNode &a = f.nodes[static_cast<size_t>(r.in[0])], &b = f.nodes[static_cast<size_t>(r.in[1])];
+    if (a.op != OpKind::Input || b.op != OpKind::Input) return false;
+    const Leaf &la = f.leaves[static_cast<size_t>(a.leaf)], &lb = f.leaves[static_cast<size_t>(b.leaf)];
+    if (is_big(la) && is_bias(lb)) { big = &la; bias = &lb; }
+    else if (is_big(lb) && is_bias(la)) { big = &lb; bias = &la; }
+    else return false;
+  } else {
+    return false;
+  }
+  if (!is_big(*big)) return false;
+  const size_t ld = static_cast<size_t>(big->view.stride[1]);
+  const bool has_bias = bias != nullptr;
+  *scratch_bytes = softmax_two_pass_scratch_bytes(static_cast<size_t>(lines), static_cast<size_t>(len));
+  out->name = "softmax_two_pass";
+  Arg in; in.kind = Arg::SlotPtr; in.slot = big->slot; in.byte_offset = big->view.base * 4; out->args.push_back(in);
+  Arg bi = in;
+  if (has_bias) { bi.slot = bias->slot; bi.byte_offset = bias->view.base * 4; }
+  out->args.push_back(bi);
+  Arg o; o.kind = Arg::SlotPtr; o.slot = -3; out->args.push_back(o);
+  Arg sc; sc.kind = Arg::SlotPtr; sc.slot = -1; out->args.push_back(sc);
+  out->host_launch = [=](const std::vector<void*>& p, cudaStream_t stream) {
+    softmax_two_pass_launch(static_cast<const float*>(p[0]), has_bias ? static_cast<const float*>(p[1]) : nullptr, static_cast<float*>(p[2]), static_cast<size_t>(lines),
+                            static_cast<size_t>(len), ld, p[3], stream);
+  };
+  return true;
+}
+
 bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args) {
   if (f.dtype() == DType::F64 || !is_float(f.dtype())) return false;
   std::string src_fn;
@@ -97,11 +146,13 @@ bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t a
     int64_t cj = (C + cl - 1) / cl;
     cj = (cj + 31) / 32 * 32;
     const int64_t boxj = cj % 256 == 0 ? 256 : cj % 128 == 0 ? 128 : cj % 64 == 0 ? 64 : 32;
-    int64_t nbuf = std::min<int64_t>(3, (200 * 1024) / (cj * 128));
+    // one tile per CTA and as many CTAs per SM as shared memory holds: co-resident CTAs of different
+    // clusters overlap each other's exchange latency better than a deeper ring in one CTA does
+    int64_t nbuf = 1;
     if (const char* e = std::getenv("KURUMI_SMT_NBUF")) nbuf = std::atoi(e);
-    if (nbuf >= 2 && R < (int64_t(1) << 30) && C < (int64_t(1) << 30)) {
+    if (nbuf >= 1 && R < (int64_t(1) << 30) && C < (int64_t(1) << 30)) {
       int64_t nt = 512;
-      if (const char* e = std::getenv("KURUMI_SMT_NT")) nt = std::atoi(e);
+      if (const char* e = std::getenv("KURUMI_SMT_NT")) nt = std::max<int64_t>(32 * cl, std::atoi(e));  // one warp per cluster peer at least
       const int64_t slabs = (R + 31) / 32;
       std::string src = device_prelude() + src_fn +
                         defines({{"R", R}, {"C", C}, {"CL", cl}, {"CJ", cj}, {"BOXJ", boxj}, {"NBUF", nbuf}, {"NT", nt}, {"NSLABS", slabs}, {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
@@ -111,7 +162,7 @@ bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t a
       out->grid[0] = static_cast<unsigned>(slabs * cl);
       out->block[0] = static_cast<unsigned>(nt);
       out->cluster[0] = static_cast<unsigned>(cl);
-      out->smem = static_cast<unsigned>(nbuf * cj * 128 + 1024);  // + slack for the 1024-byte alignment of the tile ring
+      out->smem = static_cast<unsigned>(nbuf * cj * 128);  // the kernel's static shared memory is a multiple of 1024 bytes, so the ring starts aligned
       out->persistent_clusters = -1;                              // cap the grid at the co-resident cluster count on first launch
       Arg tm;
       tm.kind = Arg::Tmap;
@@ -151,8 +202,56 @@ bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t a
   (void)sm_count;
   return true;
 }
-bool attention_supported(DType, const Shape&) { return false; }
-bool build_attention(const KernelLoader&, DType, const Shape&, bool, float, int, Launch*) { return false; }
+extern const std::string kSrc_attention_tc;
+
+bool attention_supported(DType dt, const Shape& shape) {
+  if (std::getenv("KURUMI_NO_TC_ATTENTION")) return false;
+  if (!(dt == DType::BF16 || dt == DType::F16) || shape.size() < 2) return false;
+  const size_t r = shape.size(), dh = shape[r - 1], s = shape[r - 2];
+  size_t bh = 1;
+  for (size_t i = 0; i + 2 < r; ++i) bh *= shape[i];
+  return (dh == 64 || dh == 128) && s >= 1 && s < (size_t(1) << 24) && bh >= 1 && bh < 65536;
+}
+
+bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, bool causal, float scale, int sm_count, Launch* out) {
+  if (!attention_supported(dt, shape)) return false;
+  const size_t r = shape.size();
+  const int64_t dh = static_cast<int64_t>(shape[r - 1]), s = static_cast<int64_t>(shape[r - 2]);
+  int64_t bh = 1;
+  for (size_t i = 0; i + 2 < r; ++i) bh *= static_cast<int64_t>(shape[i]);
+  const uint32_t fmt = dt == DType::BF16 ? 1u : 0u;
+  const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(128 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+  const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(dh >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+  char lit[64];
+  std::snprintf(lit, sizeof(lit), "%.9gf", static_cast<double>(scale * 1.4426950408889634f));
+  std::string src = device_prelude() +
+                    defines({{"BH", bh}, {"S", s}, {"DH", dh}, {"CAUSAL", causal ? 1 : 0}, {"IDESC_S", static_cast<int64_t>(idesc_s)}, {"IDESC_O", static_cast<int64_t>(idesc_o)},
+                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}}) +
+                    "#define SCALE_LOG2E " + lit + "\n" + kSrc_attention_tc;
+  out->name = "attention_tc";
+  out->kernel = load(src, "ku_attention_tc", true);
+  out->grid[0] = static_cast<unsigned>((s + 127) / 128);
+  out->grid[1] = static_cast<unsigned>(bh);
+  out->block[0] = 192;
+  const int64_t tile = 128 * 128 * (dh / 64);
+  out->smem = static_cast<unsigned>(std::max<int64_t>(5 * tile + 128 * 128 * 2 + 1024, 120 * 1024));
+  for (int slot = -1; slot >= -3; --slot) {
+    Arg a;
+    a.kind = Arg::Tmap;
+    a.tm.slot = slot;
+    a.tm.dt = dt == DType::BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    a.tm.rank = 3;
+    a.tm.swz = CU_TENSOR_MAP_SWIZZLE_128B;
+    a.tm.dims[0] = static_cast<uint64_t>(dh); a.tm.dims[1] = static_cast<uint64_t>(s); a.tm.dims[2] = static_cast<uint64_t>(bh);
+    a.tm.strides[0] = static_cast<uint64_t>(dh * 2); a.tm.strides[1] = static_cast<uint64_t>(s * dh * 2);
+    a.tm.box[0] = 64; a.tm.box[1] = 128; a.tm.box[2] = 1;
+    out->args.push_back(a);
+  }
+  Arg o; o.kind = Arg::SlotPtr; o.slot = -4; out->args.push_back(o);
+  Arg st; st.kind = Arg::Status; out->args.push_back(st);
+  (void)sm_count;
+  return true;
+}
 std::vector<std::pair<std::string, std::string>> representative_kernel_sources() { return {}; }
 
 }  // namespace ku::cu

@@ -1,0 +1,252 @@
+// Fused scaled-dot-product attention for sm_100a (Op::Sdpa, kurumi_core/src/graph/op.rs:55-58):
+// out = softmax(q k^T / sqrt(dh) [+ causal mask]) v over the trailing [S, DH] of [BH, S, DH] bf16 / f16
+// tensors, online softmax, no S x S buffer. The math is the interpreter's decomposition
+// (kurumi_core/src/interp/nn.rs:125-172): scale = 1/sqrt(dh) as f32, key j > query i masked to -inf,
+// softmax in f32; results stay within rel 2e-2 of the f64 run.
+//
+// One CTA per (head, block of 128 queries); key/value blocks of 128 stream through two-stage rings.
+//   warp 0      TMA producer: Q once, then K_j / V_j (cp.async.bulk.tensor, SWIZZLE_128B, no multicast)
+//   warp 1      tcgen05.mma issuer: S_j = Q K_j^T into one of two TMEM score buffers (so the scores of
+//               block j+1 are computed while block j is in the softmax), then O_j = P_j V_j
+//   warps 2..5  one query row per thread: tcgen05.ld the scores, running max / sum in the log2
+//               domain, P_j as bf16 into shared memory in the swizzled K-major layout the second
+//               MMA reads, then tcgen05.ld O_j and fold it into the register accumulator
+// Causal: key blocks above the diagonal are never loaded; the diagonal block is masked per element.
+// Every mbarrier wait is bounded (status word + sticky failure), tensor memory is always released.
+//
+// Spliced in by the host: BH, S, DH (64 or 128), CAUSAL, SCALE_LOG2E (scale * log2 e as a float
+// literal), IDESC_S, IDESC_O, KU_IS_BF16.
+#define BQ 128
+#define BKV 128
+#define DCH (DH / 64)                    // 64-element (128-byte) chunks along the head dimension
+#define TILE_BYTES (128 * 128 * DCH)     // one [128 rows][DH] bf16 tile: DCH chunks of [128][128 bytes]
+#define P_BYTES (128 * 128 * 2)          // [128 queries][128 keys] bf16: 2 chunks of [128][128 bytes]
+#define SPIN_LIMIT (1u << 24)
+
+struct alignas(64) KuTmap { unsigned long long opaque[16]; };
+
+__device__ __forceinline__ unsigned ku_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ku_mbar_init(unsigned a, unsigned n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(n)); }
+__device__ __forceinline__ void ku_mbar_expect(unsigned a, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ku_mbar_arrive(unsigned a) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory"); }
+__device__ __forceinline__ bool ku_mbar_try(unsigned a, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool ku_wait(unsigned a, unsigned parity, bool& failed, int* status) {
+  if (failed) return false;
+  unsigned spins = 0;
+  while (!ku_mbar_try(a, parity)) {
+    ++spins;
+    if ((spins & 4095u) == 0 && *(volatile int*)status != 0) { failed = true; return false; }
+    if (spins > SPIN_LIMIT) { failed = true; atomicExch(status, 6); return false; }
+  }
+  return true;
+}
+__device__ __forceinline__ void ku_tma_3d(unsigned dst, const KuTmap* map, int x, int y, int z, unsigned mbar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ unsigned long long ku_smem_desc(unsigned addr, unsigned lbo, unsigned sbo) {
+  return (unsigned long long)((addr & 0x3FFFFu) >> 4) | ((unsigned long long)(lbo >> 4) << 16) | ((unsigned long long)(sbo >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void ku_mma(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void ku_mma_commit(unsigned mbar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void ku_tmem_ld32(unsigned taddr, float* v) {
+  unsigned* r = (unsigned*)v;
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+      "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+        "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+        "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ku_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ unsigned ku_pack2(float lo, float hi) {
+#if KU_IS_BF16
+  unsigned r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r;
+#else
+  unsigned r; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r;
+#endif
+}
+
+extern "C" __global__ void __launch_bounds__(192, 1)
+ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ KuTmap tmap_k, const __grid_constant__ KuTmap tmap_v, void* __restrict__ Op,
+                int* __restrict__ status) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_ready, o_full, o_free;
+  __shared__ unsigned tmem_base_slot;
+  unsigned char* smem = smem_raw + ((1024u - (ku_smem(smem_raw) & 1023u)) & 1023u);
+  const unsigned q_s = ku_smem(smem), k_s = q_s + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES, p_s = v_s + 2 * TILE_BYTES;
+  unsigned char* p_tile = smem + 5 * TILE_BYTES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) query blocks first
+  const int bh = blockIdx.y;
+  const int kv_blocks = (S + BKV - 1) / BKV;
+  const int nkv = CAUSAL ? ((qb + 1) < kv_blocks ? (qb + 1) : kv_blocks) : kv_blocks;
+
+  if (threadIdx.x == 0) {
+    ku_mbar_init(ku_smem(&q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      ku_mbar_init(ku_smem(&k_full[i]), 1); ku_mbar_init(ku_smem(&k_empty[i]), 1); ku_mbar_init(ku_smem(&v_full[i]), 1); ku_mbar_init(ku_smem(&v_empty[i]), 1);
+      ku_mbar_init(ku_smem(&s_full[i]), 1); ku_mbar_init(ku_smem(&s_free[i]), 128);
+    }
+    ku_mbar_init(ku_smem(&p_ready), 128); ku_mbar_init(ku_smem(&o_full), 1); ku_mbar_init(ku_smem(&o_free), 128);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ku_smem(&tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = tmem_base_slot;   // columns [0,128) and [128,256): score buffers; [256, 256+DH): O_j
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer ----
+      ku_mbar_expect(ku_smem(&q_full), TILE_BYTES);
+      for (int c = 0; c < DCH; ++c) ku_tma_3d(q_s + c * 16384, &tmap_q, c * 64, qb * BQ, bh, ku_smem(&q_full));
+      for (int j = 0; j < nkv; ++j) {
+        const int st = j & 1;
+        const unsigned ph = (j >> 1) & 1;
+        ku_wait(ku_smem(&k_empty[st]), ph ^ 1, failed, status);
+        ku_mbar_expect(ku_smem(&k_full[st]), TILE_BYTES);
+        for (int c = 0; c < DCH; ++c) ku_tma_3d(k_s + st * TILE_BYTES + c * 16384, &tmap_k, c * 64, j * BKV, bh, ku_smem(&k_full[st]));
+        ku_wait(ku_smem(&v_empty[st]), ph ^ 1, failed, status);
+        ku_mbar_expect(ku_smem(&v_full[st]), TILE_BYTES);
+        for (int c = 0; c < DCH; ++c) ku_tma_3d(v_s + st * TILE_BYTES + c * 16384, &tmap_v, c * 64, j * BKV, bh, ku_smem(&v_full[st]));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // ---- MMA issuer ----
+      auto issue_s = [&](int j) {   // S_j = Q K_j^T: both operands K-major over the head dimension
+        const int st = j & 1;
+        ku_wait(ku_smem(&k_full[st]), (j >> 1) & 1, failed, status);
+        ku_wait(ku_smem(&s_free[st]), ((j >> 1) & 1) ^ 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          const unsigned off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          ku_mma(tmem_base + st * 128, ku_smem_desc(q_s + off, 16, 1024), ku_smem_desc(k_s + st * TILE_BYTES + off, 16, 1024), IDESC_S, kk != 0);
+        }
+        ku_mma_commit(ku_smem(&s_full[st]));
+        ku_mma_commit(ku_smem(&k_empty[st]));
+      };
+      ku_wait(ku_smem(&q_full), 0, failed, status);
+      issue_s(0);
+      for (int j = 0; j < nkv; ++j) {
+        if (j + 1 < nkv) issue_s(j + 1);
+        const int st = j & 1;
+        ku_wait(ku_smem(&v_full[st]), (j >> 1) & 1, failed, status);
+        ku_wait(ku_smem(&p_ready), j & 1, failed, status);
+        ku_wait(ku_smem(&o_free), (j & 1) ^ 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {   // O_j = P_j V_j: P K-major over keys, V MN-major (head dimension contiguous)
+          const unsigned long long ad = ku_smem_desc(p_s + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+          const unsigned long long bd = ku_smem_desc(v_s + st * TILE_BYTES + kk * 16 * 128, 16384, 1024);
+          ku_mma(tmem_base + 256, ad, bd, IDESC_O, kk != 0);
+        }
+        ku_mma_commit(ku_smem(&o_full));
+        ku_mma_commit(ku_smem(&v_empty[st]));
+      }
+    }
+  } else {  // ---- softmax + accumulate: one query row per thread ----
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;                 // row of the tile == TMEM lane
+    const int qrow = qb * BQ + r;
+    const unsigned lane_addr = tmem_base + ((unsigned)(q4 * 32) << 16);
+    float o[DH];
+#pragma unroll
+    for (int c = 0; c < DH; ++c) o[c] = 0.0f;
+    float m = -KU_INF, l = 0.0f;
+    for (int j = 0; j < nkv; ++j) {
+      const int st = j & 1;
+      ku_wait(ku_smem(&s_full[st]), (j >> 1) & 1, failed, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool need_mask = (CAUSAL && j == qb) || (j * BKV + BKV > S);
+      // pass A: block maximum of this row
+      float bm = -KU_INF;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BKV; c0 += 32) {
+        float v[32];
+        ku_tmem_ld32(lane_addr + st * 128 + c0, v);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int key = j * BKV + c0 + c;
+          const bool masked = need_mask && ((CAUSAL && key > qrow) || key >= S);
+          bm = fmaxf(bm, masked ? -KU_INF : v[c] * SCALE_LOG2E);
+        }
+      }
+      const float mn = fmaxf(m, bm);
+      const float alpha = ku_ex2(m - mn);   // 0 on the first block (m = -inf)
+      // pass B: probabilities, as bf16 into the swizzled K-major tile the second MMA reads
+      float bs = 0.0f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BKV; c0 += 32) {
+        float v[32];
+        ku_tmem_ld32(lane_addr + st * 128 + c0, v);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int key = j * BKV + c0 + c;
+          const bool masked = need_mask && ((CAUSAL && key > qrow) || key >= S);
+          v[c] = masked ? 0.0f : ku_ex2(__fmaf_rn(v[c], SCALE_LOG2E, -mn));
+          bs += v[c];
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {   // 8 keys = one 16-byte chunk of the row
+          uint4 pk;
+          pk.x = ku_pack2(v[g * 8 + 0], v[g * 8 + 1]); pk.y = ku_pack2(v[g * 8 + 2], v[g * 8 + 3]);
+          pk.z = ku_pack2(v[g * 8 + 4], v[g * 8 + 5]); pk.w = ku_pack2(v[g * 8 + 6], v[g * 8 + 7]);
+          const int col = c0 + g * 8;   // first key of the chunk
+          const int chunk16 = (col & 63) >> 3;
+          *(uint4*)(p_tile + (col >> 6) * 16384 + r * 128 + ((chunk16 ^ (r & 7)) << 4)) = pk;
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      ku_mbar_arrive(ku_smem(&s_free[st]));                          // the score buffer may be overwritten
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core (async proxy)
+      ku_mbar_arrive(ku_smem(&p_ready));
+      l = l * alpha + bs;
+      m = mn;
+      ku_wait(ku_smem(&o_full), j & 1, failed, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c0 = 0; c0 < DH; c0 += 32) {
+        float v[32];
+        ku_tmem_ld32(lane_addr + 256 + c0, v);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o[c0 + c] = __fmaf_rn(o[c0 + c], alpha, v[c]);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      ku_mbar_arrive(ku_smem(&o_free));
+    }
+    if (qrow < S) {
+      const float inv = 1.0f / l;
+      uint4* dst = (uint4*)((unsigned short*)Op + ((i64)bh * S + qrow) * DH);
+#pragma unroll
+      for (int g = 0; g < DH / 8; ++g) {
+        uint4 pk;
+        pk.x = ku_pack2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv); pk.y = ku_pack2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
+        pk.z = ku_pack2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv); pk.w = ku_pack2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
+        dst[g] = pk;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+}

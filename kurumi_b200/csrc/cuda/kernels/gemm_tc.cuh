@@ -29,7 +29,7 @@
 #define B_STAGE_BYTES (BN * BKB)
 #define STAGE_BYTES (A_STAGE_BYTES + B_STAGE_BYTES)
 #define KBLOCKS ((K + BK - 1) / BK)
-#define SPIN_LIMIT (1u << 27)
+#define SPIN_LIMIT (1u << 24)
 
 struct alignas(64) KuTmap { unsigned long long opaque[16]; };
 
@@ -49,7 +49,9 @@ __device__ __forceinline__ bool ku_wait(unsigned a, unsigned parity, bool& faile
   if (failed) return false;
   unsigned spins = 0;
   while (!ku_mbar_try(a, parity)) {
-    if (++spins > SPIN_LIMIT) { failed = true; atomicExch(status, 2); return false; }
+    ++spins;
+    if ((spins & 4095u) == 0 && *(volatile int*)status != 0) { failed = true; return false; }  // another role already gave up
+    if (spins > SPIN_LIMIT) { failed = true; atomicExch(status, 2); return false; }
   }
   return true;
 }

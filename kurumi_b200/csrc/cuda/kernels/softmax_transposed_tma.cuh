@@ -18,7 +18,7 @@
 #define NW (NT / 32)
 #define KU_LOG2E 1.4426950408889634f
 #define TILE_BYTES (CJ * 128)
-#define SPIN_LIMIT (1u << 26)
+#define SPIN_LIMIT (1u << 22)
 
 struct alignas(64) KuTmap { unsigned long long opaque[16]; };
 
@@ -73,6 +73,10 @@ ku_softmax_transposed_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEA
   // the swizzle pattern is a function of the shared-memory address: tiles start on a 1024-byte boundary
   unsigned char* tiles = tiles_raw + ((1024u - (ku_smem(tiles_raw) & 1023u)) & 1023u);
   const unsigned tiles_s = ku_smem(tiles);
+  if (tiles != tiles_raw) {  // the host sized the ring without slack: a misplaced ring is reported, not used
+    if (threadIdx.x == 0) atomicExch(status, 5);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int b = 0; b < NBUF; ++b) ku_mbar_init(ku_smem(&full[b]), 1);
@@ -93,9 +97,12 @@ ku_softmax_transposed_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEA
   for (int slab = cid; slab < NSLABS; slab += nclusters, ++n) {
     const int b = n % NBUF;
     const unsigned parity = (n / NBUF) & 1, mb = ku_smem(&full[b]);
+    bool failed = false;
     unsigned spins = 0;
-    while (!ku_mbar_try(mb, parity)) {
-      if (++spins > SPIN_LIMIT) { atomicExch(status, 1); break; }
+    while (!failed && !ku_mbar_try(mb, parity)) {
+      ++spins;
+      if ((spins & 1023u) == 0 && *(volatile int*)status != 0) failed = true;   // someone already gave up: stop waiting everywhere
+      if (spins > SPIN_LIMIT) { atomicExch(status, 1); failed = true; }
     }
     unsigned char* tile = tiles + b * TILE_BYTES;
     const int i0 = slab * 32, pp = n & 1;
@@ -118,7 +125,6 @@ ku_softmax_transposed_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEA
 #endif
       m = fmaxf(m, v);
     }
-    bool failed = false;
     const unsigned xparity = (n >> 1) & 1;   // each exchange barrier is used every second slab
     part[warp][lane] = m;
     __syncthreads();
@@ -133,7 +139,7 @@ ku_softmax_transposed_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEA
       ku_st_async(ku_mapa(ku_smem(&gather_max[pp][rank][lane]), warp), cta_val[lane], ku_mapa(ku_smem(&bar_max[pp]), warp));
     {
       unsigned sp = 0;
-      while (!failed && !ku_mbar_try(ku_smem(&bar_max[pp]), xparity)) if (++sp > SPIN_LIMIT) { atomicExch(status, 3); failed = true; }
+      while (!failed && !ku_mbar_try(ku_smem(&bar_max[pp]), xparity)) { ++sp; if ((sp & 1023u) == 0 && *(volatile int*)status != 0) failed = true; if (sp > SPIN_LIMIT) { atomicExch(status, 3); failed = true; } }
     }
     float mx = gather_max[pp][0][lane];
 #pragma unroll
@@ -156,7 +162,7 @@ ku_softmax_transposed_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEA
     if (warp < CL) ku_st_async(ku_mapa(ku_smem(&gather_sum[pp][rank][lane]), warp), cta_val[lane], ku_mapa(ku_smem(&bar_sum[pp]), warp));
     {
       unsigned sp = 0;
-      while (!failed && !ku_mbar_try(ku_smem(&bar_sum[pp]), xparity)) if (++sp > SPIN_LIMIT) { atomicExch(status, 4); failed = true; }
+      while (!failed && !ku_mbar_try(ku_smem(&bar_sum[pp]), xparity)) { ++sp; if ((sp & 1023u) == 0 && *(volatile int*)status != 0) failed = true; if (sp > SPIN_LIMIT) { atomicExch(status, 4); failed = true; } }
     }
     if (warp == 0) {
       float r = gather_sum[pp][0][lane];

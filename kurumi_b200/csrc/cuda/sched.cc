@@ -269,7 +269,13 @@ Fused Scheduler::softmax(OpKind k, const Fused& f0, size_t axis, float eps) {
   if (!dry() && numel(f.shape) > 0) {
     Launch L;
     std::vector<int> leaf_args;
-    if (k == OpKind::Softmax && build_softmax_transposed(*load_, f, axis, sm_, &L, &leaf_args)) {
+    size_t scratch = 0;
+    if (k == OpKind::Softmax && build_softmax_two_pass(f, axis, &L, &scratch)) {
+      const int sslot = new_slot(Slot::Temp, DType::U8, {scratch});
+      for (auto& a : L.args) { if (a.slot == -3) a.slot = slot; else if (a.slot == -1) a.slot = sslot; }
+      L.algo_bytes = leaf_bytes(f) + static_cast<double>(prog_.slots[static_cast<size_t>(slot)].bytes);
+      prog_.launches.push_back(std::move(L));
+    } else if (k == OpKind::Softmax && build_softmax_transposed(*load_, f, axis, sm_, &L, &leaf_args)) {
       for (int li : leaf_args) { Arg a; a.kind = Arg::SlotPtr; a.slot = f.leaves[static_cast<size_t>(li)].slot; L.args.push_back(a); }
       Arg o; o.kind = Arg::SlotPtr; o.slot = slot; L.args.push_back(o);
       if (L.status_arg) { Arg st; st.kind = Arg::Status; L.args.push_back(st); }

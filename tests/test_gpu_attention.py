@@ -1,0 +1,54 @@
+"""Parity of fused attention (Op::Sdpa on the tcgen05 kernel) and of the decomposed form with the CPU
+oracle. Tolerance: rel 2e-2 against the f64 interpreter run, as stated for bf16 attention."""
+import numpy as np
+import pytest
+
+from kurumi_b200 import api, configs
+from tests import util
+from tests.util import Pair
+
+pytestmark = pytest.mark.gpu
+
+
+def bf16(rng, shape, scale=1.0):
+    return api.f32_to_bf16((rng.standard_normal(shape) * scale).astype(np.float32))
+
+
+@pytest.mark.parametrize("shape,causal", [((2, 3, 256, 128), True), ((1, 2, 384, 64), True), ((2, 200, 128), True), ((1, 1, 128, 128), False),
+                                          ((3, 130, 64), False), ((1, 4, 1, 128), True), ((1, 2, 640, 128), True)])
+def test_fused_attention_matches_oracle(oracle_lib, cuda_lib, cpu, cpu64, gpu, shape, causal):
+    rng = np.random.default_rng(40)
+    p = Pair(oracle_lib, cuda_lib)
+    q, k, v = (p.feed(shape, api.BF16, bf16(rng, shape)) for _ in range(3))
+    out = p.sdpa_fused(q, k, v, causal)
+    assert api.compile_check(cuda_lib, p.gc, [out]) == ["attention_tc"]
+    o, c, dts = p.run(cpu, gpu, [out])
+    w, _, _ = p.run(cpu64, gpu, [out])
+    got = util.to_f64(c[0], dts[0])
+    util.assert_close(w[0], got, 2e-2, 2e-2 * np.abs(w[0]).max(), "fused attention vs f64 run")
+    # the native-dtype oracle rounds scores and probabilities to bf16 on the way: same band
+    util.assert_close(util.to_f64(o[0], dts[0]), got, 2e-2, 2e-2 * np.abs(w[0]).max(), "fused attention vs bf16 oracle")
+    if causal:   # query 0 attends to key 0 only (kurumi_core/tests/ops.rs:258-270)
+        vv = util.to_f64(p.feeds[v][0], api.BF16)
+        assert np.array_equal(got[..., 0, :], vv[..., 0, :])
+
+
+def test_decomposed_attention_and_auto_selection(oracle_lib, cuda_lib, cpu, cpu64, gpu):
+    rng = np.random.default_rng(41)
+    for tag, mk in ((api.F32, lambda s: rng.standard_normal(s).astype(np.float32)), (api.BF16, lambda s: bf16(rng, s))):
+        p = Pair(oracle_lib, cuda_lib)
+        shape = (2, 2, 48, 16)
+        q, k, v = (p.feed(shape, tag, mk(shape)) for _ in range(3))
+        nodes = [p.sdpa(q, k, v, True), p.sdpa_decomposed(q, k, v, False), p.sdpa_fused(q, k, v, True)]   # dh = 16: the fused primitive runs decomposed on device
+        o, c, dts = p.run(cpu, gpu, nodes)
+        w, _, _ = p.run(cpu64, gpu, nodes)
+        for a, b, z, dt in zip(o, c, w, dts):
+            tol = 1e-4 if tag == api.F32 else 2e-2
+            util.assert_close(z, util.to_f64(b, dt), tol, tol * np.abs(z).max(), "decomposed attention")
+
+
+def test_attention_config_graph_uses_the_fused_primitive(cuda_lib):
+    g = api.Graph(cuda_lib)
+    root, _ = configs.causal_attention(g)     # [8, 32, 4096, 128]: score buffer over 1 GiB -> Op::Sdpa
+    assert "Sdpa" in g.dump(root)
+    assert api.compile_check(cuda_lib, g, [root]) == ["attention_tc"]
