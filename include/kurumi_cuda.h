@@ -80,6 +80,20 @@ KuNode ku_sdpa_decomposed(KuGraph *g, KuNode q, KuNode k, KuNode v, uint32_t cau
  * graph. Queued on the backend's stream; scratch comes from the backend's device pool. 0 ok, -1 error. */
 int32_t ku_cuda_softmax_lines_f32(const KuBackend *b, const float *in, const float *bias, float *out, size_t lines, size_t len, size_t ld);
 
+/* The same softmax for callers that must not allocate device memory when they call it: a
+ * latency-critical loop that cannot take the device-wide synchronisation cudaMalloc / cudaFree may
+ * imply, a host application that owns all of HBM through its own arena, or code running where the
+ * CUDA allocator must not be entered (host callbacks, allocation hooks). No counterpart in the reference: kurumi
+ * has no device entry point of this kind. The scratch is a fixed 8 MiB array in the library's device
+ * image (every GPU that loads the library holds it until exit), so the call is rejected with -1 when
+ * lines * ceil(len / 128) * 8 + lines * 4 bytes exceed 8 MiB (for example 8192 lines of 8192 fit,
+ * 16384 lines of 16384 do not). Runs on `stream` (a cudaStream_t) of the current device. The first call
+ * on each device looks up the array's device address (cudaGetSymbolAddress); that first call should
+ * come before any stream capture begins. All
+ * calls share the one array: nothing in it needs clearing between calls, but two calls whose kernels
+ * can overlap on the GPU (different streams, no dependency) race on it. No cudaMalloc / cudaFree. */
+int32_t ku_cuda_softmax_lines_f32_noalloc(const float *in, const float *bias, float *out, size_t lines, size_t len, size_t ld, void *stream);
+
 /* Compile every kernel the evaluation of ids[0..n] needs to an sm_100a cubin, without a GPU.
  * Writes the kernel family of each launch, one per line, into out (no NUL); returns the full
  * length, or (size_t)-1 on error. */

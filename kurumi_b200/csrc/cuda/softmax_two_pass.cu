@@ -179,3 +179,48 @@ extern "C" int32_t ku_cuda_softmax_lines_f32(const KuBackend* b, const float* in
     return 0;
   });
 }
+
+// ---- the entry point that allocates nothing -------------------------------------------------------
+// Some callers may not allocate device memory at the moment they need this softmax: a serving loop
+// whose latency budget has no room for the device-wide synchronisation cudaMalloc / cudaFree can
+// imply, a host application that has handed all of HBM to its own arena so the CUDA allocator has
+// nothing left to give, or code that runs where entering the CUDA allocator is not allowed (a
+// host callback, another library's allocation hook). For them the scratch of the two-pass algorithm
+// lives in a fixed array inside the library's device image.
+namespace {
+constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;  // 8 MiB per GPU that loads the library, held until the process exits
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address: the address
+// this device gave the array has to be asked for, once per device, with that device current.
+void* noalloc_scratch_for_current_device() {
+  int dev = -1;
+  ku::cu::cuda_check(cudaGetDevice(&dev), "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) throw ku::Error::backend("ku_cuda_softmax_lines_f32_noalloc: device index out of range");
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    ku::cu::cuda_check(cudaGetSymbolAddress(&p, g_noalloc_scratch), "cudaGetSymbolAddress(scratch)");
+    g_noalloc_ptr[dev] = p;
+  }
+  return g_noalloc_ptr[dev];
+}
+}  // namespace
+
+extern "C" int32_t ku_cuda_softmax_lines_f32_noalloc(const float* in, const float* bias, float* out, size_t lines, size_t len, size_t ld, void* stream) {
+  if (!args_ok(in, out, lines, len, ld)) return -1;
+  return ku::guard<int32_t>(-1, [&]() -> int32_t {
+    const size_t need = scratch_bytes(lines, len);
+    if (need > kNoAllocScratchBytes)
+      throw ku::Error::backend("ku_cuda_softmax_lines_f32_noalloc: lines * ceil(len / 128) * 8 + lines * 4 = " + std::to_string(need) +
+                               " bytes of scratch exceed the fixed " + std::to_string(kNoAllocScratchBytes) + "; use ku_cuda_softmax_lines_f32");
+    void* scratch = noalloc_scratch_for_current_device();
+    // every scratch entry the kernels read is written earlier in the same call, so nothing needs clearing
+    ku::cu::cuda_check(launch_two_pass(in, bias, out, lines, len, ld, scratch, static_cast<cudaStream_t>(stream)), "ku_cuda_softmax_lines_f32_noalloc");
+    return 0;
+  });
+}
