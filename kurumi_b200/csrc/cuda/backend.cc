@@ -126,6 +126,7 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
       ev = ev_used_++;
       cuda_check(cudaEventRecord(ev_pool_[ev].first, rt_.stream()), "cudaEventRecord");
     }
+    if (L.zero_slot >= 0) cuda_check(cudaMemsetAsync(ptr[static_cast<size_t>(L.zero_slot)], 0, L.zero_bytes, rt_.stream()), "cudaMemsetAsync(control block)");
     if (L.host_launch) {
       L.host_launch(vals, rt_.stream());
       ++rt_.stats.launches;

@@ -99,7 +99,7 @@ int32_t ku_cuda_eval_device(KuGraph* g, const KuNode* ids, size_t n, const KuBac
   });
 }
 
-int32_t ku_cuda_sync(const KuBackend* b) { return guard<int32_t>(-1, [&]() { cuda_of(b)->runtime().sync(); return 0; }); }
+int32_t ku_cuda_sync(const KuBackend* b) { return guard<int32_t>(-1, [&]() { cuda_of(b)->runtime().check_status(); return 0; }); }
 void* ku_cuda_stream(const KuBackend* b) { return guard<void*>(nullptr, [&]() { return static_cast<void*>(cuda_of(b)->runtime().stream()); }); }
 int32_t ku_cuda_device(const KuBackend* b) { return guard<int32_t>(-1, [&]() { return cuda_of(b)->runtime().device(); }); }
 

@@ -99,6 +99,8 @@ struct Launch {
   // arguments and calls this instead of launching `kernel`.
   std::function<void(const std::vector<void*>& ptrs, cudaStream_t stream)> host_launch;
   std::vector<Arg> args;
+  int zero_slot = -1;       // when >= 0: the first zero_bytes of this slot are cleared on the stream before the launch
+  size_t zero_bytes = 0;
   double algo_bytes = 0, flops = 0;  // algorithmic traffic / work of this launch
 };
 

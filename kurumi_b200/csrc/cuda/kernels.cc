@@ -85,14 +85,13 @@ extern const std::string kSrc_softmax_transposed_tma;
 
 
 size_t softmax_two_pass_scratch_bytes(size_t lines, size_t len);
-void softmax_two_pass_launch(const float* in, const float* bias, float* out, size_t lines, size_t len, size_t ld, void* scratch, cudaStream_t stream);
+void softmax_two_pass_launch(const float* in, const float* bias, float* out, size_t lines, size_t len, size_t ld, void* scratch, cudaStream_t stream, int sm_count, int* status);
 
-bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* scratch_bytes) {
+bool build_softmax_two_pass(const Fused& f, size_t axis, int sm_count, Launch* out, size_t* scratch_bytes) {
   if (std::getenv("KURUMI_SMT_NO_TWO_PASS")) return false;
   if (f.dtype() != DType::F32 || f.shape.size() != 2 || axis != 1) return false;
   const int64_t lines = static_cast<int64_t>(f.shape[0]), len = static_cast<int64_t>(f.shape[1]);
-  // lines of 2048 positions and more go to the single-pass cluster kernel, which measured faster there
-  if (len >= 2048 && !std::getenv("KURUMI_SMT_TWO_PASS")) return false;
+  if (std::getenv("KURUMI_SMT_CLUSTER") && len >= 2048) return false;   // prefer the single-pass cluster kernel
   if (lines < 64 || len < 256 || lines >= (int64_t(1) << 31) || len >= (int64_t(1) << 31)) return false;
   auto is_big = [&](const Leaf& l) {
     return l.kind == LeafKind::Buffer && l.dtype == DType::F32 && l.view.guards.empty() && l.view.stride[0] == 1 && l.view.stride[1] >= lines && l.view.base >= 0;
@@ -125,10 +124,56 @@ bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* sc
   out->args.push_back(bi);
   Arg o; o.kind = Arg::SlotPtr; o.slot = -3; out->args.push_back(o);
   Arg sc; sc.kind = Arg::SlotPtr; sc.slot = -1; out->args.push_back(sc);
+  Arg st; st.kind = Arg::Status; out->args.push_back(st);
   out->host_launch = [=](const std::vector<void*>& p, cudaStream_t stream) {
     softmax_two_pass_launch(static_cast<const float*>(p[0]), has_bias ? static_cast<const float*>(p[1]) : nullptr, static_cast<float*>(p[2]), static_cast<size_t>(lines),
-                            static_cast<size_t>(len), ld, p[3], stream);
+                            static_cast<size_t>(len), ld, p[3], stream, sm_count, static_cast<int*>(p[4]));
   };
+  return true;
+}
+
+extern const std::string kSrc_softmax_panels_tma;
+
+size_t softmax_panels_scratch_bytes(int64_t R, int64_t C, int64_t jt, int64_t npb) {
+  const int64_t nj = (C + jt - 1) / jt;
+  return static_cast<size_t>(16384 + (R * 4 + 255) / 256 * 256 + npb * nj * 256 * 8);   // control block, c, partials [npb][nj][256 lines]
+}
+
+bool build_softmax_panels(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args, size_t* scratch_bytes) {
+  if (f.dtype() != DType::F32 || std::getenv("KURUMI_SMT_NO_PANELS")) return false;
+  std::string src_fn;
+  int64_t R = 0, C = 0;
+  bool transposed = false;
+  LineLeaf big;
+  if (!emit_line_source_fn(f, axis, &src_fn, leaf_args, &R, &C, &transposed, &big) || !transposed || big.leaf < 0) return false;
+  if (R < 64 || C < 256 || R * C < (int64_t(1) << 20) || (R + 255) / 256 > 1024 || C >= (int64_t(1) << 30)) return false;
+  auto env = [](const char* name, int64_t dflt) { const char* e = std::getenv(name); return e ? static_cast<int64_t>(std::atoi(e)) : dflt; };
+  const int64_t jt = env("KURUMI_SMP_JT", 256) == 128 ? 128 : 256;
+  const int64_t nbuf = std::min<int64_t>(6, std::max<int64_t>(1, env("KURUMI_SMP_NBUF", 2)));
+  const int64_t la = std::min<int64_t>(8, std::max<int64_t>(2, env("KURUMI_SMP_LA", 4)));
+  const int64_t lc = std::min<int64_t>(la - 1, std::max<int64_t>(1, env("KURUMI_SMP_LC", 2)));
+  const int64_t npb = la + 2;
+  std::string src = device_prelude() + src_fn +
+                    defines({{"R", R}, {"C", C}, {"JT", jt}, {"NBUF", nbuf}, {"LA", la}, {"LC", lc}, {"NPB", npb}, {"KU_L2_HINTS", env("KURUMI_SMP_HINTS", 1)}, {"KU_OUT_F32", 1}, {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
+                    kSrc_softmax_panels_tma;
+  out->name = "softmax_panels_tma";
+  out->kernel = load(src, "ku_softmax_panels_tma", false);
+  out->grid[0] = static_cast<unsigned>(sm_count * std::min<int64_t>(8, std::max<int64_t>(1, env("KURUMI_SMP_CTAS", 8))));
+  out->block[0] = 256;
+  out->smem = static_cast<unsigned>(nbuf * jt * 128 + 1024);   // 1024 bytes of slack: the ring is placed on a 1024-byte boundary
+  out->persistent_clusters = -1;                               // cap the grid at the co-resident CTA count on first launch
+  Arg tm;
+  tm.kind = Arg::Tmap;
+  tm.tm.slot = f.leaves[static_cast<size_t>(big.leaf)].slot;
+  tm.tm.byte_offset = big.base * 4;
+  tm.tm.dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  tm.tm.rank = 2;
+  tm.tm.dims[0] = static_cast<uint64_t>(R); tm.tm.dims[1] = static_cast<uint64_t>(C);
+  tm.tm.strides[0] = static_cast<uint64_t>(big.ld) * 4;
+  tm.tm.box[0] = 32; tm.tm.box[1] = static_cast<uint32_t>(jt);
+  tm.tm.swz = CU_TENSOR_MAP_SWIZZLE_128B;
+  out->args.push_back(tm);
+  *scratch_bytes = softmax_panels_scratch_bytes(R, C, jt, npb);
   return true;
 }
 

@@ -14,11 +14,16 @@ bool build_gemm_tc(const KernelLoader& load, const GemmDesc& d, const Fused* epi
 // (a softmax consumed through a transpose view). Returns false when the pattern does not apply.
 bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args);
 
+// The same softmax as two passes inside one persistent TMA-fed kernel whose second pass reads from L2
+// (kernels/softmax_panels_tma.cuh). After the leaf arguments the kernel takes {output, scratch, status};
+// the caller creates the scratch slot of `*scratch_bytes` bytes and has its first 16 KB cleared before each launch.
+bool build_softmax_panels(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args, size_t* scratch_bytes);
+
 // The streaming two-pass form of the same softmax (precompiled kernels, softmax_two_pass.cu) for the
 // plain case: one f32 buffer read transposed, optionally plus a bias that broadcasts along the lines.
 // On success `out->args` is {input, bias (or input again when absent), output, scratch} with the
 // scratch slot symbolic (-1) and `*scratch_bytes` set; the caller creates that slot.
-bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* scratch_bytes);
+bool build_softmax_two_pass(const Fused& f, size_t axis, int sm_count, Launch* out, size_t* scratch_bytes);
 
 // Fused causal / full attention with online softmax. Slots are symbolic: -1 q, -2 k, -3 v, -4 out.
 bool attention_supported(DType dt, const Shape& shape);

@@ -1,5 +1,7 @@
 #include "sched.h"
 
+#include <cstdio>
+
 #include <algorithm>
 #include <cmath>
 
@@ -270,7 +272,17 @@ Fused Scheduler::softmax(OpKind k, const Fused& f0, size_t axis, float eps) {
     Launch L;
     std::vector<int> leaf_args;
     size_t scratch = 0;
-    if (k == OpKind::Softmax && build_softmax_two_pass(f, axis, &L, &scratch)) {
+    if (k == OpKind::Softmax && build_softmax_panels(*load_, f, axis, sm_, &L, &leaf_args, &scratch)) {
+      const int sslot = new_slot(Slot::Temp, DType::U8, {scratch});
+      for (int li : leaf_args) { Arg a; a.kind = Arg::SlotPtr; a.slot = f.leaves[static_cast<size_t>(li)].slot; L.args.push_back(a); }
+      Arg o; o.kind = Arg::SlotPtr; o.slot = slot; L.args.push_back(o);
+      Arg sc; sc.kind = Arg::SlotPtr; sc.slot = sslot; L.args.push_back(sc);
+      Arg st; st.kind = Arg::Status; L.args.push_back(st);
+      L.zero_slot = sslot;
+      L.zero_bytes = 16384;
+      L.algo_bytes = leaf_bytes(f) + static_cast<double>(prog_.slots[static_cast<size_t>(slot)].bytes);
+      prog_.launches.push_back(std::move(L));
+    } else if (k == OpKind::Softmax && (L = Launch(), leaf_args.clear(), build_softmax_two_pass(f, axis, sm_, &L, &scratch))) {
       const int sslot = new_slot(Slot::Temp, DType::U8, {scratch});
       for (auto& a : L.args) { if (a.slot == -3) a.slot = slot; else if (a.slot == -1) a.slot = sslot; }
       L.algo_bytes = leaf_bytes(f) + static_cast<double>(prog_.slots[static_cast<size_t>(slot)].bytes);
@@ -533,6 +545,7 @@ std::vector<std::string> compile_check(const Graph& g, const std::vector<NodeId>
   const std::vector<bool> plan = dry.fuse_plan();
   const KernelLoader load = [](const std::string& src, const std::string& entry, bool fmad) {
     std::string log;
+    if (std::getenv("KURUMI_CUDA_DUMP")) fprintf(stderr, "---- kurumi_cuda kernel %s ----\n%s\n", entry.c_str(), src.c_str());
     std::string cubin = Runtime::compile_to_cubin(src, fmad, &log);
     if (cubin.find(entry) == std::string::npos) throw Error::backend("compiled cubin lacks entry point " + entry);
     return Kernel{};

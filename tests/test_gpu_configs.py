@@ -38,7 +38,12 @@ def run_config(make, kwargs, oracle_lib, cuda_lib, cpu, cpu64, gpu):
         dv = gpu.eval(h, mk(h)).numpy()
         ref = util.to_f64(vals[n][0], vals[n][1])
         dev = util.to_f64(dv, vals[n][1])
-        assert (np.abs(dev - ref) <= 1e-5 * np.abs(ref) + 1e-6 + (2.0 ** -7 * np.abs(ref) if vals[n][1] != api.F32 else 0)).all()
+        # the float steps after the draws (log, cos, the quantising divide) may differ in the last place, which
+        # a narrow output type turns into at most one of ITS steps, and only at a rounding boundary
+        step = {api.F32: 0.0, api.F8E4M3: 2.0 ** -3}.get(vals[n][1], 2.0 ** -7)
+        assert (np.abs(dev - ref) <= 1e-5 * np.abs(ref) + 1e-6 + step * np.abs(ref)).all()
+        if step:
+            assert (dev != ref).mean() <= 2e-3
     return util.to_f64(got.numpy(), got.dtype), util.to_f64(native.numpy(), native.dtype), wide, got.dtype
 
 
