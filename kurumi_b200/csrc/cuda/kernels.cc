@@ -85,9 +85,9 @@ extern const std::string kSrc_softmax_transposed_tma;
 
 
 size_t softmax_two_pass_scratch_bytes(size_t lines, size_t len);
-void softmax_two_pass_launch(const float* in, const float* bias, float* out, size_t lines, size_t len, size_t ld, void* scratch, cudaStream_t stream, int sm_count, int* status);
+void softmax_two_pass_launch(const float* in, const float* bias, float* out, size_t lines, size_t len, size_t ld, void* scratch, cudaStream_t stream);
 
-bool build_softmax_two_pass(const Fused& f, size_t axis, int sm_count, Launch* out, size_t* scratch_bytes) {
+bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* scratch_bytes) {
   if (std::getenv("KURUMI_SMT_NO_TWO_PASS")) return false;
   if (f.dtype() != DType::F32 || f.shape.size() != 2 || axis != 1) return false;
   const int64_t lines = static_cast<int64_t>(f.shape[0]), len = static_cast<int64_t>(f.shape[1]);
@@ -124,10 +124,9 @@ bool build_softmax_two_pass(const Fused& f, size_t axis, int sm_count, Launch* o
   out->args.push_back(bi);
   Arg o; o.kind = Arg::SlotPtr; o.slot = -3; out->args.push_back(o);
   Arg sc; sc.kind = Arg::SlotPtr; sc.slot = -1; out->args.push_back(sc);
-  Arg st; st.kind = Arg::Status; out->args.push_back(st);
   out->host_launch = [=](const std::vector<void*>& p, cudaStream_t stream) {
     softmax_two_pass_launch(static_cast<const float*>(p[0]), has_bias ? static_cast<const float*>(p[1]) : nullptr, static_cast<float*>(p[2]), static_cast<size_t>(lines),
-                            static_cast<size_t>(len), ld, p[3], stream, sm_count, static_cast<int*>(p[4]));
+                            static_cast<size_t>(len), ld, p[3], stream);
   };
   return true;
 }

@@ -23,7 +23,7 @@ bool build_softmax_panels(const KernelLoader& load, const Fused& f, size_t axis,
 // plain case: one f32 buffer read transposed, optionally plus a bias that broadcasts along the lines.
 // On success `out->args` is {input, bias (or input again when absent), output, scratch} with the
 // scratch slot symbolic (-1) and `*scratch_bytes` set; the caller creates that slot.
-bool build_softmax_two_pass(const Fused& f, size_t axis, int sm_count, Launch* out, size_t* scratch_bytes);
+bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* scratch_bytes);
 
 // Fused causal / full attention with online softmax. Slots are symbolic: -1 q, -2 k, -3 v, -4 out.
 bool attention_supported(DType dt, const Shape& shape);

@@ -282,7 +282,7 @@ Fused Scheduler::softmax(OpKind k, const Fused& f0, size_t axis, float eps) {
       L.zero_bytes = 16384;
       L.algo_bytes = leaf_bytes(f) + static_cast<double>(prog_.slots[static_cast<size_t>(slot)].bytes);
       prog_.launches.push_back(std::move(L));
-    } else if (k == OpKind::Softmax && (L = Launch(), leaf_args.clear(), build_softmax_two_pass(f, axis, sm_, &L, &scratch))) {
+    } else if (k == OpKind::Softmax && (L = Launch(), leaf_args.clear(), build_softmax_two_pass(f, axis, &L, &scratch))) {
       const int sslot = new_slot(Slot::Temp, DType::U8, {scratch});
       for (auto& a : L.args) { if (a.slot == -3) a.slot = slot; else if (a.slot == -1) a.slot = sslot; }
       L.algo_bytes = leaf_bytes(f) + static_cast<double>(prog_.slots[static_cast<size_t>(slot)].bytes);
