@@ -28,6 +28,16 @@ sys.path.insert(0, ROOT)
 
 from kurumi_b200 import api, build, configs  # noqa: E402
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each workload's dominant kernel,
+# from one ncu capture per kernel at the full workload size; the captures are summarised under profiles/.
+NCU_TRAFFIC = {
+    ("c1_fused_reduce", "reduce_rows"): 137.8e6,
+    ("c2_transposed_softmax", "softmax_panels_tma"): 535.7e6,
+    ("c3_gemm_bias_gelu", "gemm_tc"): 1094e6,
+    ("c4_causal_attention", "attention_tc"): 1057e6,
+    ("c5_fp8_weight_gemm", "gemm_tc_f8"): 2958e6,
+}
+
 WORKLOADS = {
     # name: (builder, full-size args, metric kind)
     "c1_fused_reduce": (configs.fused_reduce, dict(rows=4096, cols=4096), "hbm"),
@@ -265,15 +275,16 @@ def main():
         top = max(prof.items(), key=lambda kv: kv[1]["ms"])
         fam, p = top
         avg_s = p["ms"] / 1e3 / p["launches"]
+        traffic = NCU_TRAFFIC.get((args.workload, fam)) if args.scale == 1.0 else None
         if kind == "hbm":
             ach = (p["algo_bytes"] / p["launches"]) / avg_s / 1e9
             peak = peaks["hbm_gbs"]
-            roofline = {"bound": "hbm", "kernel": fam, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+            roofline = {"bound": "hbm", "kernel": fam, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
                         "avg_launch_us": avg_s * 1e6, "peak_source": peaks["source"], "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
         else:
             ach = (p["flops"] / p["launches"]) / avg_s / 1e12
             peak = peaks["bf16_tflops"]
-            roofline = {"bound": "tensor", "kernel": fam, "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+            roofline = {"bound": "tensor", "kernel": fam, "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": traffic,
                         "avg_launch_us": avg_s * 1e6, "peak_source": peaks["source"] + " (bf16 burst)", "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
 
     # end to end through the C ABI with host buffers: pinned host inputs -> device, evaluate, result -> pinned host

@@ -91,7 +91,8 @@ bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* sc
   if (std::getenv("KURUMI_SMT_NO_TWO_PASS")) return false;
   if (f.dtype() != DType::F32 || f.shape.size() != 2 || axis != 1) return false;
   const int64_t lines = static_cast<int64_t>(f.shape[0]), len = static_cast<int64_t>(f.shape[1]);
-  if (std::getenv("KURUMI_SMT_CLUSTER") && len >= 2048) return false;   // prefer the single-pass cluster kernel
+  // lines of 2048 positions and more go to the single-pass cluster kernel, which measured faster there
+  if (len >= 2048 && !std::getenv("KURUMI_SMT_TWO_PASS")) return false;
   if (lines < 64 || len < 256 || lines >= (int64_t(1) << 31) || len >= (int64_t(1) << 31)) return false;
   auto is_big = [&](const Leaf& l) {
     return l.kind == LeafKind::Buffer && l.dtype == DType::F32 && l.view.guards.empty() && l.view.stride[0] == 1 && l.view.stride[1] >= lines && l.view.base >= 0;
