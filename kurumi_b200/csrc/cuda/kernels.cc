@@ -14,6 +14,7 @@ std::string defines(std::initializer_list<std::pair<const char*, int64_t>> kv) {
 }  // namespace
 
 extern const std::string kSrc_gemm_tc;
+extern const std::string kSrc_gemm_tc2;
 
 static std::string lower(std::string s) { for (auto& c : s) c = static_cast<char>(std::tolower(c)); return s; }
 
@@ -35,22 +36,25 @@ bool build_gemm_tc(const KernelLoader& load, const GemmDesc& d, const Fused* epi
   int a_mn = 0, b_mn = 0;
   if (!major(d.a_ms, d.a_ks, d.m, d.a_base, d.a_bs, &a_mn) || !major(d.b_ns, d.b_ks, d.n, d.b_base, d.b_bs, &b_mn)) return false;
   const int64_t bm = 128, bn = d.n > 128 ? 256 : d.n > 64 ? 128 : 64, bkb = 128, bk = bkb / es;
-  const int64_t stage = (bm + bn) * bkb;
+  // wide outputs with at least two row blocks run on SM pairs (cta_group::2): 256 x 256 tiles, half of B per CTA
+  const bool pair = bn == 256 && d.m > 128 && sm_count >= 2 && !std::getenv("KURUMI_NO_TC2");
+  const int64_t stage = (bm + (pair ? bn / 2 : bn)) * bkb;
   const int64_t stages = std::min<int64_t>(8, (200 * 1024) / stage);
-  const int64_t tiles_m = (d.m + bm - 1) / bm, tiles_n = (d.n + bn - 1) / bn;
+  const int64_t tiles_m = pair ? (d.m + 255) / 256 : (d.m + bm - 1) / bm, tiles_n = (d.n + bn - 1) / bn;
   if (d.batch * tiles_m * tiles_n >= (int64_t(1) << 31)) return false;
   // instruction descriptor: f32 accumulate, operand formats, major-ness, N >> 3, M >> 4
   const uint32_t fmt = f8 ? 0u : (d.dtype == DType::BF16 ? 1u : 0u);
   const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
-                         (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(bm >> 4) << 24);
+                         (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>((pair ? 256 : bm) >> 4) << 24);
   std::string src = device_prelude() + emit_epilogue_fn(epi, d.dtype, epi_leaf_args) +
                     defines({{"M", d.m}, {"N", d.n}, {"K", d.k}, {"BATCH", d.batch}, {"BM", bm}, {"BN", bn}, {"BKB", bkb}, {"ESIZE", es}, {"STAGES", stages},
                              {"A_MN", a_mn}, {"B_MN", b_mn}, {"IDESC", static_cast<int64_t>(idesc)}, {"TILES_M", tiles_m}, {"TILES_N", tiles_n}}) +
-                    "#define KU_ROUND(x) ku_rnd_" + lower(dtype_name(d.dtype)) + "(x)\n" + kSrc_gemm_tc;
+                    "#define KU_ROUND(x) ku_rnd_" + lower(dtype_name(d.dtype)) + "(x)\n" + (pair ? kSrc_gemm_tc2 : kSrc_gemm_tc);
   out->name = f8 ? "gemm_tc_f8" : "gemm_tc";
-  out->kernel = load(src, "ku_gemm_tc", true);
-  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(d.batch * tiles_m * tiles_n, sm_count));
-  out->block[0] = 192;
+  out->kernel = load(src, pair ? "ku_gemm_tc2" : "ku_gemm_tc", true);
+  out->grid[0] = static_cast<unsigned>(pair ? 2 * std::min<int64_t>(d.batch * tiles_m * tiles_n, sm_count / 2) : std::min<int64_t>(d.batch * tiles_m * tiles_n, sm_count));
+  if (pair) { out->cluster[0] = 2; out->persistent_clusters = -1; }   // cap at the co-resident pair count on first launch
+  out->block[0] = 320;   // TMA warp, MMA warp, 8 epilogue warps
   out->smem = static_cast<unsigned>(std::max<int64_t>(stages * stage + 1024, 120 * 1024));  // > half an SM: one CTA per SM owns all of tensor memory
   auto tmap = [&](int slot, int mn, int64_t rows, int64_t row_stride, int64_t k_stride, int64_t base, int64_t bs, int64_t tile_rows) {
     Arg a;
@@ -75,7 +79,7 @@ bool build_gemm_tc(const KernelLoader& load, const GemmDesc& d, const Fused* epi
     return a;
   };
   out->args.push_back(tmap(-1, a_mn, d.m, d.a_ms, d.a_ks, d.a_base, d.a_bs, bm));
-  out->args.push_back(tmap(-2, b_mn, d.n, d.b_ns, d.b_ks, d.b_base, d.b_bs, bn));
+  out->args.push_back(tmap(-2, b_mn, d.n, d.b_ns, d.b_ks, d.b_base, d.b_bs, pair ? bn / 2 : bn));
   Arg c; c.kind = Arg::SlotPtr; c.slot = -3; out->args.push_back(c);
   Arg st; st.kind = Arg::Status; out->args.push_back(st);
   return true;

@@ -6,7 +6,7 @@
 // tiles, warp-specialised:
 //   warp 0      one thread issues the TMA loads
 //   warp 1      allocates tensor memory; one thread issues the MMAs and commits them to mbarriers
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes its id
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes its id
 //               selects), round it to the contraction's dtype, run the fused pointwise chain that
 //               the graph put behind the contraction, store
 // Tensor memory holds two accumulators (2 x BN of the 512 columns), so the epilogue of tile i overlaps
@@ -30,8 +30,12 @@
 #define STAGE_BYTES (A_STAGE_BYTES + B_STAGE_BYTES)
 #define KBLOCKS ((K + BK - 1) / BK)
 #define SPIN_LIMIT (1u << 24)
+#define NEPI 8                           // epilogue warps: two per tensor-memory lane quarter, each taking half of the columns
 
 struct alignas(64) KuTmap { unsigned long long opaque[16]; };
+template <int BYTES> struct KuBits { typedef unsigned char type; };
+template <> struct KuBits<2> { typedef unsigned short type; };
+template <> struct KuBits<4> { typedef unsigned type; };
 
 __device__ __forceinline__ unsigned ku_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ku_mbar_init(unsigned a, unsigned n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(n)); }
@@ -76,8 +80,8 @@ __device__ __forceinline__ void ku_mma(unsigned d_tmem, unsigned long long adesc
 __device__ __forceinline__ void ku_mma_commit(unsigned mbar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
 }
-__device__ __forceinline__ void ku_tmem_ld32(unsigned taddr, float* v) {
-  unsigned* r = (unsigned*)v;
+__device__ __forceinline__ void ku_tmem_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
       "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
@@ -86,6 +90,8 @@ __device__ __forceinline__ void ku_tmem_ld32(unsigned taddr, float* v) {
         "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
 }
 
 // tile index -> (batch, row block, column block): groups of 16 row blocks, column-major inside a group
@@ -99,7 +105,7 @@ __device__ __forceinline__ void ku_tile_coords(int t, int& b, int& mb, int& nb) 
   nb = in_group / rows;
 }
 
-extern "C" __global__ void __launch_bounds__(192, 1)
+extern "C" __global__ void __launch_bounds__(64 + 32 * NEPI, 1)
 ku_gemm_tc(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTmap tmap_b, void* __restrict__ Cp, int* __restrict__ status KU_EPI_PARAMS) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], tmem_full[2], tmem_empty[2];
@@ -111,7 +117,7 @@ ku_gemm_tc(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTmap
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { ku_mbar_init(ku_smem(&full_bar[s]), 1); ku_mbar_init(ku_smem(&empty_bar[s]), 1); }
-    for (int a = 0; a < 2; ++a) { ku_mbar_init(ku_smem(&tmem_full[a]), 1); ku_mbar_init(ku_smem(&tmem_empty[a]), 128); }
+    for (int a = 0; a < 2; ++a) { ku_mbar_init(ku_smem(&tmem_full[a]), 1); ku_mbar_init(ku_smem(&tmem_empty[a]), 32 * NEPI); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // 512 columns: two BN-wide f32 accumulators
@@ -184,6 +190,7 @@ ku_gemm_tc(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTmap
     }
   } else {  // ---- epilogue warps ----
     const int q = warp & 3;  // the TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;   // which half of the tile's columns this warp handles
     int local = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
       int b, mb, nb;
@@ -195,17 +202,26 @@ ku_gemm_tc(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTmap
       const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + acc * BN;
       ku_out_t* crow = (ku_out_t*)Cp + ((i64)b * M + m) * N;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         float v[32];
         ku_tmem_ld32(taddr + c * 32, v);
         const i64 n0 = (i64)nb * BN + c * 32;
         if (m < M && n0 < N) {
           if ((N % (16 / (int)sizeof(ku_out_t))) == 0 && n0 + 32 <= N) {
-            __align__(16) ku_out_t o[32];
+            // 16 bytes of outputs at a time, packed in registers
+            constexpr int PER = 16 / (int)sizeof(ku_out_t);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = ku_epilogue(KU_ROUND(v[j]), (i64)b, m, n0 + j KU_EPI_ARGS);
+            for (int w = 0; w < 32 / PER; ++w) {
+              unsigned pk[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-            for (int w = 0; w < (int)(32 * sizeof(ku_out_t) / 16); ++w) ((uint4*)(crow + n0))[w] = ((const uint4*)o)[w];
+              for (int e = 0; e < PER; ++e) {
+                const ku_out_t o = ku_epilogue(KU_ROUND(v[w * PER + e]), (i64)b, m, n0 + w * PER + e KU_EPI_ARGS);
+                unsigned bits;
+                if (sizeof(ku_out_t) == 4) bits = __float_as_uint(*(const float*)&o); else bits = (unsigned)(*(const typename KuBits<sizeof(ku_out_t)>::type*)&o);
+                pk[e * (int)sizeof(ku_out_t) / 4] |= bits << (8 * ((e * (int)sizeof(ku_out_t)) & 3));
+              }
+              ((uint4*)(crow + n0))[w] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
           } else {
             for (int j = 0; j < 32 && n0 + j < N; ++j) crow[n0 + j] = ku_epilogue(KU_ROUND(v[j]), (i64)b, m, n0 + j KU_EPI_ARGS);
           }
