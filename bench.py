@@ -324,6 +324,36 @@ def main():
         e2e = {"value": ev, "unit": unit, "h2d_bytes_per_step": int(sum(hb.numel() for hb, _, _ in host_in.values())), "d2h_bytes_per_step": int(out_bytes),
                "ms_per_step": dt * 1e3, "timing": "host wall clock around upload + eval + download (download waits for the device)", "steps": n_e2e}
 
+    # N > 1: gathering the ranks' output shards into one tensor on every GPU is NOT on the data path that
+    # `value` times (shards stay device-resident); its cost is reported beside it
+    assembly = None
+    if world > 1:
+        from cuda.bindings import runtime as cudart
+        o = step()
+        shard = torch.empty(o.nbytes, dtype=torch.uint8, device=f"cuda:{local}")
+        gpu.sync()
+        (err,) = cudart.cudaMemcpy(shard.data_ptr(), o.ptr, o.nbytes, cudart.cudaMemcpyKind.cudaMemcpyDeviceToDevice)
+        if int(err) != 0:
+            raise RuntimeError(f"cudaMemcpy of the output shard failed: {err}")
+        o.free()
+        whole = torch.empty(world * shard.numel(), dtype=torch.uint8, device=f"cuda:{local}")
+        for _ in range(2):
+            dist.all_gather_into_tensor(whole, shard)
+        torch.cuda.synchronize()
+        dist.barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        a0.record()
+        for _ in range(reps):
+            dist.all_gather_into_tensor(whole, shard)
+        a1.record()
+        torch.cuda.synchronize()
+        at = torch.tensor([a0.elapsed_time(a1) / reps], device=f"cuda:{local}")
+        dist.all_reduce(at, op=dist.ReduceOp.MAX)
+        assembly = {"ms": float(at.item()), "bytes_per_rank": int(shard.numel()), "collective": "nccl all_gather of the output shards (torch.distributed), CUDA events, max over ranks",
+                    "in_value": False}
+        del whole, shard
+
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu_base = cpu_baseline(name, builder, kw)
@@ -334,7 +364,7 @@ def main():
                 "data": "synthetic (seeded threefry2x32 / Box-Muller, generated on device)",
                 "config": {"workload": name, **kw, "l2": f"steps rotate through {n_sets} copies of the inputs ({in_bytes * n_sets / 1e6:.0f} MB in all, L2 is 126 MB): no step finds its inputs cached",
                            "sharding": "each rank evaluates its own shard of an N-times larger batch (same shapes); no collective on the data path"},
-                "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu_base,
+                "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu_base, "assembly": assembly,
                 "kernel_times": {k: {"launches": v["launches"], "avg_us": v["ms"] * 1e3 / v["launches"]} for k, v in prof.items()}}
         print(json.dumps(line), flush=True)
     if world > 1:

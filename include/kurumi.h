@@ -37,6 +37,7 @@ typedef struct KuGraph KuGraph;     /* kurumi.h:40-45 */
 typedef struct KuTensor KuTensor;
 typedef struct KuFeeds KuFeeds;
 typedef struct KuBackend KuBackend;
+typedef struct KuRunnable KuRunnable; /* a rebuilt graph blob with its entries */
 typedef uint32_t KuNode;            /* kurumi.h:47 */
 
 const char *ku_last_error(void);    /* kurumi.h:51 */
@@ -146,6 +147,37 @@ size_t ku_dump(const KuGraph *g, KuNode root, uint8_t *out, size_t cap);
 size_t ku_node_rank(const KuGraph *g, KuNode node);          /* SIZE_MAX on error */
 void ku_node_shape(const KuGraph *g, KuNode node, size_t *out);
 uint32_t ku_node_dtype(const KuGraph *g, KuNode node);       /* KU_ERR on error */
+
+/* runnable-graph blobs (KGPH v2, the graph section of a `.hodu` artifact), kurumi.h:407-455: serialize a
+ * graph with its output nodes and input bindings (node, role 0 = weight / 1 = runtime feed, name), and
+ * rebuild it elsewhere. Size-then-write: cap = 0 with out = NULL returns the length; 0 on error. Blobs
+ * whose nodes are outside this library's primitive set are refused by ku_graph_deserialize (NULL). */
+size_t ku_graph_serialize(const KuGraph *g, const KuNode *outputs, size_t n_out, const KuNode *in_nodes,
+                          const uint8_t *in_roles, const char *const *in_names, size_t n_in, uint8_t *out, size_t cap);
+size_t ku_graph_serialize_reachable(const KuGraph *g, const KuNode *outputs, size_t n_out, const KuNode *in_nodes,
+                                    const uint8_t *in_roles, const char *const *in_names, size_t n_in, uint8_t *out,
+                                    size_t cap);
+size_t ku_graph_serialize_multi(const KuGraph *g, size_t n_entries, const char *const *names,
+                                const uint32_t *out_counts, const KuNode *outputs, const uint32_t *in_counts,
+                                const KuNode *in_nodes, const uint8_t *in_roles, const char *const *in_names,
+                                uint8_t *out, size_t cap);
+KuRunnable *ku_graph_deserialize(const uint8_t *bytes, size_t len); /* NULL on a malformed or entry-less blob */
+KuGraph *ku_runnable_take_graph(KuRunnable *h);                     /* call once; free with ku_graph_free */
+size_t ku_runnable_output_count(const KuRunnable *h);               /* the non-entry accessors expose entry 0 */
+KuNode ku_runnable_output(const KuRunnable *h, size_t i);
+size_t ku_runnable_input_count(const KuRunnable *h);
+KuNode ku_runnable_input_node(const KuRunnable *h, size_t i);
+uint32_t ku_runnable_input_role(const KuRunnable *h, size_t i);
+size_t ku_runnable_input_name(const KuRunnable *h, size_t i, uint8_t *out, size_t cap); /* UTF-8, no NUL; returns the full length */
+size_t ku_runnable_entry_count(const KuRunnable *h);
+size_t ku_runnable_entry_name(const KuRunnable *h, size_t i, uint8_t *out, size_t cap);
+size_t ku_runnable_entry_output_count(const KuRunnable *h, size_t i);
+KuNode ku_runnable_entry_output(const KuRunnable *h, size_t i, size_t j);
+size_t ku_runnable_entry_input_count(const KuRunnable *h, size_t i);
+KuNode ku_runnable_entry_input_node(const KuRunnable *h, size_t i, size_t j);
+uint32_t ku_runnable_entry_input_role(const KuRunnable *h, size_t i, size_t j);
+size_t ku_runnable_entry_input_name(const KuRunnable *h, size_t i, size_t j, uint8_t *out, size_t cap);
+void ku_runnable_free(KuRunnable *h);
 
 /* feeds, kurumi.h:461-463 */
 KuFeeds *ku_feeds_new(void);

@@ -143,14 +143,51 @@ class Feeds:
 class Graph:
     """Graph builder: every method returns a node id or raises Error with ku_last_error()."""
 
-    def __init__(self, lib: Library):
-        self.lib, self.h = lib, C.c_void_p(lib.lib.ku_graph_new())
+    def __init__(self, lib: Library, handle=None):
+        self.lib, self.h = lib, C.c_void_p(handle if handle is not None else lib.lib.ku_graph_new())
 
     def __del__(self):
         try:
             self.lib.lib.ku_graph_free(self.h)
         except Exception:
             pass
+
+    def serialize(self, outputs: Sequence[int], inputs: Sequence[tuple] = (), reachable: bool = False) -> bytes:
+        """The graph as a KGPH v2 blob; `inputs` are (node, role, name) with role 0 = weight, 1 = runtime feed."""
+        fn = self.lib.lib.ku_graph_serialize_reachable if reachable else self.lib.lib.ku_graph_serialize
+        fn.restype = C.c_size_t
+        outs = (C.c_uint32 * max(len(outputs), 1))(*outputs)
+        nodes = (C.c_uint32 * max(len(inputs), 1))(*[i[0] for i in inputs])
+        roles = (C.c_uint8 * max(len(inputs), 1))(*[i[1] for i in inputs])
+        names = (C.c_char_p * max(len(inputs), 1))(*[i[2].encode() for i in inputs])
+        args = (self.h, outs, C.c_size_t(len(outputs)), nodes, roles, names, C.c_size_t(len(inputs)))
+        n = fn(*args, None, C.c_size_t(0))
+        if n == 0:
+            raise Error(self.lib.last_error())
+        buf = (C.c_uint8 * n)()
+        fn(*args, buf, C.c_size_t(n))
+        return bytes(buf)
+
+    def serialize_multi(self, entries: Sequence[tuple]) -> bytes:
+        """Several named entries (name, outputs, inputs) over one arena, pruned to the union of their cones."""
+        fn = self.lib.lib.ku_graph_serialize_multi
+        fn.restype = C.c_size_t
+        names = (C.c_char_p * len(entries))(*[e[0].encode() for e in entries])
+        outs = [o for e in entries for o in e[1]]
+        ins = [i for e in entries for i in e[2]]
+        oc = (C.c_uint32 * len(entries))(*[len(e[1]) for e in entries])
+        ic = (C.c_uint32 * len(entries))(*[len(e[2]) for e in entries])
+        oa = (C.c_uint32 * max(len(outs), 1))(*outs)
+        na = (C.c_uint32 * max(len(ins), 1))(*[i[0] for i in ins])
+        ra = (C.c_uint8 * max(len(ins), 1))(*[i[1] for i in ins])
+        sa = (C.c_char_p * max(len(ins), 1))(*[i[2].encode() for i in ins])
+        args = (self.h, C.c_size_t(len(entries)), names, oc, oa, ic, na, ra, sa)
+        n = fn(*args, None, C.c_size_t(0))
+        if n == 0:
+            raise Error(self.lib.last_error())
+        buf = (C.c_uint8 * n)()
+        fn(*args, buf, C.c_size_t(n))
+        return bytes(buf)
 
     def _n(self, name: str, *args) -> int:
         r = self.lib.node_fn(name)(self.h, *args)
@@ -497,6 +534,42 @@ def compile_check(lib: Library, g: Graph, nodes) -> list:
     if n == C.c_size_t(-1).value:
         raise Error(lib.last_error())
     return bytes(buf[:n]).decode().split()
+
+
+def deserialize(lib: Library, blob: bytes):
+    """Rebuild a KGPH v2 blob: (Graph, [(entry name, outputs, [(node, role, name), ...]), ...]). Raises Error when malformed."""
+    L = lib.lib
+    L.ku_graph_deserialize.restype = C.c_void_p
+    L.ku_runnable_take_graph.restype = C.c_void_p
+    for name in ("ku_runnable_entry_count", "ku_runnable_entry_name", "ku_runnable_entry_output_count", "ku_runnable_entry_input_count",
+                 "ku_runnable_entry_input_name"):
+        getattr(L, name).restype = C.c_size_t
+    for name in ("ku_runnable_entry_output", "ku_runnable_entry_input_node", "ku_runnable_entry_input_role"):
+        getattr(L, name).restype = C.c_uint32
+    buf = (C.c_uint8 * max(len(blob), 1)).from_buffer_copy(blob if blob else b"\0")
+    h = L.ku_graph_deserialize(buf, C.c_size_t(len(blob)))
+    if not h:
+        raise Error(lib.last_error())
+    h = C.c_void_p(h)
+    try:
+        def text(fn, *idx):
+            n = fn(h, *idx, None, C.c_size_t(0))
+            b = (C.c_uint8 * max(n, 1))()
+            fn(h, *idx, b, C.c_size_t(n))
+            return bytes(b[:n]).decode()
+        entries = []
+        for e in range(L.ku_runnable_entry_count(h)):
+            ce = C.c_size_t(e)
+            outs = [L.ku_runnable_entry_output(h, ce, C.c_size_t(j)) for j in range(L.ku_runnable_entry_output_count(h, ce))]
+            ins = [(L.ku_runnable_entry_input_node(h, ce, C.c_size_t(j)), L.ku_runnable_entry_input_role(h, ce, C.c_size_t(j)),
+                    text(L.ku_runnable_entry_input_name, ce, C.c_size_t(j))) for j in range(L.ku_runnable_entry_input_count(h, ce))]
+            entries.append((text(L.ku_runnable_entry_name, ce), outs, ins))
+        g = L.ku_runnable_take_graph(h)
+        if not g:
+            raise Error(lib.last_error())
+        return Graph(lib, g), entries
+    finally:
+        L.ku_runnable_free(h)
 
 
 def load_cuda_library() -> Library:

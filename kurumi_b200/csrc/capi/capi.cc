@@ -226,6 +226,107 @@ uint32_t ku_node_dtype(const KuGraph* g, KuNode node) {
   return guard<uint32_t>(KU_ERR, [&]() { return static_cast<uint32_t>(g->g.dtype(node)); });
 }
 
+// ---- runnable-graph blobs (kurumi/src/capi, kurumi.h:407-455) -----------------------------------
+namespace {
+std::vector<ku::InputBinding> bindings(const KuNode* nodes, const uint8_t* roles, const char* const* names, size_t n) {
+  if (n && (!nodes || !roles || !names)) throw ku::Error::shape("ku_graph_serialize", "null input binding arrays");
+  std::vector<ku::InputBinding> v(n);
+  for (size_t i = 0; i < n; ++i) {
+    if (!names[i]) throw ku::Error::shape("ku_graph_serialize", "null input name");
+    v[i].node = nodes[i]; v[i].role = roles[i]; v[i].name = names[i];
+  }
+  return v;
+}
+size_t write_out(const std::vector<uint8_t>& blob, uint8_t* out, size_t cap) {   // size-then-write
+  if (out && cap) std::memcpy(out, blob.data(), std::min(cap, blob.size()));
+  return blob.size();
+}
+size_t write_name(const std::string& s, uint8_t* out, size_t cap) {
+  if (out && cap) std::memcpy(out, s.data(), std::min(cap, s.size()));
+  return s.size();
+}
+const ku::Entry* entry_of(const KuRunnable* h, size_t i) { return (h && i < h->r.entries.size()) ? &h->r.entries[i] : nullptr; }
+}  // namespace
+
+size_t ku_graph_serialize(const KuGraph* g, const KuNode* outputs, size_t n_out, const KuNode* in_nodes, const uint8_t* in_roles, const char* const* in_names,
+                          size_t n_in, uint8_t* out, size_t cap) {
+  if (!g || (n_out && !outputs)) { set_err("ku_graph_serialize: null graph/outputs"); return 0; }
+  return guard<size_t>(0, [&]() {
+    return write_out(ku::serialize_graph(g->g, std::vector<NodeId>(outputs, outputs + n_out), bindings(in_nodes, in_roles, in_names, n_in)), out, cap);
+  });
+}
+size_t ku_graph_serialize_reachable(const KuGraph* g, const KuNode* outputs, size_t n_out, const KuNode* in_nodes, const uint8_t* in_roles,
+                                    const char* const* in_names, size_t n_in, uint8_t* out, size_t cap) {
+  if (!g || (n_out && !outputs)) { set_err("ku_graph_serialize_reachable: null graph/outputs"); return 0; }
+  return guard<size_t>(0, [&]() {
+    return write_out(ku::serialize_reachable(g->g, std::vector<NodeId>(outputs, outputs + n_out), bindings(in_nodes, in_roles, in_names, n_in)), out, cap);
+  });
+}
+size_t ku_graph_serialize_multi(const KuGraph* g, size_t n_entries, const char* const* names, const uint32_t* out_counts, const KuNode* outputs,
+                                const uint32_t* in_counts, const KuNode* in_nodes, const uint8_t* in_roles, const char* const* in_names, uint8_t* out, size_t cap) {
+  if (!g || (n_entries && (!names || !out_counts || !in_counts))) { set_err("ku_graph_serialize_multi: null graph/entry arrays"); return 0; }
+  return guard<size_t>(0, [&]() {
+    std::vector<ku::Entry> entries(n_entries);
+    size_t o = 0, i = 0;
+    for (size_t e = 0; e < n_entries; ++e) {
+      if (!names[e]) throw ku::Error::shape("ku_graph_serialize_multi", "null entry name");
+      if (out_counts[e] && !outputs) throw ku::Error::shape("ku_graph_serialize_multi", "null outputs");
+      entries[e].name = names[e];
+      entries[e].outputs.assign(outputs + o, outputs + o + out_counts[e]);
+      entries[e].inputs = bindings(in_counts[e] ? in_nodes + i : nullptr, in_counts[e] ? in_roles + i : nullptr, in_counts[e] ? in_names + i : nullptr, in_counts[e]);
+      o += out_counts[e];
+      i += in_counts[e];
+    }
+    return write_out(ku::serialize_multi(g->g, entries), out, cap);
+  });
+}
+KuRunnable* ku_graph_deserialize(const uint8_t* bytes, size_t len) {
+  if (!bytes && len) { set_err("ku_graph_deserialize: null bytes"); return nullptr; }
+  return guard<KuRunnable*>(nullptr, [&]() { return new KuRunnable{ku::deserialize_graph(bytes, len)}; });
+}
+KuGraph* ku_runnable_take_graph(KuRunnable* h) {
+  if (!h || !h->r.graph) { set_err("ku_runnable_take_graph: null handle or graph already taken"); return nullptr; }
+  return guard<KuGraph*>(nullptr, [&]() {
+    KuGraph* g = new KuGraph{std::move(*h->r.graph)};
+    h->r.graph.reset();
+    return g;
+  });
+}
+size_t ku_runnable_output_count(const KuRunnable* h) { return ku_runnable_entry_output_count(h, 0); }
+KuNode ku_runnable_output(const KuRunnable* h, size_t i) { return ku_runnable_entry_output(h, 0, i); }
+size_t ku_runnable_input_count(const KuRunnable* h) { return ku_runnable_entry_input_count(h, 0); }
+KuNode ku_runnable_input_node(const KuRunnable* h, size_t i) { return ku_runnable_entry_input_node(h, 0, i); }
+uint32_t ku_runnable_input_role(const KuRunnable* h, size_t i) { return ku_runnable_entry_input_role(h, 0, i); }
+size_t ku_runnable_input_name(const KuRunnable* h, size_t i, uint8_t* out, size_t cap) { return ku_runnable_entry_input_name(h, 0, i, out, cap); }
+size_t ku_runnable_entry_count(const KuRunnable* h) { return h ? h->r.entries.size() : 0; }
+size_t ku_runnable_entry_name(const KuRunnable* h, size_t i, uint8_t* out, size_t cap) {
+  const ku::Entry* e = entry_of(h, i);
+  return e ? write_name(e->name, out, cap) : 0;
+}
+size_t ku_runnable_entry_output_count(const KuRunnable* h, size_t i) { const ku::Entry* e = entry_of(h, i); return e ? e->outputs.size() : 0; }
+KuNode ku_runnable_entry_output(const KuRunnable* h, size_t i, size_t j) {
+  const ku::Entry* e = entry_of(h, i);
+  if (!e || j >= e->outputs.size()) { set_err("ku_runnable_entry_output: index out of range"); return KU_ERR; }
+  return e->outputs[j];
+}
+size_t ku_runnable_entry_input_count(const KuRunnable* h, size_t i) { const ku::Entry* e = entry_of(h, i); return e ? e->inputs.size() : 0; }
+KuNode ku_runnable_entry_input_node(const KuRunnable* h, size_t i, size_t j) {
+  const ku::Entry* e = entry_of(h, i);
+  if (!e || j >= e->inputs.size()) { set_err("ku_runnable_entry_input_node: index out of range"); return KU_ERR; }
+  return e->inputs[j].node;
+}
+uint32_t ku_runnable_entry_input_role(const KuRunnable* h, size_t i, size_t j) {
+  const ku::Entry* e = entry_of(h, i);
+  if (!e || j >= e->inputs.size()) { set_err("ku_runnable_entry_input_role: index out of range"); return KU_ERR; }
+  return e->inputs[j].role;
+}
+size_t ku_runnable_entry_input_name(const KuRunnable* h, size_t i, size_t j, uint8_t* out, size_t cap) {
+  const ku::Entry* e = entry_of(h, i);
+  if (!e || j >= e->inputs.size()) return 0;
+  return write_name(e->inputs[j].name, out, cap);
+}
+void ku_runnable_free(KuRunnable* h) { delete h; }
+
 // ---- feeds ------------------------------------------------------------------------------------
 KuFeeds* ku_feeds_new(void) { return new KuFeeds(); }
 void ku_feeds_free(KuFeeds* f) { delete f; }

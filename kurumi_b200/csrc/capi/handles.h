@@ -6,11 +6,13 @@
 #include <string>
 
 #include "../core/graph.h"
+#include "../core/serialize.h"
 
 struct KuGraph { ku::Graph g; };
 struct KuTensor { ku::TensorPtr t; };
 struct KuFeeds { ku::Feeds f; };
 struct KuBackend { std::unique_ptr<ku::Backend> b; };
+struct KuRunnable { ku::Runnable r; };
 
 namespace ku {
 void set_err(const std::string& msg);
