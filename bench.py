@@ -139,7 +139,7 @@ def reference_arm(args, name, builder, kw):
             "config": {"workload": name, **kw, "sample": what},
             "cpu_baseline": {"value": value, "unit": unit, "cores": 1, "kind": "port", "sample": what},
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def cpu_sample(name, kw):
@@ -166,7 +166,25 @@ def dtype_of(name):
     return {"c1_fused_reduce": "f32", "c2_transposed_softmax": "f32", "c3_gemm_bias_gelu": "bf16", "c4_causal_attention": "bf16", "c5_fp8_weight_gemm": "f8e4m3"}[name]
 
 
+_RESULT_FD = None
+
+
+def emit(line: dict):
+    """The one JSON line goes to the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    # libraries (NCCL's version banner, for one) write to file descriptor 1: keep it for the result line alone
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -193,6 +211,7 @@ def main():
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the JSON line only
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = api.Library(build.LIB)
     gpu = api.CudaBackend(lib, local)
@@ -366,7 +385,7 @@ def main():
                            "sharding": "each rank evaluates its own shard of an N-times larger batch (same shapes); no collective on the data path"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu_base, "assembly": assembly,
                 "kernel_times": {k: {"launches": v["launches"], "avg_us": v["ms"] * 1e3 / v["launches"]} for k, v in prof.items()}}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
