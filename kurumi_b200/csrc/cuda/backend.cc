@@ -93,6 +93,8 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
       const int fit = rt_.max_active_clusters(L.kernel, cl, L.block[0], L.smem);
       if (fit <= 0) throw Error::backend("kernel " + L.name + " cannot be launched with clusters of " + std::to_string(cl));
       L.persistent_clusters = std::min<int>(fit, static_cast<int>(L.grid[0] / cl));
+      L.persistent_clusters = L.persistent_clusters / static_cast<int>(L.grid_multiple) * static_cast<int>(L.grid_multiple);
+      if (L.persistent_clusters <= 0) throw Error::backend("kernel " + L.name + " needs " + std::to_string(L.grid_multiple) + " co-resident CTAs, the device fits " + std::to_string(fit));
       L.grid[0] = static_cast<unsigned>(L.persistent_clusters) * cl;
     }
     std::vector<void*> vals(L.args.size());
@@ -126,12 +128,12 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
       ev = ev_used_++;
       cuda_check(cudaEventRecord(ev_pool_[ev].first, rt_.stream()), "cudaEventRecord");
     }
-    if (L.zero_slot >= 0) cuda_check(cudaMemsetAsync(ptr[static_cast<size_t>(L.zero_slot)], 0, L.zero_bytes, rt_.stream()), "cudaMemsetAsync(control block)");
+    if (L.zero_slot >= 0) cuda_check(cudaMemsetAsync(ptr[static_cast<size_t>(L.zero_slot)], L.fill_byte, L.zero_bytes, rt_.stream()), "cudaMemsetAsync(control block)");
     if (L.host_launch) {
       L.host_launch(vals, rt_.stream());
       ++rt_.stats.launches;
     } else {
-      rt_.launch(L.kernel, L.grid, L.block, L.cluster, L.smem, argv.data());
+      rt_.launch(L.kernel, L.grid, L.block, L.cluster, L.smem, argv.data(), L.cooperative);
     }
     if (profiling_) {
       cuda_check(cudaEventRecord(ev_pool_[ev].second, rt_.stream()), "cudaEventRecord");

@@ -94,13 +94,16 @@ struct Launch {
   unsigned grid[3] = {1, 1, 1}, block[3] = {1, 1, 1}, cluster[3] = {1, 1, 1};
   unsigned smem = 0;
   int persistent_clusters = 0;  // -1: cap grid[0] at the co-resident cluster count (x cluster size) on first launch; > 0: done
+  unsigned grid_multiple = 1;   // with persistent_clusters: the capped grid is rounded down to a multiple of this (CTA groups)
+  bool cooperative = false;     // launch with the cooperative attribute: all CTAs co-resident, or the launch fails
   bool status_arg = false;      // append the backend's device status word as the last kernel parameter
   // When set, the step is a precompiled (nvcc-built) kernel sequence: the backend resolves the SlotPtr
   // arguments and calls this instead of launching `kernel`.
   std::function<void(const std::vector<void*>& ptrs, cudaStream_t stream)> host_launch;
   std::vector<Arg> args;
-  int zero_slot = -1;       // when >= 0: the first zero_bytes of this slot are cleared on the stream before the launch
+  int zero_slot = -1;       // when >= 0: the first zero_bytes of this slot are set to fill_byte on the stream before the launch
   size_t zero_bytes = 0;
+  int fill_byte = 0;
   double algo_bytes = 0, flops = 0;  // algorithmic traffic / work of this launch
 };
 

@@ -136,6 +136,53 @@ bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* sc
   return true;
 }
 
+extern const std::string kSrc_softmax_groups_tma;
+
+bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args, size_t* scratch_bytes, size_t* zero_bytes) {
+  if (f.dtype() != DType::F32 || std::getenv("KURUMI_SMT_NO_GROUPS")) return false;
+  std::string src_fn;
+  int64_t R = 0, C = 0;
+  bool transposed = false;
+  LineLeaf big;
+  if (!emit_line_source_fn(f, axis, &src_fn, leaf_args, &R, &C, &transposed, &big) || !transposed || big.leaf < 0) return false;
+  auto env = [](const char* name, int64_t dflt) { const char* e = std::getenv(name); return e ? static_cast<int64_t>(std::atoi(e)) : dflt; };
+  const int64_t p = 16, nt = 512, nw = nt / 32;
+  if (sm_count < p || R < 32 * 8 || C < 1024 || R * C < (int64_t(1) << 22) || R >= (int64_t(1) << 30) || C >= (int64_t(1) << 30)) return false;
+  int64_t cj = (C + p - 1) / p;
+  cj = (cj + 4 * nw - 1) / (4 * nw) * (4 * nw);      // every warp gets a multiple of four tile rows
+  int64_t nbuf = std::min<int64_t>(4, std::max<int64_t>(1, env("KURUMI_SMG_NBUF", 1)));
+  while (nbuf > 1 && nbuf * cj * 128 + 1024 > 220 * 1024) --nbuf;
+  if (nbuf * cj * 128 + 1024 > 220 * 1024) return false;   // lines too long for a ring of tiles in shared memory
+  const int64_t boxj = cj % 256 == 0 ? 256 : cj % 128 == 0 ? 128 : 64;
+  const int64_t slabs = (R + 31) / 32;
+  std::string src = device_prelude() + src_fn +
+                    defines({{"R", R}, {"C", C}, {"P", p}, {"CJ", cj}, {"BOXJ", boxj}, {"NBUF", nbuf}, {"NT", nt}, {"NSLABS", slabs}, {"KU_OUT_F32", 1},
+                             {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
+                    kSrc_softmax_groups_tma;
+  out->name = "softmax_groups_tma";
+  out->kernel = load(src, "ku_softmax_groups_tma", false);
+  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(slabs, 4 * sm_count / p) * p);
+  out->block[0] = static_cast<unsigned>(nt);
+  out->smem = static_cast<unsigned>(nbuf * cj * 128 + 1024);   // 1024 bytes of slack: the ring is placed on a 1024-byte boundary
+  out->persistent_clusters = -1;                               // cap the grid at the co-resident CTA count on first launch,
+  out->grid_multiple = static_cast<unsigned>(p);               // in whole groups,
+  out->cooperative = true;                                     // and have the driver hold the launch to it
+  Arg tm;
+  tm.kind = Arg::Tmap;
+  tm.tm.slot = f.leaves[static_cast<size_t>(big.leaf)].slot;
+  tm.tm.byte_offset = big.base * 4;
+  tm.tm.dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  tm.tm.rank = 2;
+  tm.tm.dims[0] = static_cast<uint64_t>(R); tm.tm.dims[1] = static_cast<uint64_t>(C);
+  tm.tm.strides[0] = static_cast<uint64_t>(big.ld) * 4;
+  tm.tm.box[0] = 32; tm.tm.box[1] = static_cast<uint32_t>(boxj);
+  tm.tm.swz = CU_TENSOR_MAP_SWIZZLE_128B;
+  out->args.push_back(tm);
+  *zero_bytes = static_cast<size_t>((slabs * 4 + 255) / 256 * 256);   // the per-slab counters
+  *scratch_bytes = *zero_bytes + static_cast<size_t>(slabs * p * 32 * 8);
+  return true;
+}
+
 extern const std::string kSrc_softmax_panels_tma;
 
 size_t softmax_panels_scratch_bytes(int64_t R, int64_t C, int64_t jt, int64_t npb) {

@@ -189,7 +189,7 @@ Kernel Runtime::kernel(const std::string& source, const std::string& entry_name,
   return k;
 }
 
-void Runtime::launch(const Kernel& k, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3], unsigned smem, void** args) {
+void Runtime::launch(const Kernel& k, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3], unsigned smem, void** args, bool cooperative) {
   if (smem > 48 * 1024) drv_check(cuFuncSetAttribute_(k.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, static_cast<int>(smem)), "cuFuncSetAttribute(smem)");
   CUlaunchConfig cfg;
   std::memset(&cfg, 0, sizeof(cfg));
@@ -197,15 +197,21 @@ void Runtime::launch(const Kernel& k, const unsigned grid[3], const unsigned blo
   cfg.blockDimX = block[0]; cfg.blockDimY = block[1]; cfg.blockDimZ = block[2];
   cfg.sharedMemBytes = smem;
   cfg.hStream = stream_;
-  CUlaunchAttribute attr[1];
+  CUlaunchAttribute attr[2];
+  unsigned na = 0;
   if (cluster && cluster[0] * cluster[1] * cluster[2] > 1) {
-    attr[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-    attr[0].value.clusterDim.x = cluster[0]; attr[0].value.clusterDim.y = cluster[1]; attr[0].value.clusterDim.z = cluster[2];
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[na].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attr[na].value.clusterDim.x = cluster[0]; attr[na].value.clusterDim.y = cluster[1]; attr[na].value.clusterDim.z = cluster[2];
+    ++na;
     if (cluster[0] * cluster[1] * cluster[2] > 8)
       drv_check(cuFuncSetAttribute_(k.fn, CU_FUNC_ATTRIBUTE_NON_PORTABLE_CLUSTER_SIZE_ALLOWED, 1), "cuFuncSetAttribute(cluster)");
   }
+  if (cooperative) {   // CTAs that wait on one another must all be resident: the driver checks it
+    attr[na].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE;
+    attr[na].value.cooperative = 1;
+    ++na;
+  }
+  if (na) { cfg.attrs = attr; cfg.numAttrs = na; }
   drv_check(cuLaunchKernelEx_(&cfg, k.fn, args, nullptr), "cuLaunchKernelEx");
   ++stats.launches;
 }

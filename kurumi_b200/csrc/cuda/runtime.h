@@ -51,7 +51,7 @@ class Runtime {
   static std::string compile_to_cubin(const std::string& source, bool fmad, std::string* log_out);
 
   void launch(const Kernel& k, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3], unsigned smem,
-              void** args);
+              void** args, bool cooperative = false);
 
   // Largest number of clusters of this shape that can be resident at once (0 if it cannot launch).
   int max_active_clusters(const Kernel& k, unsigned cluster, unsigned block, unsigned smem);
