@@ -7,10 +7,11 @@
 // One CTA per (head, block of 128 queries); key/value blocks of 128 stream through two-stage rings.
 //   warp 0      TMA producer: Q once, then K_j / V_j (cp.async.bulk.tensor, SWIZZLE_128B, no multicast)
 //   warp 1      tcgen05.mma issuer: S_j = Q K_j^T into one of two TMEM score buffers (so the scores of
-//               block j+1 are computed while block j is in the softmax), then O_j = P_j V_j
-//   warps 2..5  one query row per thread: tcgen05.ld the scores, running max / sum in the log2
-//               domain, P_j as bf16 into shared memory in the swizzled K-major layout the second
-//               MMA reads, then tcgen05.ld O_j and fold it into the register accumulator
+//               block j+1 are computed while block j is in the softmax), then O += P_j V_j
+//   warps 2..5  one query row per thread: tcgen05.ld the scores, maximum / sum in the log2 domain, P_j as
+//               bf16 into shared memory in the swizzled K-major layout the second MMA reads. O accumulates
+//               in tensor memory across key blocks; the threads rescale it (tcgen05.ld / st) only when a
+//               row's maximum has grown by more than 2^8 since the scale it was accumulated with
 // Causal: key blocks above the diagonal are never loaded; the diagonal block is masked per element.
 // Every mbarrier wait is bounded (status word + sticky failure), tensor memory is always released.
 //
@@ -72,6 +73,17 @@ __device__ __forceinline__ void ku_tmem_ld32(unsigned taddr, float* v) {
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void ku_tmem_st32(unsigned taddr, const float* v) {
+  const unsigned* r = (const unsigned*)v;
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
+      "%24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]),
+        "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]),
+        "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float ku_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ unsigned ku_pack2(float lo, float hi) {
 #if KU_IS_BF16
@@ -85,7 +97,7 @@ extern "C" __global__ void __launch_bounds__(192, 1)
 ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ KuTmap tmap_k, const __grid_constant__ KuTmap tmap_v, void* __restrict__ Op,
                 int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_ready, o_full, o_free;
+  __shared__ __align__(8) unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_ready, o_full;
   __shared__ unsigned tmem_base_slot;
   unsigned char* smem = smem_raw + ((1024u - (ku_smem(smem_raw) & 1023u)) & 1023u);
   const unsigned q_s = ku_smem(smem), k_s = q_s + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES, p_s = v_s + 2 * TILE_BYTES;
@@ -102,7 +114,7 @@ ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ K
       ku_mbar_init(ku_smem(&k_full[i]), 1); ku_mbar_init(ku_smem(&k_empty[i]), 1); ku_mbar_init(ku_smem(&v_full[i]), 1); ku_mbar_init(ku_smem(&v_empty[i]), 1);
       ku_mbar_init(ku_smem(&s_full[i]), 1); ku_mbar_init(ku_smem(&s_free[i]), 128);
     }
-    ku_mbar_init(ku_smem(&p_ready), 128); ku_mbar_init(ku_smem(&o_full), 1); ku_mbar_init(ku_smem(&o_free), 128);
+    ku_mbar_init(ku_smem(&p_ready), 128); ku_mbar_init(ku_smem(&o_full), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -151,14 +163,13 @@ ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ K
         if (j + 1 < nkv) issue_s(j + 1);
         const int st = j & 1;
         ku_wait(ku_smem(&v_full[st]), (j >> 1) & 1, failed, status);
-        ku_wait(ku_smem(&p_ready), j & 1, failed, status);
-        ku_wait(ku_smem(&o_free), (j & 1) ^ 1, failed, status);
+        ku_wait(ku_smem(&p_ready), j & 1, failed, status);   // P_j is in shared memory and O has been rescaled if it had to be
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {   // O_j = P_j V_j: P K-major over keys, V MN-major (head dimension contiguous)
+        for (int kk = 0; kk < BKV / 16; ++kk) {   // O += P_j V_j: P K-major over keys, V MN-major (head dimension contiguous)
           const unsigned long long ad = ku_smem_desc(p_s + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
           const unsigned long long bd = ku_smem_desc(v_s + st * TILE_BYTES + kk * 16 * 128, 16384, 1024);
-          ku_mma(tmem_base + 256, ad, bd, IDESC_O, kk != 0);
+          ku_mma(tmem_base + 256, ad, bd, IDESC_O, (j | kk) != 0);
         }
         ku_mma_commit(ku_smem(&o_full));
         ku_mma_commit(ku_smem(&v_empty[st]));
@@ -169,70 +180,81 @@ ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ K
     const int r = q4 * 32 + lane;                 // row of the tile == TMEM lane
     const int qrow = qb * BQ + r;
     const unsigned lane_addr = tmem_base + ((unsigned)(q4 * 32) << 16);
-    float o[DH];
-#pragma unroll
-    for (int c = 0; c < DH; ++c) o[c] = 0.0f;
+    // m is the reference maximum the accumulator O (in tensor memory) and the sum l are scaled by. It follows
+    // the running maximum lazily: only when a block's maximum exceeds it by more than 2^8 are O and l rescaled,
+    // so most blocks touch O with the tensor core alone (probabilities stay below 2^8, accumulation is f32).
     float m = -KU_INF, l = 0.0f;
     for (int j = 0; j < nkv; ++j) {
       const int st = j & 1;
       ku_wait(ku_smem(&s_full[st]), (j >> 1) & 1, failed, status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool need_mask = (CAUSAL && j == qb) || (j * BKV + BKV > S);
-      // pass A: block maximum of this row
-      float bm = -KU_INF;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        float v[32];
-        ku_tmem_ld32(lane_addr + st * 128 + c0, v);
+      // the row's scores of this block, in log2 units, masked keys at -inf
+      float sc[BKV];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int key = j * BKV + c0 + c;
-          const bool masked = need_mask && ((CAUSAL && key > qrow) || key >= S);
-          bm = fmaxf(bm, masked ? -KU_INF : v[c] * SCALE_LOG2E);
-        }
-      }
-      const float mn = fmaxf(m, bm);
-      const float alpha = ku_ex2(m - mn);   // 0 on the first block (m = -inf)
-      // pass B: probabilities, as bf16 into the swizzled K-major tile the second MMA reads
-      float bs = 0.0f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        float v[32];
-        ku_tmem_ld32(lane_addr + st * 128 + c0, v);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int key = j * BKV + c0 + c;
-          const bool masked = need_mask && ((CAUSAL && key > qrow) || key >= S);
-          v[c] = masked ? 0.0f : ku_ex2(__fmaf_rn(v[c], SCALE_LOG2E, -mn));
-          bs += v[c];
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {   // 8 keys = one 16-byte chunk of the row
-          uint4 pk;
-          pk.x = ku_pack2(v[g * 8 + 0], v[g * 8 + 1]); pk.y = ku_pack2(v[g * 8 + 2], v[g * 8 + 3]);
-          pk.z = ku_pack2(v[g * 8 + 4], v[g * 8 + 5]); pk.w = ku_pack2(v[g * 8 + 6], v[g * 8 + 7]);
-          const int col = c0 + g * 8;   // first key of the chunk
-          const int chunk16 = (col & 63) >> 3;
-          *(uint4*)(p_tile + (col >> 6) * 16384 + r * 128 + ((chunk16 ^ (r & 7)) << 4)) = pk;
-        }
-      }
+      for (int c0 = 0; c0 < BKV; c0 += 32) ku_tmem_ld32(lane_addr + st * 128 + c0, sc + c0);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       ku_mbar_arrive(ku_smem(&s_free[st]));                          // the score buffer may be overwritten
+      float bm = -KU_INF;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < BKV; ++c) {
+          const int key = j * BKV + c;
+          sc[c] = ((CAUSAL && key > qrow) || key >= S) ? -KU_INF : sc[c] * SCALE_LOG2E;
+          bm = fmaxf(bm, sc[c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < BKV; ++c) { sc[c] *= SCALE_LOG2E; bm = fmaxf(bm, sc[c]); }
+      }
+      // the previous block's P V product must have retired before P is overwritten or O is touched
+      if (j > 0) {
+        ku_wait(ku_smem(&o_full), (j - 1) & 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+      const bool grow = bm > m + 8.0f || (m == -KU_INF && bm != -KU_INF);
+      if (__any_sync(0xffffffffu, grow)) {   // tensor-memory loads and stores are warp-wide: rows that keep their reference scale by 1
+        const float alpha = grow ? ku_ex2(m - bm) : 1.0f;   // 0 for a row's first finite block: O holds nothing for it yet
+        if (j > 0) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < DH; c0 += 32) {
+            float v[32];
+            ku_tmem_ld32(lane_addr + 256 + c0, v);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] *= alpha;
+            ku_tmem_st32(lane_addr + 256 + c0, v);
+          }
+        }
+        l *= alpha;
+        if (grow) m = bm;
+      }
+      const float mref = (m == -KU_INF) ? 0.0f : m;   // a row with nothing finite so far: exp2(-inf - 0) = 0
+      float bs = 0.0f;
+#pragma unroll
+      for (int c0 = 0; c0 < BKV; c0 += 8) {   // 8 keys = one 16-byte chunk of the row, as bf16 in the swizzled K-major tile
+        float e[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) { e[c] = ku_ex2(sc[c0 + c] - mref); bs += e[c]; }
+        uint4 pk;
+        pk.x = ku_pack2(e[0], e[1]); pk.y = ku_pack2(e[2], e[3]); pk.z = ku_pack2(e[4], e[5]); pk.w = ku_pack2(e[6], e[7]);
+        const int chunk16 = (c0 & 63) >> 3;
+        *(uint4*)(p_tile + (c0 >> 6) * 16384 + r * 128 + ((chunk16 ^ (r & 7)) << 4)) = pk;
+      }
+      l += bs;
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core (async proxy)
       ku_mbar_arrive(ku_smem(&p_ready));
-      l = l * alpha + bs;
-      m = mn;
-      ku_wait(ku_smem(&o_full), j & 1, failed, status);
+    }
+    // the last product, then this row of O
+    float o[DH];
+    if (nkv > 0) {
+      ku_wait(ku_smem(&o_full), (nkv - 1) & 1, failed, status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int c0 = 0; c0 < DH; c0 += 32) {
-        float v[32];
-        ku_tmem_ld32(lane_addr + 256 + c0, v);
+      for (int c0 = 0; c0 < DH; c0 += 32) ku_tmem_ld32(lane_addr + 256 + c0, o + c0);
+    } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) o[c0 + c] = __fmaf_rn(o[c0 + c], alpha, v[c]);
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      ku_mbar_arrive(ku_smem(&o_free));
+      for (int c = 0; c < DH; ++c) o[c] = 0.0f;
     }
     if (qrow < S) {
       const float inv = 1.0f / l;
