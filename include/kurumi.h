@@ -140,6 +140,16 @@ KuTensor *ku_eval_with(KuGraph *g, KuNode node, const KuBackend *backend, const 
 int32_t ku_eval_many(KuGraph *g, const KuNode *ids, size_t n, const KuBackend *backend, const KuFeeds *feeds,
                      KuTensor **out); /* 0 ok, -1 err */
 
+/* weight-only quantised matmul, kurumi.h:225-234: act[M,K] x dequant(qweight)[N,K]^T -> [M,N] in act's dtype.
+ * qweight is a KU_U8-packed tensor [N, K*bits/8], scales / mins are KU_F16 [N, K/group_size]; mins = KU_ERR for
+ * symmetric. ku_quantize writes out_packed (rows*cols*bits/8 bytes), out_scales (rows*cols/group_size f16 bit
+ * patterns) and out_mins (same count, or NULL when symmetric != 0); bits is 2, 4 or 8; bad arguments leave the
+ * outputs untouched and set ku_last_error. */
+KuNode ku_quant_matmul(KuGraph *g, KuNode act, KuNode qweight, KuNode scales, KuNode mins, uint8_t bits,
+                       size_t group_size);
+void ku_quantize(const float *w, size_t rows, size_t cols, uint8_t bits, size_t group_size, uint32_t symmetric,
+                 uint8_t *out_packed, uint16_t *out_scales, uint16_t *out_mins);
+
 /* passes and inspection, kurumi.h:395-405 */
 KuNode ku_amp(KuGraph *g, KuNode root); /* mixed precision (f16 matmuls) */
 size_t ku_node_count(const KuGraph *g, KuNode root);

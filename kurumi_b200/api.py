@@ -207,6 +207,11 @@ class Graph:
         s, r = _sz(a.shape)
         return self._n("ku_constant", C.c_uint32(dtype), a.ctypes.data_as(C.c_void_p), C.c_size_t(a.nbytes), s, C.c_size_t(r))
 
+    def quant_matmul(self, act: int, qweight: int, scales: int, mins: int | None, bits: int, group_size: int) -> int:
+        """act [M, K] x dequant(qweight [N, K*bits/8] U8, scales / mins [N, K/group_size] F16)^T -> [M, N]; mins None = symmetric."""
+        return self._n("ku_quant_matmul", C.c_uint32(act), C.c_uint32(qweight), C.c_uint32(scales), C.c_uint32(KU_ERR if mins is None else mins),
+                       C.c_uint8(bits), C.c_size_t(group_size))
+
     def scalar(self, like: int, v: float) -> int:
         return self._n("ku_scalar", C.c_uint32(like), C.c_float(v))
 
@@ -534,6 +539,21 @@ def compile_check(lib: Library, g: Graph, nodes) -> list:
     if n == C.c_size_t(-1).value:
         raise Error(lib.last_error())
     return bytes(buf[:n]).decode().split()
+
+
+def quantize(lib: Library, w: np.ndarray, bits: int, group_size: int, symmetric: bool):
+    """Group-wise weight quantisation (ku_quantize): returns (packed u8 [rows, cols*bits/8], scales f16 [rows, cols/group], mins or None)."""
+    w = np.ascontiguousarray(w, np.float32)
+    rows, cols = w.shape
+    if bits not in (2, 4, 8) or group_size <= 0 or cols % group_size:
+        raise Error("quantize: bits must be 2, 4 or 8 and cols a multiple of group_size")
+    packed = np.zeros((rows, cols * bits // 8), np.uint8)
+    scales = np.zeros((rows, cols // group_size), np.float16)
+    mins = None if symmetric else np.zeros((rows, cols // group_size), np.float16)
+    lib.lib.ku_quantize.restype = None
+    lib.lib.ku_quantize(w.ctypes.data_as(C.c_void_p), C.c_size_t(rows), C.c_size_t(cols), C.c_uint8(bits), C.c_size_t(group_size), C.c_uint32(1 if symmetric else 0),
+                        packed.ctypes.data_as(C.c_void_p), scales.ctypes.data_as(C.c_void_p), None if mins is None else mins.ctypes.data_as(C.c_void_p))
+    return packed, scales, mins
 
 
 def deserialize(lib: Library, blob: bytes):

@@ -200,6 +200,13 @@ int32_t ku_eval_many(KuGraph* g, const KuNode* ids, size_t n, const KuBackend* b
   });
 }
 
+KuNode ku_quant_matmul(KuGraph* g, KuNode act, KuNode qweight, KuNode scales, KuNode mins, uint8_t bits, size_t group_size) {
+  return build(g, [&](Graph& gr) { return gr.quant_matmul(act, qweight, scales, mins == KU_ERR ? nullptr : &mins, bits, group_size); });
+}
+void ku_quantize(const float* w, size_t rows, size_t cols, uint8_t bits, size_t group_size, uint32_t symmetric, uint8_t* out_packed, uint16_t* out_scales,
+                 uint16_t* out_mins) {
+  guard<int>(0, [&]() { ku::quantize(w, rows, cols, bits, group_size, symmetric != 0, out_packed, out_scales, out_mins); return 0; });
+}
 KuNode ku_amp(KuGraph* g, KuNode root) { return build(g, [&](Graph& gr) { return amp(gr, root); }); }
 size_t ku_node_count(const KuGraph* g, KuNode root) {
   if (!g) return 0;

@@ -26,7 +26,7 @@ const char* op_name(OpKind k) {
   static const char* n[] = {"Const", "Input", "Iota", "RandUniform", "Cast", "Bitcast", "Detach", "Add", "Mul", "Max",
                             "Neg", "IDiv", "And", "Or", "Xor", "Shl", "Shr", "CmpLt", "CmpEq", "Where", "Recip", "Sqrt",
                             "Exp2", "Log2", "Sin", "Floor", "Sum", "Prod", "ReduceMax", "Softmax", "RmsNorm", "Sdpa",
-                            "Reshape", "Permute", "Expand", "Slice", "Flip", "Pad", "DotGeneral"};
+                            "Reshape", "Permute", "Expand", "Slice", "Flip", "Pad", "DotGeneral", "QuantMatmul"};
   return n[static_cast<size_t>(k)];
 }
 
@@ -92,6 +92,7 @@ Shape Graph::derive_shape(const Op& op, const std::vector<NodeId>& src) const {
       for (size_t i : free_axes(b.size(), op.rb, op.rc)) o.push_back(b[i]);
       return o;
     }
+    case OpKind::QuantMatmul: return Shape{ishape(0)[0], ishape(1)[0]};   // act [M, K] x dequant(qweight) [N, K]^T
     default: return ishape(0);  // elementwise, Softmax, RmsNorm, Sdpa, Flip
   }
 }
@@ -407,6 +408,94 @@ NodeId Graph::sdpa_fused(NodeId q, NodeId k, NodeId v, bool causal) {
   Op op; op.kind = OpKind::Sdpa; op.causal = causal;
   return push(std::move(op), {q, k, v});
 }
+// kurumi_core/src/graph/ops/core/contract.rs:52-116
+NodeId Graph::quant_matmul(NodeId act, NodeId qweight, NodeId scales, const NodeId* mins, uint8_t bits, size_t group_size) {
+  const Shape sa = shape(act), sq = shape(qweight);
+  if (sa.size() != 2 || sq.size() != 2)
+    throw Error::shape("quant_matmul", "act rank " + std::to_string(sa.size()) + ", qweight rank " + std::to_string(sq.size()) + ": both must be rank-2");
+  if (dtype(qweight) != DType::U8) throw Error::shape("quant_matmul", std::string("qweight must be U8, got ") + dtype_name(dtype(qweight)));
+  if (dtype(scales) != DType::F16) throw Error::shape("quant_matmul", std::string("scales must be F16, got ") + dtype_name(dtype(scales)));
+  if (mins && dtype(*mins) != DType::F16) throw Error::shape("quant_matmul", std::string("mins must be F16, got ") + dtype_name(dtype(*mins)));
+  if (!is_float(dtype(act))) throw Error::shape("quant_matmul", std::string("act must be float, got ") + dtype_name(dtype(act)));
+  const size_t k = sa[1], n = sq[0];
+  if (!(bits == 2 || bits == 4 || bits == 8)) throw Error::shape("quant_matmul", "bits " + std::to_string(bits) + " must be 2, 4, or 8");
+  if (group_size == 0 || k % group_size != 0)
+    throw Error::shape("quant_matmul", "K " + std::to_string(k) + " must be a nonzero multiple of group_size " + std::to_string(group_size));
+  if (sq[1] * 8 != k * bits)
+    throw Error::shape("quant_matmul", "qweight cols " + std::to_string(sq[1]) + " must equal K*bits/8 = " + std::to_string(k) + "*" + std::to_string(bits) + "/8");
+  const size_t want = n * (k / group_size);
+  if (numel(shape(scales)) != want) throw Error::shape("quant_matmul", "scales must have N*K/group_size = " + std::to_string(want) + " entries");
+  if (mins && numel(shape(*mins)) != want) throw Error::shape("quant_matmul", "mins must have N*K/group_size = " + std::to_string(want) + " entries");
+  Op op; op.kind = OpKind::QuantMatmul; op.bits = bits; op.group_size = group_size; op.symmetric = mins == nullptr;
+  std::vector<NodeId> src{act, qweight, scales};
+  if (mins) src.push_back(*mins);
+  return push(std::move(op), std::move(src));
+}
+
+// kurumi_core/src/quant.rs:38-88
+void quantize(const float* w, size_t rows, size_t cols, uint8_t bits, size_t group_size, bool symmetric, uint8_t* packed, uint16_t* scales, uint16_t* mins) {
+  if (!(bits == 2 || bits == 4 || bits == 8)) throw Error::shape("quantize", "bits must be 2, 4, or 8");
+  if (group_size == 0 || cols % group_size != 0) throw Error::shape("quantize", "cols must be a multiple of group_size");
+  if (!w || !packed || !scales || (!symmetric && !mins)) throw Error::shape("quantize", "null buffer");
+  const size_t ng = cols / group_size, rb = cols * bits / 8, per = 8 / bits;
+  std::memset(packed, 0, rows * rb);
+  auto put = [&](size_t r, size_t c, uint8_t v) {
+    const size_t i = r * rb + c / per, shift = (c % per) * bits;
+    const uint8_t mask = static_cast<uint8_t>((1u << bits) - 1);
+    packed[i] = static_cast<uint8_t>((packed[i] & ~(mask << shift)) | ((v & mask) << shift));
+  };
+  auto f16_of = [](float f) { uint16_t h; f64_to_elem(DType::F16, static_cast<double>(f), &h); return h; };
+  auto f32_of = [](uint16_t h) { return static_cast<float>(elem_to_f64(DType::F16, &h)); };
+  for (size_t r = 0; r < rows; ++r)
+    for (size_t g = 0; g < ng; ++g) {
+      const float* grp = w + r * cols + g * group_size;
+      const size_t si = r * ng + g;
+      if (symmetric) {
+        float amax = 0.0f;
+        for (size_t i = 0; i < group_size; ++i) amax = std::fmax(amax, std::fabs(grp[i]));
+        const int qlo = -(1 << (bits - 1)), qhi = (1 << (bits - 1)) - 1;
+        scales[si] = f16_of(amax > 0.0f ? amax / static_cast<float>(qhi) : 1.0f);
+        const float sv = f32_of(scales[si]);
+        for (size_t i = 0; i < group_size; ++i) {
+          float q = std::round(grp[i] / sv);
+          q = std::fmin(std::fmax(q, static_cast<float>(qlo)), static_cast<float>(qhi));
+          put(r, g * group_size + i, static_cast<uint8_t>(static_cast<int>(q) & ((1 << bits) - 1)));
+        }
+      } else {
+        float mn = std::numeric_limits<float>::infinity(), mx = -std::numeric_limits<float>::infinity();
+        for (size_t i = 0; i < group_size; ++i) { mn = std::fmin(mn, grp[i]); mx = std::fmax(mx, grp[i]); }
+        const float qmax = static_cast<float>((1u << bits) - 1);
+        scales[si] = f16_of(mx > mn ? (mx - mn) / qmax : 1.0f);
+        mins[si] = f16_of(mn);
+        const float sv = f32_of(scales[si]), mv = f32_of(mins[si]);
+        for (size_t i = 0; i < group_size; ++i) {
+          float q = std::round((grp[i] - mv) / sv);
+          q = std::fmin(std::fmax(q, 0.0f), qmax);
+          put(r, g * group_size + i, static_cast<uint8_t>(static_cast<unsigned>(q)));
+        }
+      }
+    }
+}
+
+std::vector<float> dequantize(const uint8_t* packed, const uint16_t* scales, const uint16_t* mins, size_t rows, size_t cols, uint8_t bits, size_t group_size) {
+  const size_t ng = cols / group_size, rb = cols * bits / 8, per = 8 / bits;
+  std::vector<float> out(rows * cols);
+  for (size_t r = 0; r < rows; ++r)
+    for (size_t c = 0; c < cols; ++c) {
+      const size_t gi = r * ng + c / group_size;
+      const uint8_t raw = static_cast<uint8_t>((packed[r * rb + c / per] >> ((c % per) * bits)) & ((1u << bits) - 1));
+      const float scale = static_cast<float>(elem_to_f64(DType::F16, scales + gi));
+      if (mins) {
+        out[r * cols + c] = static_cast<float>(raw) * scale + static_cast<float>(elem_to_f64(DType::F16, mins + gi));
+      } else {
+        const int sh = 32 - bits;   // sign-extend the field
+        const int v = static_cast<int>(static_cast<uint32_t>(raw) << sh) >> sh;
+        out[r * cols + c] = static_cast<float>(v) * scale;
+      }
+    }
+  return out;
+}
+
 NodeId Graph::causal_bias(size_t s, const Shape& out_shape) {
   std::vector<float> data(s * s, 0.0f);
   for (size_t i = 0; i < s; ++i)

@@ -53,6 +53,7 @@ enum class OpKind : uint8_t {
   Recip, Sqrt, Exp2, Log2, Sin, Floor,
   Sum, Prod, ReduceMax, Softmax, RmsNorm, Sdpa,
   Reshape, Permute, Expand, Slice, Flip, Pad, DotGeneral,
+  QuantMatmul,
 };
 const char* op_name(OpKind k);
 inline bool is_movement(OpKind k) { return k >= OpKind::Reshape && k <= OpKind::Pad; }
@@ -69,6 +70,9 @@ struct Op {
   std::vector<size_t> perm;                    // Permute perm / Flip axes
   std::vector<std::array<size_t, 3>> ranges;   // Slice (start, end, step) / Pad (lo, hi, 0)
   std::vector<size_t> lc, rc, lb, rb;          // DotGeneral contract / batch axes
+  uint8_t bits = 0;                            // QuantMatmul: 2, 4 or 8 bits per weight
+  size_t group_size = 0;                       // QuantMatmul: weights per (scale, min) group along K
+  bool symmetric = true;                       // QuantMatmul: no mins operand
 };
 
 struct Node {
@@ -131,6 +135,8 @@ class Graph {
   NodeId dot_general(NodeId a, NodeId b, std::vector<size_t> lc, std::vector<size_t> rc, std::vector<size_t> lb,
                      std::vector<size_t> rb);
   NodeId sdpa_fused(NodeId q, NodeId k, NodeId v, bool causal);
+  // weight-only quantised matmul: act [M, K] x dequant(qweight) [N, K]^T -> [M, N] in act's dtype; `mins` absent = symmetric
+  NodeId quant_matmul(NodeId act, NodeId qweight, NodeId scales, const NodeId* mins, uint8_t bits, size_t group_size);
   // decompositions
   NodeId scalar(NodeId like, float v);
   NodeId sub(NodeId a, NodeId b);
@@ -193,6 +199,13 @@ std::string dump(const Graph& g, NodeId root);
 //    the products are the same numbers.
 NodeId amp(Graph& g, NodeId root);
 NodeId amp_to(Graph& g, NodeId root, DType target);
+
+// Group-wise weight quantisation for quant_matmul (kurumi_core/src/quant.rs:38-88): w is [rows, cols] f32,
+// packed receives rows * cols * bits / 8 bytes (fields of a byte fill from its low bits), scales and mins one
+// f16 per [row, group]; symmetric: w ~ q * scale with q a signed field, else w ~ q * scale + min with q unsigned.
+void quantize(const float* w, size_t rows, size_t cols, uint8_t bits, size_t group_size, bool symmetric, uint8_t* packed, uint16_t* scales, uint16_t* mins);
+// The f32 weights a quantised operand stands for (kurumi_core/src/quant.rs:90-113).
+std::vector<float> dequantize(const uint8_t* packed, const uint16_t* scales, const uint16_t* mins, size_t rows, size_t cols, uint8_t bits, size_t group_size);
 
 // Cast a host buffer through f64 (kurumi_core/src/dtype/convert.rs:14-47).
 Tensor cast_tensor(const Tensor& src, DType to);

@@ -19,7 +19,7 @@ constexpr TagRow kTags[] = {
     {OpKind::CmpEq, 18},  {OpKind::Where, 19},  {OpKind::Recip, 20},    {OpKind::Sqrt, 21},       {OpKind::Exp2, 22},    {OpKind::Log2, 23},
     {OpKind::Sin, 24},    {OpKind::Floor, 25},  {OpKind::Sum, 26},      {OpKind::Prod, 27},       {OpKind::ReduceMax, 28}, {OpKind::Softmax, 30},
     {OpKind::RmsNorm, 31}, {OpKind::Sdpa, 32},  {OpKind::Reshape, 33},  {OpKind::Permute, 34},    {OpKind::Expand, 35},  {OpKind::Slice, 36},
-    {OpKind::Flip, 37},   {OpKind::Pad, 38},    {OpKind::DotGeneral, 39},
+    {OpKind::Flip, 37},   {OpKind::Pad, 38},    {OpKind::DotGeneral, 39}, {OpKind::QuantMatmul, 40},
 };
 uint8_t tag_of(OpKind k) {
   for (const TagRow& r : kTags) if (r.kind == k) return r.tag;
@@ -69,6 +69,7 @@ void write_op(Writer& w, const Op& op) {
       for (auto& r : op.ranges) { w.u64(r[0]); w.u64(r[1]); }
       break;
     case OpKind::DotGeneral: w.vec(op.lc); w.vec(op.rc); w.vec(op.lb); w.vec(op.rb); break;
+    case OpKind::QuantMatmul: w.u8(op.bits); w.u64(op.group_size); w.u8(op.symmetric ? 1 : 0); break;
     default: break;   // attribute-free primitives
   }
 }
@@ -214,6 +215,7 @@ NodeId read_node(Reader& r, Graph& g, size_t index) {
       break;
     }
     case OpKind::DotGeneral: op.lc = r.vec(); op.rc = r.vec(); op.lb = r.vec(); op.rb = r.vec(); break;
+    case OpKind::QuantMatmul: op.bits = r.u8(); op.group_size = r.usize(); op.symmetric = r.u8() != 0; break;
     default: break;
   }
   // sources: each must already exist
@@ -267,6 +269,7 @@ NodeId read_node(Reader& r, Graph& g, size_t index) {
     case OpKind::Flip: need(1); id = g.flip(src[0], op.perm); break;
     case OpKind::Pad: need(1); id = g.pad(src[0], pads); break;
     case OpKind::DotGeneral: need(2); id = g.dot_general(src[0], src[1], op.lc, op.rc, op.lb, op.rb); break;
+    case OpKind::QuantMatmul: need(op.symmetric ? 3 : 4); id = g.quant_matmul(src[0], src[1], src[2], op.symmetric ? nullptr : &src[3], op.bits, op.group_size); break;
   }
   if (id != index || g.size() != index + 1 || g.node(id).op.kind != kind)
     throw bad("node " + std::to_string(index) + " (" + op_name(kind) + ") did not rebuild as one primitive");

@@ -439,6 +439,75 @@ Fused Scheduler::sdpa(const Node& n, const Fused& q0, const Fused& k0, const Fus
   return dot_general(dt, n.shape, attn, v, {r - 1}, {r - 2}, batch, batch);
 }
 
+// ---- weight-only quantised matmul ---------------------------------------------------------------------
+// Lowered onto the primitives above (kurumi_core/src/interp/contract.rs:69-99 is the semantics): the packed
+// weight becomes a fused pointwise expression W[n][c] = field(n, c) * scale(n, c / group) (+ min) over views of
+// the operands - a byte is shared by 8 / bits columns (expand + reshape), its field index is an iota - and
+// the contraction act x W^T runs on the regular paths: true f32 for an f32 activation; for a 16-bit
+// activation the dequantised weight is rounded to that dtype and the tensor cores accumulate in f32.
+Fused Scheduler::view_step(OpKind k, Fused f, const Shape& shape) {
+  Node tmp;
+  tmp.op.kind = k;
+  tmp.op.shape = shape;
+  tmp.shape = shape;
+  return movement(tmp, std::move(f));
+}
+
+Fused Scheduler::quant_matmul(const Node& n, const std::vector<Fused>& in) {
+  const Op& op = n.op;
+  const size_t M = n.shape[0], N = n.shape[1], K = in[0].shape[1];
+  const size_t per = 8 / op.bits, ng = K / op.group_size;
+  const Shape nk{N, K};
+  // byte of column c: packed[n][c / per]
+  Fused q = view_step(OpKind::Reshape, resolve_acc(in[1]), {N, K / per, 1});
+  q = view_step(OpKind::Expand, q, {N, K / per, per});
+  q = view_step(OpKind::Reshape, q, nk);
+  Fused qi = combine(OpKind::Cast, DType::I32, {&q});
+  // field index c % per (K is a multiple of per, so the flat index serves) times the field width
+  Leaf il;
+  il.kind = LeafKind::Iota; il.dtype = DType::I32; il.view = View::source(nk);
+  il.iota_len = static_cast<int64_t>(per);
+  il.iota_stride = 1;
+  Fused field = fused_leaf(nk, il);
+  Fused width = imm_value(nk, DType::I32, elem_bits(DType::I32, static_cast<double>(op.bits)));
+  Fused shift = combine(OpKind::Mul, DType::I32, {&field, &width});
+  Fused raw = combine(OpKind::Shr, DType::I32, {&qi, &shift});
+  Fused mask = imm_value(nk, DType::I32, elem_bits(DType::I32, static_cast<double>((1u << op.bits) - 1)));
+  raw = combine(OpKind::And, DType::I32, {&raw, &mask});
+  if (op.symmetric) {   // sign-extend the field: (raw << (32 - bits)) >> (32 - bits), arithmetic
+    Fused sh = imm_value(nk, DType::I32, elem_bits(DType::I32, static_cast<double>(32 - op.bits)));
+    raw = combine(OpKind::Shl, DType::I32, {&raw, &sh});
+    raw = combine(OpKind::Shr, DType::I32, {&raw, &sh});
+  }
+  Fused w = combine(OpKind::Cast, DType::F32, {&raw});
+  auto per_group = [&](const Fused& g16) {   // [N, ng] f16 -> f32 value of every column's group
+    Fused g = view_step(OpKind::Reshape, resolve_acc(g16), {N, ng, 1});
+    g = view_step(OpKind::Expand, g, {N, ng, op.group_size});
+    g = view_step(OpKind::Reshape, g, nk);
+    return combine(OpKind::Cast, DType::F32, {&g});
+  };
+  Fused sc = per_group(in[2]);
+  w = combine(OpKind::Mul, DType::F32, {&w, &sc});
+  if (!op.symmetric) {
+    Fused mn = per_group(in[3]);
+    w = combine(OpKind::Add, DType::F32, {&w, &mn});
+  }
+  const DType dt = n.dtype;
+  Fused act = resolve_acc(in[0]);
+  if (dt == DType::F32 || dt == DType::F64) {
+    if (dt == DType::F64) w = combine(OpKind::Cast, DType::F64, {&w});
+    return dot_general(dt, {M, N}, act, w, {1}, {1}, {}, {});
+  }
+  if (dt == DType::BF16 || dt == DType::F16) {
+    Fused wl = combine(OpKind::Cast, dt, {&w});
+    return dot_general(dt, {M, N}, act, wl, {1}, {1}, {}, {});
+  }
+  // fp8 activations: contract in f32 and round once, as the interpreter does
+  Fused a32 = combine(OpKind::Cast, DType::F32, {&act});
+  Fused r = dot_general(DType::F32, {M, N}, a32, w, {1}, {1}, {}, {});
+  return combine(OpKind::Cast, dt, {&r});
+}
+
 // ---- the walk ---------------------------------------------------------------------------------------
 Fused Scheduler::value_of(NodeId id) { return memo_.at(id); }
 
@@ -509,6 +578,7 @@ Fused Scheduler::eval_node(NodeId id) {
     case OpKind::Reshape: case OpKind::Permute: case OpKind::Expand: case OpKind::Slice: case OpKind::Flip: case OpKind::Pad:
       return movement(n, in[0]);
     case OpKind::DotGeneral: return dot(n, in[0], in[1]);
+    case OpKind::QuantMatmul: return quant_matmul(n, in);
   }
   throw Error::backend(std::string("op ") + op_name(op.kind) + " has no CUDA kernel");
 }

@@ -48,6 +48,8 @@ class Scheduler {
   Fused dot_general(DType dt, const Shape& out_shape, const Fused& a, const Fused& b, const std::vector<size_t>& lc,
                     const std::vector<size_t>& rc, const std::vector<size_t>& lb, const std::vector<size_t>& rb);
   Fused sdpa(const Node& n, const Fused& q, const Fused& k, const Fused& v);
+  Fused quant_matmul(const Node& n, const std::vector<Fused>& in);
+  Fused view_step(OpKind k, Fused f, const Shape& shape);
   Fused imm_value(const Shape& shape, DType dt, uint64_t bits) const;
   void emit_gemm(int id, const Fused* epi, int out_slot);
   void push_launch(const Emitted& e, const Fused& f, int out_slot, double flops = 0);

@@ -607,6 +607,46 @@ Val sdpa_val(const Val& q, const Val& k, const Val& v, bool causal) {
 }
 
 // ---- generation (kurumi_core/src/interp/random.rs:10-28, dtype/convert.rs:72-80) ----------------
+// kurumi_core/src/interp/contract.rs:69-99 with kurumi_core/src/quant.rs:90-113: dequantise the packed weight
+// [N, K] to f32 (raw * scale + min, or the sign-extended field * scale), then act [M, K] x W^T as an f32
+// contraction, rounded once to act's dtype. The wide run does the same in f64.
+Val quant_matmul_val(const Val& act, const Val& qw, const Val& scales, const Val* mins, const Op& op) {
+  const size_t m = act.shape[0], k = act.shape[1], n = qw.shape[0];
+  const size_t ng = k / op.group_size, rb = k * op.bits / 8, per = 8 / op.bits;
+  auto half_at = [](const Val& v, size_t i) -> double {
+    if (v.wide) return wd(v)[i];
+    return elem_to_f64(DType::F16, v.bytes.data() + 2 * i);
+  };
+  Op dot;
+  dot.kind = OpKind::DotGeneral;
+  dot.lc = {1};
+  dot.rc = {1};
+  if (act.wide) {
+    Val w = make_val(DType::F64, {n, k}, true);
+    double* wp = wd(w);
+    for (size_t r = 0; r < n; ++r)
+      for (size_t c = 0; c < k; ++c) {
+        const size_t gi = r * ng + c / op.group_size;
+        const unsigned raw = (qw.bytes[r * rb + c / per] >> ((c % per) * op.bits)) & ((1u << op.bits) - 1);
+        if (mins) wp[r * k + c] = static_cast<double>(raw) * half_at(scales, gi) + half_at(*mins, gi);
+        else { const int sh = 32 - op.bits; wp[r * k + c] = static_cast<double>(static_cast<int>(raw << sh) >> sh) * half_at(scales, gi); }
+      }
+    Val o = make_val(act.dtype, {m, n}, true);
+    dot_num<double>(wd(act), act.shape, wp, w.shape, dot, wd(o));
+    return o;
+  }
+  std::vector<uint16_t> sc(n * ng), mn(mins ? n * ng : 0);
+  for (size_t i = 0; i < n * ng; ++i) {
+    f64_to_elem(DType::F16, half_at(scales, i), &sc[i]);
+    if (mins) f64_to_elem(DType::F16, half_at(*mins, i), &mn[i]);
+  }
+  std::vector<float> wf = ku::dequantize(qw.bytes.data(), sc.data(), mins ? mn.data() : nullptr, n, k, op.bits, op.group_size);
+  Val w = make_val(DType::F32, {n, k}, false);
+  std::memcpy(w.bytes.data(), wf.data(), wf.size() * 4);
+  Val r = dot_f32(cast_val(act, DType::F32, false), w, dot);
+  return cast_val(r, act.dtype, false);
+}
+
 Val iota_val(const Op& op, bool wide_mode) {
   const size_t len = numel(op.shape);
   size_t stride = 1;
@@ -672,6 +712,7 @@ Val eval_op(const Node& n, const std::vector<const Val*>& in, bool wide_mode) {
     case OpKind::Reshape: case OpKind::Permute: case OpKind::Expand: case OpKind::Slice: case OpKind::Flip: case OpKind::Pad:
       return movement_val(op, *in[0]);
     case OpKind::DotGeneral: return dot_val(*in[0], *in[1], op);
+    case OpKind::QuantMatmul: return quant_matmul_val(*in[0], *in[1], *in[2], in.size() > 3 ? in[3] : nullptr, op);
   }
   throw Error("oracle: unknown op");
 }

@@ -1,0 +1,123 @@
+"""Weight-only quantised matmul (Op::QuantMatmul): the quantiser, the oracle and the graph layer against the
+values the reference's own tests pin (kurumi_core/src/quant/tests.rs), the record-time checks of
+kurumi_core/src/graph/ops/core/contract.rs:52-116, the blob tag, and the device lowering compiled for sm_100a."""
+import numpy as np
+import pytest
+
+from kurumi_b200 import api
+
+
+def dequant(packed, scales, mins, bits, group):
+    rows, cols = packed.shape[0], packed.shape[1] * 8 // bits
+    per = 8 // bits
+    c = np.arange(cols)
+    raw = (packed[:, c // per] >> ((c % per) * bits)) & ((1 << bits) - 1)
+    s = scales.astype(np.float32)[:, c // group]
+    if mins is not None:
+        return raw.astype(np.float32) * s + mins.astype(np.float32)[:, c // group]
+    sh = 32 - bits
+    signed = (raw.astype(np.int32) << sh) >> sh
+    return signed.astype(np.float32) * s
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("sym", [True, False])
+def test_roundtrip_bound(oracle_lib, bits, group, sym):
+    rows, cols = 3, 128
+    i = np.arange(rows * cols)
+    w = (((i * 37 % 211).astype(np.float32) / np.float32(211.0) - np.float32(0.5)) * np.float32(6.0)).reshape(rows, cols)
+    packed, scales, mins = api.quantize(oracle_lib, w, bits, group, sym)
+    assert packed.shape == (rows, cols * bits // 8)
+    dq = dequant(packed, scales, mins, bits, group)
+    s = scales.astype(np.float32)[:, np.arange(cols) // group]
+    assert (np.abs(w - dq) <= s * 0.55 + 1e-3).all()
+
+
+def test_int8_beats_int4_and_nibble_packing(oracle_lib):
+    w = (np.sin(np.arange(128, dtype=np.float32)) * np.float32(3.0)).reshape(2, 64)
+    mse = lambda bits: float(((w - dequant(*api.quantize(oracle_lib, w, bits, 32, False), bits, 32)) ** 2).mean())
+    assert mse(8) < mse(4)
+    ramp = (np.arange(32, dtype=np.float32) - 16.0).reshape(1, 32)
+    packed, scales, mins = api.quantize(oracle_lib, ramp, 4, 32, True)
+    assert packed.shape == (1, 16) and mins is None
+    # scale = 16/7 rounded to f16; fields are round(x / scale) clamped to [-8, 7], low nibble first
+    sv = np.float32(np.float16(np.float32(16.0) / np.float32(7.0)))
+    want = np.clip(np.sign(ramp / sv) * np.floor(np.abs(ramp / sv) + np.float32(0.5)), -8, 7).astype(np.int32)[0] & 15
+    got = np.stack([packed[0] & 15, packed[0] >> 4], 1).reshape(-1)
+    np.testing.assert_array_equal(got, want)
+
+
+def operands(lib, g, m, n, k, bits, group, sym, act_dtype=api.F32, seed=0):
+    i = np.arange(n * k)
+    w = (((i * 13 % 97).astype(np.float32) / np.float32(97.0) - np.float32(0.5)) * np.float32(4.0)).reshape(n, k)
+    act = ((np.arange(m * k) * 7 % 53).astype(np.float32) / np.float32(53.0)).reshape(m, k)
+    packed, scales, mins = api.quantize(lib, w, bits, group, sym)
+    a = g.constant(act) if act_dtype == api.F32 else g.cast(g.constant(act), act_dtype)
+    qw, sc = g.constant(packed), g.constant(scales.view(np.uint16), api.F16)
+    mn = None if sym else g.constant(mins.view(np.uint16), api.F16)
+    return w, act, packed, scales, mins, g.quant_matmul(a, qw, sc, mn, bits, group)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("sym", [True, False])
+def test_op_matches_dequantised_matmul(oracle_lib, cpu, cpu64, bits, sym):
+    g = api.Graph(oracle_lib)
+    w, act, packed, scales, mins, out = operands(oracle_lib, g, 2, 3, 64, bits, 32, sym)
+    assert g.shape(out) == (2, 3) and g.dtype(out) == api.F32
+    wdq = dequant(packed, scales, mins, bits, 32)
+    want = act.astype(np.float64) @ wdq.astype(np.float64).T
+    got = cpu.eval(g, out).numpy()
+    assert np.abs(got - want).max() < 1e-3
+    np.testing.assert_allclose(cpu64.eval(g, out).numpy(), want, rtol=1e-12, atol=1e-12)
+    if bits == 4 and not sym:   # the reference's own figure: int4 stays within 15 % of the unquantised product
+        full = act @ w.T
+        assert np.abs(got - full).sum() / np.abs(full).sum() < 0.15
+
+
+def test_low_precision_activation_rounds_once(oracle_lib, cpu, cpu64):
+    g = api.Graph(oracle_lib)
+    *_, out = operands(oracle_lib, g, 4, 8, 128, 4, 64, False, act_dtype=api.BF16)
+    assert g.dtype(out) == api.BF16
+    got = api.bf16_to_f32(cpu.eval(g, out).numpy())
+    wide = cpu64.eval(g, out).numpy()
+    assert np.abs(got - wide).max() <= 2.0 ** -8 * np.abs(wide).max()
+
+
+def test_record_time_checks(oracle_lib):
+    g = api.Graph(oracle_lib)
+    a = g.input([2, 64], api.F32)
+    qw, sc = g.input([3, 32], api.U8), g.input([3, 2], api.F16)
+    assert g.shape(g.quant_matmul(a, qw, sc, None, 4, 32)) == (2, 3)
+    bad = [
+        (g.input([2, 64, 1], api.F32), qw, sc, None, 4, 32, "rank"),
+        (a, g.input([3, 32], api.I8), sc, None, 4, 32, "U8"),
+        (a, qw, g.input([3, 2], api.F32), None, 4, 32, "F16"),
+        (a, qw, sc, g.input([3, 2], api.BF16), 4, 32, "mins must be F16"),
+        (g.input([2, 64], api.I32), qw, sc, None, 4, 32, "float"),
+        (a, qw, sc, None, 3, 32, "bits"),
+        (a, qw, sc, None, 4, 48, "group_size"),
+        (a, qw, sc, None, 4, 0, "group_size"),
+        (a, g.input([3, 64], api.U8), sc, None, 4, 32, "qweight cols"),
+        (a, qw, g.input([3, 3], api.F16), None, 4, 32, "scales must have"),
+        (a, qw, sc, g.input([3, 4], api.F16), 4, 32, "mins must have"),
+    ]
+    for act, q, s, m, bits, grp, msg in bad:
+        with pytest.raises(api.Error, match=msg):
+            g.quant_matmul(act, q, s, m, bits, grp)
+
+
+def test_blob_round_trip_and_device_lowering(oracle_lib, cuda_lib, cpu):
+    g = api.Graph(oracle_lib)
+    *_, out = operands(oracle_lib, g, 2, 3, 64, 2, 32, False)
+    blob = g.serialize([out], reachable=True)
+    rg, entries = api.deserialize(oracle_lib, blob)
+    assert rg.serialize(entries[0][1]) == blob
+    np.testing.assert_array_equal(cpu.eval(rg, entries[0][1][0]).numpy(), cpu.eval(g, out).numpy())
+    # the CUDA library reads the same blob and compiles the lowering (no GPU needed)
+    cg, ce = api.deserialize(cuda_lib, blob)
+    fams = api.compile_check(cuda_lib, cg, ce[0][1])
+    assert fams and all(f in ("pointwise", "gemm_simt", "gemm_tc", "quant_gemv") for f in fams)
+    h = api.Graph(cuda_lib)
+    *_, big = operands(cuda_lib, h, 256, 512, 1024, 4, 128, True, act_dtype=api.BF16)
+    assert "gemm_tc" in api.compile_check(cuda_lib, h, [big])
