@@ -136,6 +136,41 @@ bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* sc
   return true;
 }
 
+extern const std::string kSrc_quant_gemv;
+
+bool quant_gemv_supported(DType act, int64_t m, int64_t n, int64_t k, int bits, int64_t group) {
+  if (std::getenv("KURUMI_NO_QUANT_GEMV")) return false;
+  if (!(act == DType::F32 || act == DType::BF16 || act == DType::F16)) return false;
+  const int64_t piece = 128 / bits;
+  return m >= 1 && m <= 8 && n >= 1 && k >= piece && (k * bits / 8) % 16 == 0 && (group % piece == 0 || piece % group == 0) && n < (int64_t(1) << 31) && k < (int64_t(1) << 31);
+}
+
+// slots are symbolic: -1 qweight, -2 scales, -3 mins (or scales again when symmetric), -4 act, -5 out
+bool build_quant_gemv(const KernelLoader& load, DType act, int64_t m, int64_t n, int64_t k, int bits, int64_t group, bool symmetric, int sm_count, Launch* out) {
+  if (!quant_gemv_supported(act, m, n, k, bits, group)) return false;
+  const int64_t piece = 128 / bits;
+  // a chunk of activation columns in shared memory: whole warp-wide strides of 32 pieces (the kernel's layout
+  // permutes columns inside such a stride), about 96 KB at most, never more than K rounded up to a stride
+  const int64_t stride = 32 * piece;
+  int64_t kc = std::max<int64_t>(stride, (96 * 1024) / (4 * m) / stride * stride);
+  kc = std::min<int64_t>(kc, (k + stride - 1) / stride * stride);
+  const int64_t rpw = m <= 2 ? 4 : 2;
+  std::string src = device_prelude() +
+                    defines({{"M", m}, {"N", n}, {"K", k}, {"BITS", bits}, {"GROUP", group}, {"SYM", symmetric ? 1 : 0},
+                             {"ACT", act == DType::F32 ? 0 : act == DType::BF16 ? 1 : 2}, {"KC", kc}, {"RPW", rpw}}) +
+                    kSrc_quant_gemv;
+  out->name = "quant_gemv";
+  out->kernel = load(src, "ku_quant_gemv", true);
+  const int64_t blocks = (n + 8 * rpw - 1) / (8 * rpw);
+  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(blocks, static_cast<int64_t>(sm_count) * 4));
+  out->block[0] = 256;
+  out->smem = static_cast<unsigned>(m * kc * 4);
+  for (int sidx = 1; sidx <= 5; ++sidx) { Arg a; a.kind = Arg::SlotPtr; a.slot = -sidx; out->args.push_back(a); }
+  out->algo_bytes = static_cast<double>(n * k * bits / 8 + n * (k / group) * 2 * (symmetric ? 1 : 2) + m * k * dtype_width(act) + m * n * dtype_width(act));
+  out->flops = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k);
+  return true;
+}
+
 extern const std::string kSrc_softmax_groups_tma;
 
 bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args, size_t* scratch_bytes, size_t* zero_bytes) {

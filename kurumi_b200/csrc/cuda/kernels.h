@@ -32,6 +32,11 @@ bool build_softmax_panels(const KernelLoader& load, const Fused& f, size_t axis,
 // scratch slot symbolic (-1) and `*scratch_bytes` set; the caller creates that slot.
 bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* scratch_bytes);
 
+// Quantised matmul for at most 8 activation rows, reading the packed weight directly (kernels/quant_gemv.cuh).
+// Slots are symbolic: -1 qweight, -2 scales, -3 mins (scales again when symmetric), -4 act, -5 out.
+bool quant_gemv_supported(DType act, int64_t m, int64_t n, int64_t k, int bits, int64_t group);
+bool build_quant_gemv(const KernelLoader& load, DType act, int64_t m, int64_t n, int64_t k, int bits, int64_t group, bool symmetric, int sm_count, Launch* out);
+
 // Fused causal / full attention with online softmax. Slots are symbolic: -1 q, -2 k, -3 v, -4 out.
 bool attention_supported(DType dt, const Shape& shape);
 bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, bool causal, float scale, int sm_count, Launch* out);

@@ -458,6 +458,32 @@ Fused Scheduler::quant_matmul(const Node& n, const std::vector<Fused>& in) {
   const size_t M = n.shape[0], N = n.shape[1], K = in[0].shape[1];
   const size_t per = 8 / op.bits, ng = K / op.group_size;
   const Shape nk{N, K};
+  // a few activation rows: one kernel that streams the packed weight once
+  if (quant_gemv_supported(n.dtype, static_cast<int64_t>(M), static_cast<int64_t>(N), static_cast<int64_t>(K), op.bits, static_cast<int64_t>(op.group_size))) {
+    const int slot = new_slot(Slot::Temp, n.dtype, n.shape);
+    auto plain = [](const Fused& f) {
+      if (!f.is_plain_buffer()) return false;
+      const View& v = f.root_leaf().view;
+      if (!v.guards.empty() || v.base != 0) return false;
+      const std::vector<size_t> rm = row_major_strides(v.shape);
+      for (size_t d = 0; d < rm.size(); ++d) if (v.shape[d] > 1 && v.stride[d] != static_cast<int64_t>(rm[d])) return false;
+      return true;
+    };
+    auto dense = [&](const Fused& f0) { Fused f = resolve_acc(f0); return plain(f) ? f : materialize(f); };   // a contiguous buffer of its own
+    Fused qw = dense(in[1]), sc = dense(in[2]), act = dense(in[0]);
+    Fused mn = op.symmetric ? sc : dense(in[3]);
+    if (plain(qw) && plain(sc) && plain(mn) && plain(act)) {
+      if (!dry()) {
+        Launch L;
+        if (!build_quant_gemv(*load_, n.dtype, static_cast<int64_t>(M), static_cast<int64_t>(N), static_cast<int64_t>(K), op.bits, static_cast<int64_t>(op.group_size), op.symmetric, sm_, &L))
+          throw Error::backend("internal: quantised gemv kernel rejected a supported shape");
+        const int slots[5] = {qw.root_leaf().slot, sc.root_leaf().slot, mn.root_leaf().slot, act.root_leaf().slot, slot};
+        for (auto& a : L.args) if (a.kind == Arg::SlotPtr && a.slot < 0) a.slot = slots[-a.slot - 1];
+        prog_.launches.push_back(std::move(L));
+      }
+      return buffer_value(slot, n.dtype, n.shape);
+    }
+  }
   // byte of column c: packed[n][c / per]
   Fused q = view_step(OpKind::Reshape, resolve_acc(in[1]), {N, K / per, 1});
   q = view_step(OpKind::Expand, q, {N, K / per, per});
