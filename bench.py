@@ -32,10 +32,11 @@ from kurumi_b200 import api, build, configs  # noqa: E402
 # from one ncu capture per kernel at the full workload size; the captures are summarised under profiles/.
 NCU_TRAFFIC = {
     ("c1_fused_reduce", "reduce_rows"): 137.8e6,
+    ("c2_transposed_softmax", "softmax_groups_tma"): 481.4e6,
     ("c2_transposed_softmax", "softmax_panels_tma"): 535.7e6,
-    ("c3_gemm_bias_gelu", "gemm_tc"): 1094e6,
-    ("c4_causal_attention", "attention_tc"): 1057e6,
-    ("c5_fp8_weight_gemm", "gemm_tc_f8"): 2958e6,
+    ("c3_gemm_bias_gelu", "gemm_tc"): 1231e6,
+    ("c4_causal_attention", "attention_tc"): 1056e6,
+    ("c5_fp8_weight_gemm", "gemm_tc_f8"): 3556e6,
 }
 
 WORKLOADS = {
