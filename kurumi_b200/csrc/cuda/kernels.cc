@@ -363,7 +363,7 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   out->kernel = load(src, "ku_attention_tc", true);
   out->grid[0] = static_cast<unsigned>((s + 127) / 128);
   out->grid[1] = static_cast<unsigned>(bh);
-  out->block[0] = 192;
+  out->block[0] = 320;   // TMA warp, MMA warp, 8 softmax warps
   const int64_t tile = 128 * 128 * (dh / 64);
   out->smem = static_cast<unsigned>(std::max<int64_t>(5 * tile + 128 * 128 * 2 + 1024, 120 * 1024));
   for (int slot = -1; slot >= -3; --slot) {

@@ -8,8 +8,10 @@
 //   warp 0      TMA producer: Q once, then K_j / V_j (cp.async.bulk.tensor, SWIZZLE_128B, no multicast)
 //   warp 1      tcgen05.mma issuer: S_j = Q K_j^T into one of two TMEM score buffers (so the scores of
 //               block j+1 are computed while block j is in the softmax), then O += P_j V_j
-//   warps 2..5  one query row per thread: tcgen05.ld the scores, maximum / sum in the log2 domain, P_j as
-//               bf16 into shared memory in the swizzled K-major layout the second MMA reads. O accumulates
+//   warps 2..9  softmax, two threads per query row (one per half of the key block, so that two warps per
+//               scheduler hide each other's latencies): tcgen05.ld the scores, maximum (exchanged through
+//               shared memory inside the warp pair) / sum in the log2 domain, P_j as bf16 into shared
+//               memory in the swizzled K-major layout the second MMA reads. O accumulates
 //               in tensor memory across key blocks; the threads rescale it (tcgen05.ld / st) only when a
 //               row's maximum has grown by more than 2^8 since the scale it was accumulated with
 // Causal: key blocks above the diagonal are never loaded; the diagonal block is masked per element.
@@ -93,12 +95,13 @@ __device__ __forceinline__ unsigned ku_pack2(float lo, float hi) {
 #endif
 }
 
-extern "C" __global__ void __launch_bounds__(192, 1)
+extern "C" __global__ void __launch_bounds__(320, 1)
 ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ KuTmap tmap_k, const __grid_constant__ KuTmap tmap_v, void* __restrict__ Op,
                 int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_ready, o_full;
   __shared__ unsigned tmem_base_slot;
+  __shared__ float x_max[2][2][128], x_sum[2][128];   // [block parity][column half][row], [column half][row]
   unsigned char* smem = smem_raw + ((1024u - (ku_smem(smem_raw) & 1023u)) & 1023u);
   const unsigned q_s = ku_smem(smem), k_s = q_s + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES, p_s = v_s + 2 * TILE_BYTES;
   unsigned char* p_tile = smem + 5 * TILE_BYTES;
@@ -112,9 +115,9 @@ ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ K
     ku_mbar_init(ku_smem(&q_full), 1);
     for (int i = 0; i < 2; ++i) {
       ku_mbar_init(ku_smem(&k_full[i]), 1); ku_mbar_init(ku_smem(&k_empty[i]), 1); ku_mbar_init(ku_smem(&v_full[i]), 1); ku_mbar_init(ku_smem(&v_empty[i]), 1);
-      ku_mbar_init(ku_smem(&s_full[i]), 1); ku_mbar_init(ku_smem(&s_free[i]), 128);
+      ku_mbar_init(ku_smem(&s_full[i]), 1); ku_mbar_init(ku_smem(&s_free[i]), 256);
     }
-    ku_mbar_init(ku_smem(&p_ready), 128); ku_mbar_init(ku_smem(&o_full), 1);
+    ku_mbar_init(ku_smem(&p_ready), 256); ku_mbar_init(ku_smem(&o_full), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -175,92 +178,107 @@ ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ K
         ku_mma_commit(ku_smem(&v_empty[st]));
       }
     }
-  } else {  // ---- softmax + accumulate: one query row per thread ----
-    const int q4 = warp & 3;
+  } else {  // ---- softmax: eight warps; a query row is shared by two threads, one per half of the key block ----
+    const int q4 = warp & 3;                      // the TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;             // key columns [64 half, 64 half + 64) of every block, head-dim columns [DH/2 half, ...) of O
     const int r = q4 * 32 + lane;                 // row of the tile == TMEM lane
     const int qrow = qb * BQ + r;
     const unsigned lane_addr = tmem_base + ((unsigned)(q4 * 32) << 16);
+    const unsigned pair_bar = 1 + q4;             // named barrier of the two warps that share these 32 rows
+    constexpr int HK = BKV / 2, HD = DH / 2;
     // m is the reference maximum the accumulator O (in tensor memory) and the sum l are scaled by. It follows
     // the running maximum lazily: only when a block's maximum exceeds it by more than 2^8 are O and l rescaled,
     // so most blocks touch O with the tensor core alone (probabilities stay below 2^8, accumulation is f32).
-    float m = -KU_INF, l = 0.0f;
+    float m = -KU_INF, l = 0.0f;   // l: this thread's share (its half of the keys)
     for (int j = 0; j < nkv; ++j) {
       const int st = j & 1;
       ku_wait(ku_smem(&s_full[st]), (j >> 1) & 1, failed, status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool need_mask = (CAUSAL && j == qb) || (j * BKV + BKV > S);
-      // the row's scores of this block, in log2 units, masked keys at -inf
-      float sc[BKV];
+      // this thread's half of the row's scores, in log2 units, masked keys at -inf
+      float sc[HK];
 #pragma unroll
-      for (int c0 = 0; c0 < BKV; c0 += 32) ku_tmem_ld32(lane_addr + st * 128 + c0, sc + c0);
+      for (int c0 = 0; c0 < HK; c0 += 32) ku_tmem_ld32(lane_addr + st * 128 + half * HK + c0, sc + c0);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       ku_mbar_arrive(ku_smem(&s_free[st]));                          // the score buffer may be overwritten
       float bm = -KU_INF;
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < BKV; ++c) {
-          const int key = j * BKV + c;
+        for (int c = 0; c < HK; ++c) {
+          const int key = j * BKV + half * HK + c;
           sc[c] = ((CAUSAL && key > qrow) || key >= S) ? -KU_INF : sc[c] * SCALE_LOG2E;
           bm = fmaxf(bm, sc[c]);
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < BKV; ++c) { sc[c] *= SCALE_LOG2E; bm = fmaxf(bm, sc[c]); }
+        for (int c = 0; c < HK; ++c) { sc[c] *= SCALE_LOG2E; bm = fmaxf(bm, sc[c]); }
       }
-      // the previous block's P V product must have retired before P is overwritten or O is touched
+      // the row maximum over both halves (double-buffered by block parity: a fast thread may be a block ahead)
+      x_max[j & 1][half][r] = bm;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      bm = fmaxf(bm, x_max[j & 1][half ^ 1][r]);
+      const bool grow = bm > m + 8.0f || (m == -KU_INF && bm != -KU_INF);
+      const bool any_grow = __any_sync(0xffffffffu, grow);
+      const float alpha = grow ? ku_ex2(m - bm) : 1.0f;   // 0 for a row's first finite block: O holds nothing for it yet
+      if (grow) m = bm;
+      const float mref = (m == -KU_INF) ? 0.0f : m;   // a row with nothing finite so far: exp2(-inf - 0) = 0
+      // the probabilities, packed 8 keys = one 16-byte chunk at a time, while the previous block's P V product still runs
+      float bs = 0.0f;
+      uint4 pk[HK / 8];
+#pragma unroll
+      for (int c0 = 0; c0 < HK; c0 += 8) {
+        float e[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) { e[c] = ku_ex2(sc[c0 + c] - mref); bs += e[c]; }
+        pk[c0 >> 3].x = ku_pack2(e[0], e[1]); pk[c0 >> 3].y = ku_pack2(e[2], e[3]);
+        pk[c0 >> 3].z = ku_pack2(e[4], e[5]); pk[c0 >> 3].w = ku_pack2(e[6], e[7]);
+      }
+      // that product must have retired before P is overwritten or O is touched
       if (j > 0) {
         ku_wait(ku_smem(&o_full), (j - 1) & 1, failed, status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       }
-      const bool grow = bm > m + 8.0f || (m == -KU_INF && bm != -KU_INF);
-      if (__any_sync(0xffffffffu, grow)) {   // tensor-memory loads and stores are warp-wide: rows that keep their reference scale by 1
-        const float alpha = grow ? ku_ex2(m - bm) : 1.0f;   // 0 for a row's first finite block: O holds nothing for it yet
+      if (any_grow) {   // tensor-memory loads and stores are warp-wide: rows that keep their reference scale by 1
         if (j > 0) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < DH; c0 += 32) {
+          for (int c0 = 0; c0 < HD; c0 += 32) {   // this thread's half of the head dimension
             float v[32];
-            ku_tmem_ld32(lane_addr + 256 + c0, v);
+            ku_tmem_ld32(lane_addr + 256 + half * HD + c0, v);
 #pragma unroll
             for (int c = 0; c < 32; ++c) v[c] *= alpha;
-            ku_tmem_st32(lane_addr + 256 + c0, v);
+            ku_tmem_st32(lane_addr + 256 + half * HD + c0, v);
           }
         }
         l *= alpha;
-        if (grow) m = bm;
       }
-      const float mref = (m == -KU_INF) ? 0.0f : m;   // a row with nothing finite so far: exp2(-inf - 0) = 0
-      float bs = 0.0f;
+      // as bf16 in the swizzled K-major tile; the half IS the 64-key (128-byte) chunk of the P tile
 #pragma unroll
-      for (int c0 = 0; c0 < BKV; c0 += 8) {   // 8 keys = one 16-byte chunk of the row, as bf16 in the swizzled K-major tile
-        float e[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) { e[c] = ku_ex2(sc[c0 + c] - mref); bs += e[c]; }
-        uint4 pk;
-        pk.x = ku_pack2(e[0], e[1]); pk.y = ku_pack2(e[2], e[3]); pk.z = ku_pack2(e[4], e[5]); pk.w = ku_pack2(e[6], e[7]);
-        const int chunk16 = (c0 & 63) >> 3;
-        *(uint4*)(p_tile + (c0 >> 6) * 16384 + r * 128 + ((chunk16 ^ (r & 7)) << 4)) = pk;
-      }
+      for (int ch = 0; ch < HK / 8; ++ch) *(uint4*)(p_tile + half * 16384 + r * 128 + ((ch ^ (r & 7)) << 4)) = pk[ch];
       l += bs;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core (async proxy)
       ku_mbar_arrive(ku_smem(&p_ready));
     }
-    // the last product, then this row of O
-    float o[DH];
+    // the row's sum over both halves
+    x_sum[half][r] = l;
+    asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+    l += x_sum[half ^ 1][r];
+    // the last product, then this thread's half of the row of O
+    float o[HD];
     if (nkv > 0) {
       ku_wait(ku_smem(&o_full), (nkv - 1) & 1, failed, status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int c0 = 0; c0 < DH; c0 += 32) ku_tmem_ld32(lane_addr + 256 + c0, o + c0);
+      for (int c0 = 0; c0 < HD; c0 += 32) ku_tmem_ld32(lane_addr + 256 + half * HD + c0, o + c0);
     } else {
 #pragma unroll
-      for (int c = 0; c < DH; ++c) o[c] = 0.0f;
+      for (int c = 0; c < HD; ++c) o[c] = 0.0f;
     }
     if (qrow < S) {
       const float inv = 1.0f / l;
-      uint4* dst = (uint4*)((unsigned short*)Op + ((i64)bh * S + qrow) * DH);
+      uint4* dst = (uint4*)((unsigned short*)Op + ((i64)bh * S + qrow) * DH + half * HD);
 #pragma unroll
-      for (int g = 0; g < DH / 8; ++g) {
+      for (int g = 0; g < HD / 8; ++g) {
         uint4 pk;
         pk.x = ku_pack2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv); pk.y = ku_pack2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
         pk.z = ku_pack2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv); pk.w = ku_pack2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);

@@ -50,16 +50,22 @@ ku_quant_gemv(const u8* __restrict__ qw, const u16* __restrict__ scales, const u
         a_s[m * KC + blkc * (32 * PIECE) + (within % PIECE) * 32 + within / PIECE] = ku_act_at(act, (size_t)m * K + kc0 + c);
       }
       __syncthreads();
+      // the pieces of all RPW rows at a stride position are loaded before any is used, and two stride positions
+      // are unrolled: 2 * RPW 16-byte loads in flight per lane keep HBM busy
+#pragma unroll 2
+      for (int b = lane * 16, blkc = 0; b < kc * BITS / 8; b += 32 * 16, ++blkc) {
+        uint4 pks[RPW];
 #pragma unroll
-      for (int r = 0; r < RPW; ++r) {
-        const int n = n0 + r;
-        if (n >= N) continue;
-        const u8* row = qw + (size_t)n * RB + (size_t)kc0 * BITS / 8;
-        for (int b = lane * 16, blkc = 0; b < kc * BITS / 8; b += 32 * 16, ++blkc) {
-          const uint4 pk = *(const uint4*)(row + b);
-          const unsigned wds[4] = {pk.x, pk.y, pk.z, pk.w};
-          const int c0 = b * 8 / BITS;   // first column of the piece inside the chunk
-          const float* ap = a_s + blkc * (32 * PIECE) + lane;   // this lane's column f of the block is ap[f * 32]
+        for (int r = 0; r < RPW; ++r) {
+          const int n = (n0 + r) < N ? (n0 + r) : (N - 1);   // rows past the end re-read the last row; their results are dropped
+          pks[r] = *(const uint4*)(qw + (size_t)n * RB + (size_t)kc0 * BITS / 8 + b);
+        }
+        const int c0 = b * 8 / BITS;   // first column of the piece inside the chunk
+        const float* ap = a_s + blkc * (32 * PIECE) + lane;   // this lane's column f of the block is ap[f * 32]
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+          const int n = (n0 + r) < N ? (n0 + r) : (N - 1);
+          const unsigned wds[4] = {pks[r].x, pks[r].y, pks[r].z, pks[r].w};
 #pragma unroll
           for (int sb = 0; sb < PIECE / SUB; ++sb) {
             const int gi = (kc0 + c0 + sb * SUB) / GROUP;
@@ -81,10 +87,11 @@ ku_quant_gemv(const u8* __restrict__ qw, const u16* __restrict__ scales, const u
             for (int j = 0; j < SUB; ++j) {
               const int f = sb * SUB + j;                      // field index inside the piece
               const unsigned raw = (wds[(f * BITS) >> 5] >> ((f * BITS) & 31)) & ((1u << BITS) - 1u);
+              // integer -> float without the quarter-rate conversion instruction: 2^23 + v has v in its low mantissa bits
 #if SYM
-              const float q = (float)((int)(raw << (32 - BITS)) >> (32 - BITS));
+              const float q = __uint_as_float(0x4B000000u | (raw ^ (1u << (BITS - 1)))) - (8388608.0f + (float)(1u << (BITS - 1)));   // the sign-extended field
 #else
-              const float q = (float)raw;
+              const float q = __uint_as_float(0x4B000000u | raw) - 8388608.0f;
 #endif
 #pragma unroll
               for (int m = 0; m < M; ++m) {
