@@ -75,6 +75,17 @@ __device__ __forceinline__ void ku_tmem_ld32(unsigned taddr, float* v) {
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// the same load without the wait: several can be in flight before one tcgen05.wait::ld
+__device__ __forceinline__ void ku_tmem_ld32_nowait(unsigned taddr, float* v) {
+  unsigned* r = (unsigned*)v;
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+      "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+        "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+        "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
 __device__ __forceinline__ void ku_tmem_st32(unsigned taddr, const float* v) {
   const unsigned* r = (const unsigned*)v;
   asm volatile(
@@ -134,15 +145,22 @@ ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ K
     if (lane == 0) {  // ---- TMA producer ----
       ku_mbar_expect(ku_smem(&q_full), TILE_BYTES);
       for (int c = 0; c < DCH; ++c) ku_tma_3d(q_s + c * 16384, &tmap_q, c * 64, qb * BQ, bh, ku_smem(&q_full));
-      for (int j = 0; j < nkv; ++j) {
+      // K runs a block ahead of V: K_{j+2} only needs S_j to have retired (early), V_j needs P_{j-2} V_{j-2} to have
+      // retired (late); loading them in lock step would hold every K load back behind a V wait
+      auto load_k = [&](int j) {
         const int st = j & 1;
-        const unsigned ph = (j >> 1) & 1;
-        ku_wait(ku_smem(&k_empty[st]), ph ^ 1, failed, status);
+        ku_wait(ku_smem(&k_empty[st]), ((j >> 1) & 1) ^ 1, failed, status);
         ku_mbar_expect(ku_smem(&k_full[st]), TILE_BYTES);
         for (int c = 0; c < DCH; ++c) ku_tma_3d(k_s + st * TILE_BYTES + c * 16384, &tmap_k, c * 64, j * BKV, bh, ku_smem(&k_full[st]));
-        ku_wait(ku_smem(&v_empty[st]), ph ^ 1, failed, status);
+      };
+      if (nkv > 0) load_k(0);
+      if (nkv > 1) load_k(1);
+      for (int j = 0; j < nkv; ++j) {
+        const int st = j & 1;
+        ku_wait(ku_smem(&v_empty[st]), ((j >> 1) & 1) ^ 1, failed, status);
         ku_mbar_expect(ku_smem(&v_full[st]), TILE_BYTES);
         for (int c = 0; c < DCH; ++c) ku_tma_3d(v_s + st * TILE_BYTES + c * 16384, &tmap_v, c * 64, j * BKV, bh, ku_smem(&v_full[st]));
+        if (j + 2 < nkv) load_k(j + 2);
       }
     }
   } else if (warp == 1) {
@@ -198,7 +216,10 @@ ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ K
       // this thread's half of the row's scores, in log2 units, masked keys at -inf
       float sc[HK];
 #pragma unroll
-      for (int c0 = 0; c0 < HK; c0 += 32) ku_tmem_ld32(lane_addr + st * 128 + half * HK + c0, sc + c0);
+      for (int c0 = 0; c0 < HK; c0 += 32) ku_tmem_ld32_nowait(lane_addr + st * 128 + half * HK + c0, sc + c0);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < HK; ++c) asm volatile("" : "+f"(sc[c]));   // the values may only be read after the wait: tie every register to this point
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       ku_mbar_arrive(ku_smem(&s_free[st]));                          // the score buffer may be overwritten
       float bm = -KU_INF;
