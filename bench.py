@@ -10,6 +10,12 @@ view, f32 [8192, 8192] + bias): the metric is achieved HBM GB/s = algorithmic by
 one read of the bias, one write of the output) / device time. With N > 1 every rank evaluates its
 own shard of an N-times larger batch (weak scaling, no data-path collective); the value is the
 sum over ranks divided by the slowest rank's time. One JSON line is printed by rank 0.
+
+`e2e` is the same metric with every input in pinned host memory and the result read back to pinned host
+memory inside the timed region, through the library's public calls: the evaluation is cut into chunks of
+independent output rows (kurumi_b200/pipeline.py) so that uploads, kernels and downloads overlap; the
+chunked result is compared with the single evaluation byte for byte. Inputs smaller than a few L2s are
+rotated through copies so that no step finds them cached.
 """
 from __future__ import annotations
 
@@ -37,6 +43,17 @@ NCU_TRAFFIC = {
     ("c3_gemm_bias_gelu", "gemm_tc"): 1231e6,
     ("c4_causal_attention", "attention_tc"): 1056e6,
     ("c5_fp8_weight_gemm", "gemm_tc_f8"): 3556e6,
+}
+
+# how a workload's evaluation is cut into chunks of independent output rows for the end-to-end measurement:
+# chunk count, the builder arguments of one chunk, and per input (in the builder's order) the axis it is
+# sharded along (None = every chunk needs all of it)
+CHUNKING = {
+    "c1_fused_reduce": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, rows=kw["rows"] // c), "axes": [0, 0]},
+    "c2_transposed_softmax": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, lines=kw["n"] // c), "axes": [1, None]},
+    "c3_gemm_bias_gelu": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, m=kw["m"] // c), "axes": [0, None, None]},
+    "c4_causal_attention": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, batch=kw["batch"] // c), "axes": [0, 0, 0]},
+    "c5_fp8_weight_gemm": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, m=kw["m"] // c), "axes": [0, None, None]},
 }
 
 WORKLOADS = {
@@ -323,16 +340,31 @@ def main():
             host_in[node] = (hb, d.shape, d.dtype)
         out0 = step()
         host_out = torch.empty(out0.nbytes, dtype=torch.uint8).pin_memory()
-        out_bytes = out0.nbytes
+        out_bytes, out0_shape = out0.nbytes, tuple(out0.shape)
         out0.free()
 
-        def e2e_step():
+        def serial_step():
             ups = {node: gpu.upload_ptr(hb.data_ptr(), hb.numel(), shape, dt) for node, (hb, shape, dt) in host_in.items()}
             o = gpu.eval_device(g, [root], None, ups)[0]
             o.download_into(host_out.data_ptr(), out_bytes)   # waits for the result
             o.free()
             for u in ups.values():
                 u.free()
+
+        # the same step chunk by chunk over the independent output rows, uploads, kernels and downloads overlapped
+        pipe, e2e_method = None, "one upload of every input, one evaluation, one download"
+        plan = CHUNKING.get(name)
+        if plan is not None and args.scale == 1.0:
+            from kurumi_b200 import pipeline
+            chunks, chunk_kw, axes = plan["chunks"], plan["chunk_kw"](kw, plan["chunks"]), plan["axes"]
+            gch = api.Graph(lib)
+            root_ch, gens_ch = builder(gch, **chunk_kw)
+            inputs = [pipeline.HostInput(node_ch, host_in[node][0].data_ptr(), tuple(host_in[node][1]), host_in[node][2], axes[i])
+                      for i, (node, node_ch) in enumerate(zip(dev_in, gens_ch))]
+            out_rows = out0_shape[0]
+            pipe = pipeline.RowPipeline(gpu, gch, root_ch, inputs, host_out.data_ptr(), out_rows, out_bytes // out_rows, chunks)
+            e2e_method = f"{chunks} chunks of output rows; host-to-device copies, evaluations (ku_cuda_eval_device) and device-to-host copies overlapped on three streams"
+        e2e_step = pipe.step if pipe is not None else serial_step
         n_e2e = max(3, min(args.steps, 10))
         for _ in range(2):
             e2e_step()
@@ -348,7 +380,15 @@ def main():
         dt = float(tt.item())
         ev = world * (nbytes / dt / 1e9 if kind == "hbm" else flops / dt / 1e12)
         e2e = {"value": ev, "unit": unit, "h2d_bytes_per_step": int(sum(hb.numel() for hb, _, _ in host_in.values())), "d2h_bytes_per_step": int(out_bytes),
-               "ms_per_step": dt * 1e3, "timing": "host wall clock around upload + eval + download (download waits for the device)", "steps": n_e2e}
+               "ms_per_step": dt * 1e3, "timing": "host wall clock around upload + eval + download (download waits for the device)", "steps": n_e2e,
+               "method": e2e_method}
+        if pipe is not None:   # the result of the chunked step is the result of the single evaluation
+            ref_out = step()
+            check = torch.empty(out_bytes, dtype=torch.uint8).pin_memory()
+            ref_out.download_into(check.data_ptr(), out_bytes)
+            ref_out.free()
+            e2e["matches_single_evaluation"] = bool(torch.equal(check, host_out))
+            pipe.close()
 
     # N > 1: gathering the ranks' output shards into one tensor on every GPU is NOT on the data path that
     # `value` times (shards stay device-resident); its cost is reported beside it

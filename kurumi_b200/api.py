@@ -23,6 +23,12 @@ DTYPES = ["BOOL", "U8", "U16", "U32", "U64", "I8", "I16", "I32", "I64", "F8E4M3"
           "F64", "C64", "C128"]
 (BOOL, U8, U16, U32, U64, I8, I16, I32, I64, F8E4M3, F8E5M2, F16, BF16, F32, F64, C64, C128) = range(17)
 WIDTH = [1, 1, 2, 4, 8, 1, 2, 4, 8, 1, 1, 2, 2, 4, 8, 8, 16]
+
+
+def dtype_width(dtype: int) -> int:
+    """Bytes per element of a KuDType index."""
+    return WIDTH[dtype]
+
 # numpy carrier per dtype: narrow floats travel as their raw bit patterns
 _NP = {BOOL: np.uint8, U8: np.uint8, U16: np.uint16, U32: np.uint32, U64: np.uint64, I8: np.int8, I16: np.int16,
        I32: np.int32, I64: np.int64, F8E4M3: np.uint8, F8E5M2: np.uint8, F16: np.float16, BF16: np.uint16,

@@ -48,15 +48,17 @@ def fused_reduce(g: api.Graph, rows=4096, cols=4096):
     return out, gens
 
 
-def transposed_softmax(g: api.Graph, n=8192):
-    """Config 2: softmax over axis 0 of L (rows of L^T) after adding a broadcast bias, f32."""
-    L, bias = g.input([n, n], api.F32), g.input([n], api.F32)
+def transposed_softmax(g: api.Graph, n=8192, lines=None):
+    """Config 2: softmax over axis 0 of L (rows of L^T) after adding a broadcast bias, f32. `lines` (default n)
+    is the number of columns of L, i.e. of softmax lines: a column slab of the square problem."""
+    lines = n if lines is None else lines
+    L, bias = g.input([n, lines], api.F32), g.input([n], api.F32)
     lt = g.permute(L, [1, 0])
-    out = g.softmax(g.add(lt, g.broadcast_to(bias, [n, n])), 1)
+    out = g.softmax(g.add(lt, g.broadcast_to(bias, [lines, n])), 1)
     k = split_n(1, 2)
 
     def gen_l(h):
-        z = h.randn([n, n], k[0])
+        z = h.randn([n, lines], k[0])
         return h.mul(z, h.scalar(z, 2.0))
     gens = {L: gen_l, bias: lambda h: h.rand_range([n], k[1], -1.0, 1.0)}
     return out, gens

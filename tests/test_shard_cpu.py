@@ -75,3 +75,26 @@ def test_two_rank_sharded_evaluation_equals_unsharded(tmp_path, oracle_lib, cpu,
     sm = g2.softmax(g2.add(xs, g2.broadcast_to(bias, [rows, cols])), 1)
     want2 = cpu.eval_with(g2, sm, api.Feeds(oracle_lib).set(xs, x).set(bias, y[0])).numpy()
     assert np.array_equal(np.load(tmp_path / "softmax.npy"), want2)
+
+
+def test_chunk_plans_of_the_bench_build_row_slices(oracle_lib):
+    """The end-to-end measurement cuts every workload into chunks of independent output rows: the chunk graph's
+    result is exactly one chunk of rows of the full result, and its sharded inputs are one chunk of theirs."""
+    import bench
+    from kurumi_b200 import api
+    for name, plan in bench.CHUNKING.items():
+        builder, kw, _ = bench.WORKLOADS[name]
+        small = {k: (v // 8 if isinstance(v, int) and v >= 1024 else v) for k, v in kw.items()}   # same structure, cheaper to record
+        c = plan["chunks"]
+        gf, gc = api.Graph(oracle_lib), api.Graph(oracle_lib)
+        rf, gens_f = builder(gf, **small)
+        rc, gens_c = builder(gc, **plan["chunk_kw"](small, c))
+        sf, sc = gf.shape(rf), gc.shape(rc)
+        assert sc[0] * c == sf[0] and sc[1:] == sf[1:], name
+        assert len(plan["axes"]) == len(gens_f) == len(gens_c)
+        for (nf, nc, axis) in zip(gens_f, gens_c, plan["axes"]):
+            a, b = gf.shape(nf), gc.shape(nc)
+            if axis is None:
+                assert a == b, name
+            else:
+                assert b[axis] * c == a[axis] and all(x == y for i, (x, y) in enumerate(zip(a, b)) if i != axis), name
