@@ -181,24 +181,26 @@ bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis,
   LineLeaf big;
   if (!emit_line_source_fn(f, axis, &src_fn, leaf_args, &R, &C, &transposed, &big) || !transposed || big.leaf < 0) return false;
   auto env = [](const char* name, int64_t dflt) { const char* e = std::getenv(name); return e ? static_cast<int64_t>(std::atoi(e)) : dflt; };
-  const int64_t p = 16, nt = 512, nw = nt / 32;
-  if (sm_count < p || R < 32 * 8 || C < 1024 || R * C < (int64_t(1) << 22) || R >= (int64_t(1) << 30) || C >= (int64_t(1) << 30)) return false;
+  // slabs of 32 lines (128-byte tile rows); slabs of 16 (64-byte rows, 256-thread CTAs, twice the groups) measured 7 % slower
+  const int64_t lw = env("KURUMI_SMG_LW", 32) == 16 ? 16 : 32;
+  const int64_t p = 16, nt = lw == 32 ? 512 : 256, nw = nt / 32, rsn = 128 / lw;
+  if (sm_count < p || R < lw * 8 || C < 1024 || R * C < (int64_t(1) << 22) || R >= (int64_t(1) << 30) || C >= (int64_t(1) << 30) || (big.base * 4) % 16 != 0) return false;
   int64_t cj = (C + p - 1) / p;
-  cj = (cj + 4 * nw - 1) / (4 * nw) * (4 * nw);      // every warp gets a multiple of four tile rows
+  cj = (cj + rsn * nw - 1) / (rsn * nw) * (rsn * nw);      // every warp gets whole groups of tile rows (rsn * nw = 64: also whole 32-position strips)
   int64_t nbuf = std::min<int64_t>(4, std::max<int64_t>(1, env("KURUMI_SMG_NBUF", 1)));
-  while (nbuf > 1 && nbuf * cj * 128 + 1024 > 220 * 1024) --nbuf;
-  if (nbuf * cj * 128 + 1024 > 220 * 1024) return false;   // lines too long for a ring of tiles in shared memory
-  const int64_t boxj = cj % 256 == 0 ? 256 : cj % 128 == 0 ? 128 : 64;
-  const int64_t slabs = (R + 31) / 32;
+  while (nbuf > 1 && nbuf * cj * lw * 4 + 1024 > 220 * 1024) --nbuf;
+  if (nbuf * cj * lw * 4 + 1024 > 220 * 1024) return false;   // lines too long for a ring of tiles in shared memory
+  const int64_t boxj = cj % 256 == 0 ? 256 : cj % 128 == 0 ? 128 : cj % 64 == 0 ? 64 : 32;
+  const int64_t slabs = (R + lw - 1) / lw;
   std::string src = device_prelude() + src_fn +
-                    defines({{"R", R}, {"C", C}, {"P", p}, {"CJ", cj}, {"BOXJ", boxj}, {"NBUF", nbuf}, {"NT", nt}, {"NSLABS", slabs}, {"KU_OUT_F32", 1},
+                    defines({{"R", R}, {"C", C}, {"LW", lw}, {"P", p}, {"CJ", cj}, {"BOXJ", boxj}, {"NBUF", nbuf}, {"NT", nt}, {"NSLABS", slabs}, {"KU_OUT_F32", 1},
                              {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
                     kSrc_softmax_groups_tma;
   out->name = "softmax_groups_tma";
   out->kernel = load(src, "ku_softmax_groups_tma", false);
-  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(slabs, 4 * sm_count / p) * p);
+  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(slabs, 8 * sm_count / p) * p);
   out->block[0] = static_cast<unsigned>(nt);
-  out->smem = static_cast<unsigned>(nbuf * cj * 128 + 1024);   // 1024 bytes of slack: the ring is placed on a 1024-byte boundary
+  out->smem = static_cast<unsigned>(nbuf * cj * lw * 4 + 1024);   // 1024 bytes of slack: the ring is placed on a 1024-byte boundary
   out->persistent_clusters = -1;                               // cap the grid at the co-resident CTA count on first launch,
   out->grid_multiple = static_cast<unsigned>(p);               // in whole groups,
   out->cooperative = true;                                     // and have the driver hold the launch to it
@@ -210,11 +212,11 @@ bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis,
   tm.tm.rank = 2;
   tm.tm.dims[0] = static_cast<uint64_t>(R); tm.tm.dims[1] = static_cast<uint64_t>(C);
   tm.tm.strides[0] = static_cast<uint64_t>(big.ld) * 4;
-  tm.tm.box[0] = 32; tm.tm.box[1] = static_cast<uint32_t>(boxj);
-  tm.tm.swz = CU_TENSOR_MAP_SWIZZLE_128B;
+  tm.tm.box[0] = static_cast<uint32_t>(lw); tm.tm.box[1] = static_cast<uint32_t>(boxj);
+  tm.tm.swz = lw == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   out->args.push_back(tm);
   *zero_bytes = static_cast<size_t>((slabs * 4 + 255) / 256 * 256);   // the per-slab counters
-  *scratch_bytes = *zero_bytes + static_cast<size_t>(slabs * p * 32 * 8);
+  *scratch_bytes = *zero_bytes + static_cast<size_t>(slabs * p * lw * 8);
   return true;
 }
 

@@ -15,11 +15,15 @@
 // and the neighbours on the SM fill the waits; with a deeper ring step 2 of a slab runs after step 1 of the next.
 // Every wait is bounded: a CTA that gives up records it in *status and carries on.
 //
-// Spliced in by the host: R, C, P, CJ (multiple of 4 * NT / 32), BOXJ, NBUF, NT, NSLABS, KU_OUT_F32, KU_SRC_IDENTITY and
+// Spliced in by the host: R, C, LW (lines per slab: 32 or 16), P, CJ (multiple of (128 / LW) * NT / 32), BOXJ, NBUF, NT, NSLABS,
+// KU_OUT_F32, KU_SRC_IDENTITY and
 //   float ku_src_t(float lval, idx i, idx j KU_SRC_PARAMS) - the fused producer given the loaded value.
 #define NW (NT / 32)
+#define ROWB (LW * 4)          /* bytes of a tile row: LW lines at one position */
+#define CHUNKS (LW / 4)        /* 16-byte chunks (4 lines) per tile row */
+#define RSN (32 / CHUNKS)      /* tile rows a warp reads with one 16-byte load per lane */
 #define KU_LOG2E 1.4426950408889634f
-#define TILE_BYTES (CJ * 128)
+#define TILE_BYTES (CJ * ROWB)
 #define SPIN_LIMIT (1u << 22)
 #define RPW (CJ / NW)   /* tile rows per warp */
 #if KU_OUT_F32
@@ -32,6 +36,15 @@ struct alignas(64) KuTmap { unsigned long long opaque[16]; };
 
 __device__ __forceinline__ float ku_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ unsigned ku_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+// byte offset of 16-byte chunk q (lines 4q .. 4q+3) of tile row jj: rows are ROWB bytes, swizzled as the TMA wrote them
+// (128-byte rows: chunk ^ (row & 7); 64-byte rows: chunk ^ ((row >> 1) & 3))
+__device__ __forceinline__ unsigned ku_chunk_off(int jj, int q) {
+#if LW == 32
+  return (unsigned)(jj * ROWB + ((q ^ (jj & 7)) << 4));
+#else
+  return (unsigned)(jj * ROWB + ((q ^ ((jj >> 1) & 3)) << 4));
+#endif
+}
 __device__ __forceinline__ void ku_mbar_init(unsigned a, unsigned n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(n)); }
 __device__ __forceinline__ void ku_mbar_expect(unsigned a, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
@@ -63,14 +76,14 @@ extern "C" __global__ void __launch_bounds__(NT)
 ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD void* __restrict__ out, void* __restrict__ scratch, int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char tiles_raw[];  // NBUF tiles of [CJ][32] f32, 128-byte swizzled rows
   __shared__ __align__(8) unsigned long long full[NBUF];
-  __shared__ __align__(16) float2 s_part[NW][32];
-  __shared__ __align__(16) float line_c[32];
+  __shared__ __align__(16) float2 s_part[NW][LW];
+  __shared__ __align__(16) float line_c[LW];
   __shared__ int s_failed;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int group = blockIdx.x / P, ngroups = gridDim.x / P, rank = blockIdx.x % P;
   const int j0 = rank * CJ;
   unsigned* counters = (unsigned*)scratch;                                  // [NSLABS], cleared by the host before the launch
-  float2* partials = (float2*)((char*)scratch + (((size_t)NSLABS * 4 + 255) / 256) * 256);   // [NSLABS][P][32]
+  float2* partials = (float2*)((char*)scratch + (((size_t)NSLABS * 4 + 255) / 256) * 256);   // [NSLABS][P][LW]
   // the swizzle pattern is a function of the shared-memory address: tiles start on a 1024-byte boundary
   // (the host sizes the ring with 1024 bytes of slack)
   unsigned char* tiles = tiles_raw + ((1024u - (ku_smem(tiles_raw) & 1023u)) & 1023u);
@@ -80,7 +93,7 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
   auto issue = [&](int slab, int b) {  // one thread: stream this CTA's share of a slab into tile b
     const unsigned mb = ku_smem(&full[b]);
     ku_mbar_expect(mb, TILE_BYTES);
-    for (int k = 0; k < CJ / BOXJ; ++k) ku_tma_2d(tiles_s + b * TILE_BYTES + k * BOXJ * 128, &tmap, slab * 32, j0 + k * BOXJ, mb);
+    for (int k = 0; k < CJ / BOXJ; ++k) ku_tma_2d(tiles_s + b * TILE_BYTES + k * BOXJ * ROWB, &tmap, slab * LW, j0 + k * BOXJ, mb);
   };
   if (threadIdx.x == 0) {
     s_failed = 0;
@@ -100,13 +113,13 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
       if (++spins > SPIN_LIMIT) { atomicExch(status, 1); break; }
     }
     const unsigned char* tile = tiles + b * TILE_BYTES;
-    const int i0 = slab * 32;
-    // thread = (4 lines: chunk q of the 32, row group rs of 4); a warp owns RPW consecutive rows of the tile
-    const int q = lane & 7, rs = lane >> 3;
+    const int i0 = slab * LW;
+    // thread = (4 lines: chunk q of the row, row group rs); a warp owns RPW consecutive rows of the tile
+    const int q = lane % CHUNKS, rs = lane / CHUNKS;
     // two passes over the warp's rows of the tile (16-byte shared-memory loads are cheap; registers are not)
     auto load = [&](int it) {
-      const int row = warp * RPW + it * 4 + rs, j = j0 + row;
-      float4 v = *(const float4*)(tile + row * 128 + ((q ^ (row & 7)) << 4));
+      const int row = warp * RPW + it * RSN + rs, j = j0 + row;
+      float4 v = *(const float4*)(tile + ku_chunk_off(row, q));
 #if !KU_SRC_IDENTITY
       v.x = ku_src_t(v.x, i0 + q * 4 + 0, j KU_SRC_ARGS);
       v.y = ku_src_t(v.y, i0 + q * 4 + 1, j KU_SRC_ARGS);
@@ -118,9 +131,9 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
     };
     float4 m = load(0);
 #pragma unroll 4
-    for (int it = 1; it < RPW / 4; ++it) { const float4 v = load(it); m.x = fmaxf(m.x, v.x); m.y = fmaxf(m.y, v.y); m.z = fmaxf(m.z, v.z); m.w = fmaxf(m.w, v.w); }
+    for (int it = 1; it < RPW / RSN; ++it) { const float4 v = load(it); m.x = fmaxf(m.x, v.x); m.y = fmaxf(m.y, v.y); m.z = fmaxf(m.z, v.z); m.w = fmaxf(m.w, v.w); }
 #pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
+    for (int o = CHUNKS; o <= 16; o <<= 1) {
       m.x = fmaxf(m.x, __shfl_xor_sync(0xffffffffu, m.x, o)); m.y = fmaxf(m.y, __shfl_xor_sync(0xffffffffu, m.y, o));
       m.z = fmaxf(m.z, __shfl_xor_sync(0xffffffffu, m.z, o)); m.w = fmaxf(m.w, __shfl_xor_sync(0xffffffffu, m.w, o));
     }
@@ -129,13 +142,13 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
                                  m.z == -KU_INF ? 0.0f : m.z * KU_LOG2E, m.w == -KU_INF ? 0.0f : m.w * KU_LOG2E);
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-    for (int it = 0; it < RPW / 4; ++it) {
+    for (int it = 0; it < RPW / RSN; ++it) {
       const float4 v = load(it);
       sum.x += ku_ex2(__fmaf_rn(v.x, KU_LOG2E, -k.x)); sum.y += ku_ex2(__fmaf_rn(v.y, KU_LOG2E, -k.y));
       sum.z += ku_ex2(__fmaf_rn(v.z, KU_LOG2E, -k.z)); sum.w += ku_ex2(__fmaf_rn(v.w, KU_LOG2E, -k.w));
     }
 #pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
+    for (int o = CHUNKS; o <= 16; o <<= 1) {
       sum.x += __shfl_xor_sync(0xffffffffu, sum.x, o); sum.y += __shfl_xor_sync(0xffffffffu, sum.y, o);
       sum.z += __shfl_xor_sync(0xffffffffu, sum.z, o); sum.w += __shfl_xor_sync(0xffffffffu, sum.w, o);
     }
@@ -145,10 +158,12 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
     }
     __syncthreads();
     if (warp == 0) {
-      float mm = s_part[0][lane].x, tot = s_part[0][lane].y;
+      if (lane < LW) {
+        float mm = s_part[0][lane].x, tot = s_part[0][lane].y;
 #pragma unroll
-      for (int w = 1; w < NW; ++w) ku_merge(mm, tot, s_part[w][lane].x, s_part[w][lane].y);
-      partials[((size_t)slab * P + rank) * 32 + lane] = make_float2(mm, tot);
+        for (int w = 1; w < NW; ++w) ku_merge(mm, tot, s_part[w][lane].x, s_part[w][lane].y);
+        partials[((size_t)slab * P + rank) * LW + lane] = make_float2(mm, tot);
+      }
       __syncwarp();
       // the warp's 32 stores are ordered before this release by the warp barrier above
       if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counters + slab) : "memory");
@@ -160,7 +175,7 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
   auto finish = [&](int n, int slab) {
     const int b = n % NBUF;
     const unsigned char* tile = tiles + b * TILE_BYTES;
-    const int i0 = slab * 32;
+    const int i0 = slab * LW;
     if (warp == 0) {
       if (lane == 0) {   // one poller per CTA: the counter is shared by the whole group
         unsigned spins = 0;
@@ -172,23 +187,25 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
         if (bad) s_failed = 1;
       }
       __syncwarp();   // orders the other lanes' loads of the pairs after lane 0's acquire
-      const float2* src = partials + (size_t)slab * P * 32 + lane;
-      float2 pr[P];
+      if (lane < LW) {
+        const float2* src = partials + (size_t)slab * P * LW + lane;
+        float2 pr[P];
 #pragma unroll
-      for (int c = 0; c < P; ++c) pr[c] = __ldcg(src + c * 32);
-      float mm = pr[0].x, tot = pr[0].y;
+        for (int c = 0; c < P; ++c) pr[c] = __ldcg(src + c * LW);
+        float mm = pr[0].x, tot = pr[0].y;
 #pragma unroll
-      for (int c = 1; c < P; ++c) ku_merge(mm, tot, pr[c].x, pr[c].y);
-      line_c[lane] = (mm == -KU_INF) ? __int_as_float(0x7fc00000) : mm + log2f(tot);
+        for (int c = 1; c < P; ++c) ku_merge(mm, tot, pr[c].x, pr[c].y);
+        line_c[lane] = (mm == -KU_INF) ? __int_as_float(0x7fc00000) : mm + log2f(tot);
+      }
     }
     __syncthreads();
     // lane = position within a 32-position strip; one 16-byte load gives 4 lines at that position,
     // then 4 warp-wide stores of 128 contiguous bytes each
 #pragma unroll 4
-    for (int t = warp; t < 8 * (CJ / 32); t += NW) {
-      const int q = t & 7, js = t >> 3;
+    for (int t = warp; t < CHUNKS * (CJ / 32); t += NW) {
+      const int q = t % CHUNKS, js = t / CHUNKS;
       const int jj = js * 32 + lane, j = j0 + jj;
-      float4 v = *(const float4*)(tile + jj * 128 + ((q ^ (jj & 7)) << 4));
+      float4 v = *(const float4*)(tile + ku_chunk_off(jj, q));
       const float4 c4 = *(const float4*)&line_c[q * 4];
       if ((C % CJ == 0) || j < C) {
 #if !KU_SRC_IDENTITY
@@ -198,10 +215,10 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
         v.w = ku_src_t(v.w, i0 + q * 4 + 3, j KU_SRC_ARGS);
 #endif
         ku_out_t* o = (ku_out_t*)out + (i64)(i0 + q * 4) * C + j;
-        if ((R % 32 == 0) || i0 + q * 4 + 0 < R) KU_STORE(&o[0], KU_ENC(ku_ex2(__fmaf_rn(v.x, KU_LOG2E, -c4.x))));
-        if ((R % 32 == 0) || i0 + q * 4 + 1 < R) KU_STORE(&o[(i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.y, KU_LOG2E, -c4.y))));
-        if ((R % 32 == 0) || i0 + q * 4 + 2 < R) KU_STORE(&o[2 * (i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.z, KU_LOG2E, -c4.z))));
-        if ((R % 32 == 0) || i0 + q * 4 + 3 < R) KU_STORE(&o[3 * (i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.w, KU_LOG2E, -c4.w))));
+        if ((R % LW == 0) || i0 + q * 4 + 0 < R) KU_STORE(&o[0], KU_ENC(ku_ex2(__fmaf_rn(v.x, KU_LOG2E, -c4.x))));
+        if ((R % LW == 0) || i0 + q * 4 + 1 < R) KU_STORE(&o[(i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.y, KU_LOG2E, -c4.y))));
+        if ((R % LW == 0) || i0 + q * 4 + 2 < R) KU_STORE(&o[2 * (i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.z, KU_LOG2E, -c4.z))));
+        if ((R % LW == 0) || i0 + q * 4 + 3 < R) KU_STORE(&o[3 * (i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.w, KU_LOG2E, -c4.w))));
       }
     }
     __syncthreads();  // every thread is done with tile b and with line_c
