@@ -133,7 +133,18 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
       L.host_launch(vals, rt_.stream());
       ++rt_.stats.launches;
     } else {
-      rt_.launch(L.kernel, L.grid, L.block, L.cluster, L.smem, argv.data(), L.cooperative);
+      // A cooperative grid is sized from an occupancy query; if the device can hold fewer CTAs at launch time (another
+      // context shares it) the driver refuses the launch: drop whole CTA groups until it fits.
+      for (;;) {
+        try {
+          rt_.launch(L.kernel, L.grid, L.block, L.cluster, L.smem, argv.data(), L.cooperative);
+          break;
+        } catch (const Error& e) {
+          const bool too_large = std::string(e.what()).find("(720)") != std::string::npos;   // CUDA_ERROR_COOPERATIVE_LAUNCH_TOO_LARGE
+          if (!L.cooperative || !too_large || L.grid[0] <= L.grid_multiple) throw;
+          L.grid[0] -= L.grid_multiple;
+        }
+      }
     }
     if (profiling_) {
       cuda_check(cudaEventRecord(ev_pool_[ev].second, rt_.stream()), "cudaEventRecord");
