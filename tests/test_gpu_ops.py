@@ -259,6 +259,38 @@ def test_softmax_through_transpose_and_bias(oracle_lib, cuda_lib, cpu, cpu64, gp
         assert c[0].shape == (m, n)
 
 
+@pytest.mark.parametrize("family,env", [("softmax_groups_tma", {}), ("softmax_panels_tma", {"KURUMI_SMT_NO_GROUPS": "1"}),
+                                        ("softmax_transposed_tma", {"KURUMI_SMT_NO_GROUPS": "1", "KURUMI_SMT_NO_PANELS": "1"})])
+def test_large_transposed_softmax_ragged_and_special_lines(oracle_lib, cuda_lib, cpu64, gpu, monkeypatch, family, env):
+    """Each of the three large-problem kernels on a shape that divides into nothing (2100 positions, 2052 lines),
+    with lines that are all -inf, hold a NaN, hold +inf, or a single finite entry."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    rng = np.random.default_rng(21)
+    n, m = 2100, 2052                       # positions (rows of L), lines (columns of L)
+    Lv = rng_f32(rng, (n, m), 2.0)
+    Lv[:, 5] = -np.inf                      # nothing finite: the line is NaN
+    Lv[:, 6] = -np.inf; Lv[1234, 6] = 0.5   # one finite entry: a one-hot line
+    Lv[17, 7] = np.nan                      # NaN poisons its line
+    Lv[99, 2051] = np.inf                   # +inf: inf - inf in the exponent
+    Lv[:, 2050] = 60.0; Lv[3, 2050] = 88.0  # large but finite
+    bv = rng.uniform(-1, 1, n).astype(np.float32)
+    p = Pair(oracle_lib, cuda_lib)
+    L = p.feed((n, m), api.F32, Lv)
+    bias = p.feed((n,), api.F32, bv)
+    out = p.softmax(p.add(p.permute(L, [1, 0]), p.broadcast_to(bias, [m, n])), 1)
+    assert api.compile_check(cuda_lib, p.gc, [out]) == [family]
+    w, c, _ = p.run(cpu64, gpu, [out])
+    want, got = w[0], c[0]
+    assert got.shape == (m, n)
+    nan_lines = [5, 7, 2051]
+    for i in nan_lines:
+        assert np.isnan(want[i]).all() and np.isnan(got[i]).all(), i
+    keep = np.setdiff1d(np.arange(m), nan_lines)
+    util.assert_close(want[keep], got[keep], 1e-5, 1e-12, f"{family} ragged")
+    assert abs(got[6, 1234] - 1.0) < 1e-6 and np.count_nonzero(got[6]) == 1
+
+
 def test_softmax_special_values(oracle_lib, cuda_lib, cpu, gpu):
     p = Pair(oracle_lib, cuda_lib)
     v = np.zeros((4, 256), np.float32)
