@@ -98,6 +98,8 @@ KuNode ku_mean(KuGraph *g, KuNode x, size_t axis);
 KuNode ku_reduce_max(KuGraph *g, KuNode x, size_t axis);
 KuNode ku_reduce_min(KuGraph *g, KuNode x, size_t axis);
 KuNode ku_softmax(KuGraph *g, KuNode x, size_t axis);
+KuNode ku_argmax(KuGraph *g, KuNode x, size_t axis); /* kurumi.h:193-194: I64 index of the first maximum / minimum */
+KuNode ku_argmin(KuGraph *g, KuNode x, size_t axis);
 KuNode ku_rmsnorm(KuGraph *g, KuNode x, size_t axis, float eps); /* kurumi.h:302 */
 KuNode ku_clamp_min(KuGraph *g, KuNode x, float v);
 

@@ -213,6 +213,12 @@ class Graph:
         s, r = _sz(a.shape)
         return self._n("ku_constant", C.c_uint32(dtype), a.ctypes.data_as(C.c_void_p), C.c_size_t(a.nbytes), s, C.c_size_t(r))
 
+    def argmax(self, x: int, axis: int) -> int:
+        return self._n("ku_argmax", C.c_uint32(x), C.c_size_t(axis))
+
+    def argmin(self, x: int, axis: int) -> int:
+        return self._n("ku_argmin", C.c_uint32(x), C.c_size_t(axis))
+
     def quant_matmul(self, act: int, qweight: int, scales: int, mins: int | None, bits: int, group_size: int) -> int:
         """act [M, K] x dequant(qweight [N, K*bits/8] U8, scales / mins [N, K/group_size] F16)^T -> [M, N]; mins None = symmetric."""
         return self._n("ku_quant_matmul", C.c_uint32(act), C.c_uint32(qweight), C.c_uint32(scales), C.c_uint32(KU_ERR if mins is None else mins),

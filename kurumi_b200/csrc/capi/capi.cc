@@ -89,7 +89,7 @@ KU_UN(ku_cos, cos) KU_UN(ku_relu, relu) KU_UN(ku_gelu, gelu) KU_UN(ku_silu, silu
 KU_UN(ku_tanh, tanh) KU_UN(ku_logical_not, logical_not) KU_UN(ku_detach, detach)
 
 KU_AXIS(ku_sum, sum) KU_AXIS(ku_prod, prod) KU_AXIS(ku_mean, mean) KU_AXIS(ku_reduce_max, reduce_max)
-KU_AXIS(ku_reduce_min, reduce_min) KU_AXIS(ku_softmax, softmax)
+KU_AXIS(ku_reduce_min, reduce_min) KU_AXIS(ku_softmax, softmax) KU_AXIS(ku_argmax, argmax) KU_AXIS(ku_argmin, argmin)
 
 KuNode ku_rmsnorm(KuGraph* g, KuNode x, size_t axis, float eps) { return build(g, [&](Graph& gr) { return gr.rmsnorm(x, axis, eps); }); }
 KuNode ku_clamp_min(KuGraph* g, KuNode x, float v) { return build(g, [&](Graph& gr) { return gr.clamp_min(x, v); }); }

@@ -26,7 +26,7 @@ const char* op_name(OpKind k) {
   static const char* n[] = {"Const", "Input", "Iota", "RandUniform", "Cast", "Bitcast", "Detach", "Add", "Mul", "Max",
                             "Neg", "IDiv", "And", "Or", "Xor", "Shl", "Shr", "CmpLt", "CmpEq", "Where", "Recip", "Sqrt",
                             "Exp2", "Log2", "Sin", "Floor", "Sum", "Prod", "ReduceMax", "Softmax", "RmsNorm", "Sdpa",
-                            "Reshape", "Permute", "Expand", "Slice", "Flip", "Pad", "DotGeneral", "QuantMatmul"};
+                            "Reshape", "Permute", "Expand", "Slice", "Flip", "Pad", "DotGeneral", "QuantMatmul", "ArgReduce"};
   return n[static_cast<size_t>(k)];
 }
 
@@ -52,6 +52,7 @@ DType Graph::infer_dtype(const Op& op, const std::vector<NodeId>& src) const {
     case OpKind::Const: return op.data->dtype;
     case OpKind::Input: case OpKind::Iota: case OpKind::Cast: case OpKind::Bitcast: return op.to;
     case OpKind::CmpLt: case OpKind::CmpEq: return DType::BOOL;
+    case OpKind::ArgReduce: return DType::I64;   // indices
     case OpKind::RandUniform: return DType::F32;
     case OpKind::Where: return node(src[1]).dtype;
     default: return node(src[0]).dtype;
@@ -64,7 +65,7 @@ Shape Graph::derive_shape(const Op& op, const std::vector<NodeId>& src) const {
     case OpKind::Const: case OpKind::Input: case OpKind::Iota: case OpKind::RandUniform:
     case OpKind::Reshape: case OpKind::Expand:
       return op.shape;
-    case OpKind::Sum: case OpKind::Prod: case OpKind::ReduceMax: {
+    case OpKind::Sum: case OpKind::Prod: case OpKind::ReduceMax: case OpKind::ArgReduce: {
       Shape s = ishape(0);
       s.erase(s.begin() + static_cast<long>(op.axis));
       return s;
@@ -200,6 +201,9 @@ NodeId Graph::select(NodeId cond, NodeId a, NodeId b) {
 NodeId Graph::sum(NodeId a, size_t axis) { reduce_axis_ok("sum", a, axis); require("sum", a, is_arith(dtype(a)), "numeric or complex"); Op op; op.kind = OpKind::Sum; op.axis = axis; return push(std::move(op), {a}); }
 NodeId Graph::prod(NodeId a, size_t axis) { reduce_axis_ok("prod", a, axis); require("prod", a, is_arith(dtype(a)), "numeric or complex"); Op op; op.kind = OpKind::Prod; op.axis = axis; return push(std::move(op), {a}); }
 NodeId Graph::reduce_max(NodeId a, size_t axis) { reduce_axis_ok("reduce_max", a, axis); require("reduce_max", a, is_numeric(dtype(a)), "numeric"); Op op; op.kind = OpKind::ReduceMax; op.axis = axis; return push(std::move(op), {a}); }
+// kurumi_core/src/graph/ops/core/reduce.rs:24-33
+NodeId Graph::argmax(NodeId a, size_t axis) { reduce_axis_ok("argmax", a, axis); require("argmax", a, is_numeric(dtype(a)), "numeric"); Op op; op.kind = OpKind::ArgReduce; op.axis = axis; op.arg_min = false; return push(std::move(op), {a}); }
+NodeId Graph::argmin(NodeId a, size_t axis) { reduce_axis_ok("argmin", a, axis); require("argmin", a, is_numeric(dtype(a)), "numeric"); Op op; op.kind = OpKind::ArgReduce; op.axis = axis; op.arg_min = true; return push(std::move(op), {a}); }
 NodeId Graph::softmax(NodeId a, size_t axis) { reduce_axis_ok("softmax", a, axis); require("softmax", a, is_float(dtype(a)), "float"); Op op; op.kind = OpKind::Softmax; op.axis = axis; return push(std::move(op), {a}); }
 NodeId Graph::rmsnorm(NodeId a, size_t axis, float eps) { reduce_axis_ok("rmsnorm", a, axis); require("rmsnorm", a, is_float(dtype(a)), "float"); Op op; op.kind = OpKind::RmsNorm; op.axis = axis; op.eps = eps; return push(std::move(op), {a}); }
 

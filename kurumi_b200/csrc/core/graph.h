@@ -53,7 +53,7 @@ enum class OpKind : uint8_t {
   Recip, Sqrt, Exp2, Log2, Sin, Floor,
   Sum, Prod, ReduceMax, Softmax, RmsNorm, Sdpa,
   Reshape, Permute, Expand, Slice, Flip, Pad, DotGeneral,
-  QuantMatmul,
+  QuantMatmul, ArgReduce,
 };
 const char* op_name(OpKind k);
 inline bool is_movement(OpKind k) { return k >= OpKind::Reshape && k <= OpKind::Pad; }
@@ -73,6 +73,7 @@ struct Op {
   uint8_t bits = 0;                            // QuantMatmul: 2, 4 or 8 bits per weight
   size_t group_size = 0;                       // QuantMatmul: weights per (scale, min) group along K
   bool symmetric = true;                       // QuantMatmul: no mins operand
+  bool arg_min = false;                        // ArgReduce: index of the minimum instead of the maximum
 };
 
 struct Node {
@@ -125,6 +126,8 @@ class Graph {
   NodeId prod(NodeId a, size_t axis);
   NodeId reduce_max(NodeId a, size_t axis);
   NodeId softmax(NodeId a, size_t axis);
+  NodeId argmax(NodeId a, size_t axis);   // I64 index of the first maximum along the axis
+  NodeId argmin(NodeId a, size_t axis);
   NodeId rmsnorm(NodeId a, size_t axis, float eps);
   NodeId reshape(NodeId a, Shape shape);
   NodeId permute(NodeId a, std::vector<size_t> perm);

@@ -19,7 +19,7 @@ constexpr TagRow kTags[] = {
     {OpKind::CmpEq, 18},  {OpKind::Where, 19},  {OpKind::Recip, 20},    {OpKind::Sqrt, 21},       {OpKind::Exp2, 22},    {OpKind::Log2, 23},
     {OpKind::Sin, 24},    {OpKind::Floor, 25},  {OpKind::Sum, 26},      {OpKind::Prod, 27},       {OpKind::ReduceMax, 28}, {OpKind::Softmax, 30},
     {OpKind::RmsNorm, 31}, {OpKind::Sdpa, 32},  {OpKind::Reshape, 33},  {OpKind::Permute, 34},    {OpKind::Expand, 35},  {OpKind::Slice, 36},
-    {OpKind::Flip, 37},   {OpKind::Pad, 38},    {OpKind::DotGeneral, 39}, {OpKind::QuantMatmul, 40},
+    {OpKind::Flip, 37},   {OpKind::Pad, 38},    {OpKind::DotGeneral, 39}, {OpKind::QuantMatmul, 40}, {OpKind::ArgReduce, 29},
 };
 uint8_t tag_of(OpKind k) {
   for (const TagRow& r : kTags) if (r.kind == k) return r.tag;
@@ -56,6 +56,7 @@ void write_op(Writer& w, const Op& op) {
     case OpKind::RandUniform: w.vec(op.shape); break;
     case OpKind::Cast: case OpKind::Bitcast: w.dtype(op.to); break;
     case OpKind::Sum: case OpKind::Prod: case OpKind::ReduceMax: case OpKind::Softmax: w.u64(op.axis); break;
+    case OpKind::ArgReduce: w.u64(op.axis); w.u8(op.arg_min ? 1 : 0); break;
     case OpKind::RmsNorm: w.u64(op.axis); w.f32(op.eps); break;
     case OpKind::Sdpa: w.u8(op.causal ? 1 : 0); break;
     case OpKind::Reshape: case OpKind::Expand: w.vec(op.shape); break;
@@ -200,6 +201,13 @@ NodeId read_node(Reader& r, Graph& g, size_t index) {
     case OpKind::RandUniform: op.shape = r.vec(); checked_numel(op.shape); break;
     case OpKind::Cast: case OpKind::Bitcast: op.to = r.dtype(); break;
     case OpKind::Sum: case OpKind::Prod: case OpKind::ReduceMax: case OpKind::Softmax: op.axis = r.usize(); break;
+    case OpKind::ArgReduce: {
+      op.axis = r.usize();
+      const uint8_t kind = r.u8();
+      if (kind > 1) throw bad("unknown argkind " + std::to_string(kind));
+      op.arg_min = kind == 1;
+      break;
+    }
     case OpKind::RmsNorm: op.axis = r.usize(); op.eps = r.f32(); break;
     case OpKind::Sdpa: op.causal = r.u8() != 0; break;
     case OpKind::Reshape: case OpKind::Expand: op.shape = r.vec(); checked_numel(op.shape); break;
@@ -260,6 +268,7 @@ NodeId read_node(Reader& r, Graph& g, size_t index) {
     case OpKind::Prod: need(1); id = g.prod(src[0], op.axis); break;
     case OpKind::ReduceMax: need(1); id = g.reduce_max(src[0], op.axis); break;
     case OpKind::Softmax: need(1); id = g.softmax(src[0], op.axis); break;
+    case OpKind::ArgReduce: need(1); id = op.arg_min ? g.argmin(src[0], op.axis) : g.argmax(src[0], op.axis); break;
     case OpKind::RmsNorm: need(1); id = g.rmsnorm(src[0], op.axis, op.eps); break;
     case OpKind::Sdpa: need(3); id = g.sdpa_fused(src[0], src[1], src[2], op.causal); break;
     case OpKind::Reshape: need(1); id = g.reshape(src[0], op.shape); break;

@@ -7,7 +7,7 @@
 //   u32 entry_count; per entry: str name, u32 n_out, out ids, u32 n_in, per input: u32 node, u8 role, str name
 // with usize as u64, vectors as u32 length + items, str as u32 length + UTF-8, dtypes as the C ABI tags,
 // Const storage as dtype, u64 byte count, bytes. Op tags are the reference's; the primitives this
-// library does not evaluate (tags 29, 41..54) are refused with a clear error on read.
+// library does not evaluate (tags 41..54) are refused with a clear error on read.
 // The reader mirrors kurumi_core/src/graph/serialize/decode.rs:23-88 (bad magic, version, truncated
 // blobs, forward source references, under- or over-filled Const payloads are errors, never crashes).
 #pragma once

@@ -595,6 +595,50 @@ Emitted emit_reduce(const Fused& f, OpKind kind, size_t axis, int sm_count) {
   return e;
 }
 
+// Index of the first maximum / minimum along an axis (kurumi_core/src/interp/reduce.rs:41-66): one thread per output
+// element walks the axis in index order, starting from element 0 and replacing the best only on a strict
+// comparison, which is also what keeps a NaN from ever replacing anything. Output is I64.
+Emitted emit_arg_reduce(const Fused& f, size_t axis, bool arg_min, int sm_count) {
+  Space sp = collapse(f, static_cast<int>(axis));
+  Gen g(f, sp);
+  const DType d = f.dtype();
+  const size_t nd = sp.dims.size();
+  const size_t ax = static_cast<size_t>(sp.special);
+  const int64_t len = sp.dims[ax];
+  int64_t outer = 1, inner = 1;
+  for (size_t q = 0; q < ax; ++q) outer *= sp.dims[q];
+  for (size_t q = ax + 1; q < nd; ++q) inner *= sp.dims[q];
+  std::vector<std::string> coords(nd);
+  for (size_t q = 0; q < nd; ++q) coords[q] = "c" + std::to_string(q);
+  coords[ax] = "k";
+  const int64_t outs = outer * inner;
+  std::ostringstream o;
+  o << device_prelude();
+  Emitted e;
+  e.leaf_args = g.args;
+  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_arg_fold(" << g.params() << "void* __restrict__ out) {\n";
+  o << "  for (" << g.idx_t << " o = blockIdx.x * 256 + threadIdx.x; o < " << outs << "; o += (" << g.idx_t << ")gridDim.x * 256) {\n";
+  o << "    const " << g.idx_t << " oi = o % " << inner << ", oo = o / " << inner << ";\n";
+  if (ax > 0) o << decompose("oo", sp.dims, 0, ax, g.idx_t, "c", "    ");
+  if (ax + 1 < nd) {
+    std::vector<int64_t> tail(sp.dims);
+    o << decompose("oi", tail, ax + 1, nd, g.idx_t, "c", "    ");
+  }
+  o << "    " << ctype(d) << " best = 0;\n    i64 best_k = 0;\n";
+  o << "    for (" << g.idx_t << " k = 0; k < " << len << "; ++k) {\n";
+  std::vector<std::string> lv(f.leaves.size());
+  for (size_t li = 0; li < f.leaves.size(); ++li) lv[li] = g.leaf_value(li, coords);
+  o << g.body(lv, "      ");
+  o << "      if (k == 0 || v" << f.root << (arg_min ? " < " : " > ") << "best) { best = v" << f.root << "; best_k = (i64)k; }\n    }\n";
+  o << "    ((i64*)out)[o] = best_k;\n  }\n}\n";
+  e.entry = "ku_arg_fold";
+  e.block = 256;
+  e.grid = pick_grid(outs, 256, sm_count, 8);
+  e.family = "arg_fold";
+  e.source = o.str();
+  return e;
+}
+
 // ---- softmax / rmsnorm ----------------------------------------------------------------------------
 // Softmax follows kurumi_core/src/interp/nn.rs:35-69: line max, e = exp(x - max) (exp, not exp2),
 // sum of e, e / sum (a division). RmsNorm follows nn.rs:88-116: x / sqrt(sum(x*x)/n + eps).

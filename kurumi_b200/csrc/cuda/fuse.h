@@ -131,6 +131,8 @@ struct Emitted {
 Emitted emit_pointwise(const Fused& f, int sm_count);
 // Sum / Prod / ReduceMax over `axis` of `f`; output is row-major over the remaining axes.
 Emitted emit_reduce(const Fused& f, OpKind kind, size_t axis, int sm_count);
+// I64 index of the first maximum / minimum of `f` along `axis` (one thread per output, index order).
+Emitted emit_arg_reduce(const Fused& f, size_t axis, bool arg_min, int sm_count);
 // Softmax / RmsNorm over `axis` of `f`; output has f's shape, row-major.
 Emitted emit_softmax(const Fused& f, OpKind kind, size_t axis, float eps, int sm_count);
 

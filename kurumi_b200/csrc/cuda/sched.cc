@@ -605,6 +605,15 @@ Fused Scheduler::eval_node(NodeId id) {
       return movement(n, in[0]);
     case OpKind::DotGeneral: return dot(n, in[0], in[1]);
     case OpKind::QuantMatmul: return quant_matmul(n, in);
+    case OpKind::ArgReduce: {
+      Fused f = resolve_acc(in[0]);
+      const int slot = new_slot(Slot::Temp, DType::I64, n.shape);
+      if (!dry() && numel(n.shape) > 0) {
+        if (g_.shape(n.src[0])[op.axis] == 0) throw Error::backend("argreduce over an empty axis");
+        push_launch(emit_arg_reduce(f, op.axis, op.arg_min, sm_), f, slot);
+      }
+      return buffer_value(slot, DType::I64, n.shape);
+    }
   }
   throw Error::backend(std::string("op ") + op_name(op.kind) + " has no CUDA kernel");
 }

@@ -312,6 +312,58 @@ void reduce_fold(const T* data, const Shape& shape, size_t axis, T init, F f, T*
   }
 }
 
+// kurumi_core/src/interp/reduce.rs:16-66: I64 index of the maximum / minimum along `axis`; the first element is the
+// starting best and a later one replaces it only when strictly greater / smaller, so ties keep the lowest index
+// and a NaN never replaces anything (nor is a leading NaN ever replaced). Elements compare by value.
+Val arg_reduce_val(const Val& a, size_t axis, bool arg_min) {
+  Shape out_shape = a.shape;
+  out_shape.erase(out_shape.begin() + static_cast<long>(axis));
+  Val o = make_val(DType::I64, out_shape, false);
+  auto* out = reinterpret_cast<int64_t*>(o.bytes.data());
+  const size_t len = a.shape[axis];
+  size_t inner = 1, outer = 1;
+  for (size_t d = axis + 1; d < a.shape.size(); ++d) inner *= a.shape[d];
+  for (size_t d = 0; d < axis; ++d) outer *= a.shape[d];
+  if (len == 0 && outer * inner > 0) throw Error("panic: index out of bounds: argreduce over an empty axis");
+  const bool integral = !is_float(a.dtype);
+  const size_t w = a.wide ? 8 : dtype_width(a.dtype);
+  // integers compare as integers (u64 / i64 do not fit a double), floats by value
+  auto as_f = [&](size_t i) { return a.wide ? wd(a)[i] : elem_to_f64(a.dtype, a.bytes.data() + i * w); };
+  auto as_i = [&](size_t i) -> std::pair<bool, uint64_t> {   // (negative, magnitude-ordered key)
+    int64_t sv = 0; uint64_t uv = 0;
+    const uint8_t* p = a.bytes.data() + i * w;
+    switch (a.dtype) {
+      case DType::I8: sv = *reinterpret_cast<const int8_t*>(p); break;
+      case DType::I16: { int16_t t; std::memcpy(&t, p, 2); sv = t; break; }
+      case DType::I32: { int32_t t; std::memcpy(&t, p, 4); sv = t; break; }
+      case DType::I64: std::memcpy(&sv, p, 8); break;
+      case DType::U8: case DType::BOOL: uv = *p; return {false, uv};
+      case DType::U16: { uint16_t t; std::memcpy(&t, p, 2); return {false, t}; }
+      case DType::U32: { uint32_t t; std::memcpy(&t, p, 4); return {false, t}; }
+      default: std::memcpy(&uv, p, 8); return {false, uv};
+    }
+    return {sv < 0, static_cast<uint64_t>(sv)};
+  };
+  auto less_i = [](std::pair<bool, uint64_t> x, std::pair<bool, uint64_t> y) {
+    if (x.first != y.first) return x.first;   // negative < non-negative
+    return x.second < y.second;                // two's complement order holds within a sign
+  };
+  for (size_t oo = 0; oo < outer; ++oo)
+    for (size_t oi = 0; oi < inner; ++oi) {
+      const size_t base = oo * len * inner + oi;
+      size_t best = 0;
+      for (size_t k = 1; k < len; ++k) {
+        const size_t i = base + k * inner, b = base + best * inner;
+        bool better;
+        if (integral) better = arg_min ? less_i(as_i(i), as_i(b)) : less_i(as_i(b), as_i(i));
+        else better = arg_min ? as_f(i) < as_f(b) : as_f(i) > as_f(b);
+        if (better) best = k;
+      }
+      out[oo * inner + oi] = static_cast<int64_t>(best);
+    }
+  return o;
+}
+
 Val reduce_val(OpKind k, const Val& a, size_t axis, bool wide_mode) {
   Shape out_shape = a.shape;
   out_shape.erase(out_shape.begin() + static_cast<long>(axis));
@@ -706,6 +758,7 @@ Val eval_op(const Node& n, const std::vector<const Val*>& in, bool wide_mode) {
     case OpKind::Floor:
       return ew_unary(op.kind, *in[0]);
     case OpKind::Sum: case OpKind::Prod: case OpKind::ReduceMax: return reduce_val(op.kind, *in[0], op.axis, wide_mode);
+    case OpKind::ArgReduce: return arg_reduce_val(*in[0], op.axis, op.arg_min);
     case OpKind::Softmax: return softmax_val(*in[0], op.axis);
     case OpKind::RmsNorm: return rmsnorm_val(*in[0], op.axis, op.eps);
     case OpKind::Sdpa: return sdpa_val(*in[0], *in[1], *in[2], op.causal);

@@ -48,9 +48,9 @@ def test_rejections(oracle_lib):
     no_entry = GOLDEN[:-len(struct.pack("<IIIII", 1, 0, 1, 3, 0))] + struct.pack("<I", 0)
     with pytest.raises(api.Error, match="no entries"):
         api.deserialize(lib, no_entry)
-    argreduce = b"KGPH\x02" + struct.pack("<I", 1) + bytes([29]) + struct.pack("<Q", 0) + bytes([0]) + struct.pack("<I", 0) + struct.pack("<I", 0)
+    solve = b"KGPH\x02" + struct.pack("<I", 1) + bytes([41]) + struct.pack("<I", 0) + struct.pack("<I", 0)
     with pytest.raises(api.Error, match="not a primitive"):
-        api.deserialize(lib, argreduce)
+        api.deserialize(lib, solve)
     bad_role = GOLDEN[:-4] + struct.pack("<I", 1) + struct.pack("<I", 0) + bytes([2]) + struct.pack("<I", 0)
     with pytest.raises(api.Error, match="role"):
         api.deserialize(lib, bad_role)
