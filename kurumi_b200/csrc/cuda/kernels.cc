@@ -353,21 +353,30 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   int64_t bh = 1;
   for (size_t i = 0; i + 2 < r; ++i) bh *= static_cast<int64_t>(shape[i]);
   const uint32_t fmt = dt == DType::BF16 ? 1u : 0u;
-  const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(128 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+  // two CTAs per SM over key blocks of 64 by default; KURUMI_ATTENTION_ONE_CTA selects the one-CTA kernel (key blocks of 128)
+  const bool twin = std::getenv("KURUMI_ATTENTION_ONE_CTA") == nullptr;
+  const int64_t tk = twin ? 64 : 128;
+  const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tk >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
   const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(dh >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
   char lit[64];
   std::snprintf(lit, sizeof(lit), "%.9gf", static_cast<double>(scale * 1.4426950408889634f));
   std::string src = device_prelude() +
                     defines({{"BH", bh}, {"S", s}, {"DH", dh}, {"CAUSAL", causal ? 1 : 0}, {"IDESC_S", static_cast<int64_t>(idesc_s)}, {"IDESC_O", static_cast<int64_t>(idesc_o)},
-                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}}) +
+                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", twin ? 1 : 0}}) +
                     "#define SCALE_LOG2E " + lit + "\n" + kSrc_attention_tc;
   out->name = "attention_tc";
-  out->kernel = load(src, "ku_attention_tc", true);
+  out->kernel = load(src, twin ? "ku_attention_tc_twin" : "ku_attention_tc", true);
   out->grid[0] = static_cast<unsigned>((s + 127) / 128);
   out->grid[1] = static_cast<unsigned>(bh);
-  out->block[0] = 320;   // TMA warp, MMA warp, 8 softmax warps
   const int64_t tile = 128 * 128 * (dh / 64);
-  out->smem = static_cast<unsigned>(std::max<int64_t>(5 * tile + 128 * 128 * 2 + 1024, 120 * 1024));
+  if (twin) {
+    out->block[0] = 192;   // TMA warp, MMA warp, 4 softmax warps
+    // Q, two K and two V stages of 64 keys, P, barriers; at least 80 KB so that no third CTA (which would wait for tensor memory) joins an SM
+    out->smem = static_cast<unsigned>(std::max<int64_t>(tile + 4 * (tile / 2) + 128 * 128 + 128, 80 * 1024));
+  } else {
+    out->block[0] = 320;   // TMA warp, MMA warp, 8 softmax warps
+    out->smem = static_cast<unsigned>(std::max<int64_t>(5 * tile + 128 * 128 * 2 + 1024, 120 * 1024));
+  }
   for (int slot = -1; slot >= -3; --slot) {
     Arg a;
     a.kind = Arg::Tmap;
@@ -377,7 +386,7 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
     a.tm.swz = CU_TENSOR_MAP_SWIZZLE_128B;
     a.tm.dims[0] = static_cast<uint64_t>(dh); a.tm.dims[1] = static_cast<uint64_t>(s); a.tm.dims[2] = static_cast<uint64_t>(bh);
     a.tm.strides[0] = static_cast<uint64_t>(dh * 2); a.tm.strides[1] = static_cast<uint64_t>(s * dh * 2);
-    a.tm.box[0] = 64; a.tm.box[1] = 128; a.tm.box[2] = 1;
+    a.tm.box[0] = 64; a.tm.box[1] = (slot == -1) ? 128 : static_cast<uint32_t>(tk); a.tm.box[2] = 1;   // slot -1 is Q
     out->args.push_back(a);
   }
   Arg o; o.kind = Arg::SlotPtr; o.slot = -4; out->args.push_back(o);

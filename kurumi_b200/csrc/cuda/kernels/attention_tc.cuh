@@ -106,6 +106,7 @@ __device__ __forceinline__ unsigned ku_pack2(float lo, float hi) {
 #endif
 }
 
+#if !KU_TWIN
 extern "C" __global__ void __launch_bounds__(320, 1)
 ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ KuTmap tmap_k, const __grid_constant__ KuTmap tmap_v, void* __restrict__ Op,
                 int* __restrict__ status) {
@@ -311,3 +312,211 @@ ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ K
   __syncthreads();
   if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
 }
+#endif  // !KU_TWIN
+
+#if KU_TWIN
+// ---- Two CTAs per SM -------------------------------------------------------------------------------------
+// The same algorithm with key blocks of 64, four softmax warps (one thread per query row) and half the
+// tensor memory (two 64-column score buffers + O = 256 columns), so that two CTAs share an SM: while one
+// CTA's softmax threads wait for scores, store P or wait for a product, the other CTA's exponentials keep
+// the special-function unit busy and its MMAs keep the tensor core busy. Shared memory (DH = 128): Q 32 KB,
+// K and V rings 2 x 16 KB each, P 16 KB, barriers: 112.25 KB per CTA, all of it dynamic (the swizzled tiles
+// need 1024-byte alignment, which the start of dynamic shared memory has when nothing static precedes it).
+#define TK 64
+#define Q_BYTES (128 * 128 * DCH)
+#define KV_BYTES (TK * 128 * DCH)
+#define KV_CHUNK (TK * 128)
+
+extern "C" __global__ void __launch_bounds__(192, 2)
+ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ KuTmap tmap_k, const __grid_constant__ KuTmap tmap_v, void* __restrict__ Op,
+                     int* __restrict__ status) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const unsigned q_s = ku_smem(smem), k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
+  if (q_s & 1023u) {   // never seen; a misplaced tile would corrupt the MMA operands silently
+    if (threadIdx.x == 0) atomicExch(status, 7);
+    return;
+  }
+  unsigned char* p_tile = smem + Q_BYTES + 4 * KV_BYTES;
+  unsigned long long* bars = (unsigned long long*)(p_tile + 128 * 128);
+  unsigned long long *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7, *s_full = bars + 9, *s_free = bars + 11,
+                     *p_ready = bars + 13, *o_full = bars + 14;
+  unsigned* tmem_base_slot = (unsigned*)(bars + 15);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) query blocks first
+  const int bh = blockIdx.y;
+  const int kv_blocks = (S + TK - 1) / TK;
+  const int nkv = CAUSAL ? ((qb + 1) * (BQ / TK) < kv_blocks ? (qb + 1) * (BQ / TK) : kv_blocks) : kv_blocks;
+
+  if (threadIdx.x == 0) {
+    ku_mbar_init(ku_smem(q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      ku_mbar_init(ku_smem(&k_full[i]), 1); ku_mbar_init(ku_smem(&k_empty[i]), 1); ku_mbar_init(ku_smem(&v_full[i]), 1); ku_mbar_init(ku_smem(&v_empty[i]), 1);
+      ku_mbar_init(ku_smem(&s_full[i]), 1); ku_mbar_init(ku_smem(&s_free[i]), 128);
+    }
+    ku_mbar_init(ku_smem(p_ready), 128); ku_mbar_init(ku_smem(o_full), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ku_smem(tmem_base_slot)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_base_slot;   // columns [0,64) and [64,128): score buffers; [128, 128+DH): O
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer ----
+      ku_mbar_expect(ku_smem(q_full), Q_BYTES);
+      for (int c = 0; c < DCH; ++c) ku_tma_3d(q_s + c * 16384, &tmap_q, c * 64, qb * BQ, bh, ku_smem(q_full));
+      auto load_k = [&](int j) {   // K runs a block ahead of V (see the one-CTA kernel)
+        const int st = j & 1;
+        ku_wait(ku_smem(&k_empty[st]), ((j >> 1) & 1) ^ 1, failed, status);
+        ku_mbar_expect(ku_smem(&k_full[st]), KV_BYTES);
+        for (int c = 0; c < DCH; ++c) ku_tma_3d(k_s + st * KV_BYTES + c * KV_CHUNK, &tmap_k, c * 64, j * TK, bh, ku_smem(&k_full[st]));
+      };
+      if (nkv > 0) load_k(0);
+      if (nkv > 1) load_k(1);
+      for (int j = 0; j < nkv; ++j) {
+        const int st = j & 1;
+        ku_wait(ku_smem(&v_empty[st]), ((j >> 1) & 1) ^ 1, failed, status);
+        ku_mbar_expect(ku_smem(&v_full[st]), KV_BYTES);
+        for (int c = 0; c < DCH; ++c) ku_tma_3d(v_s + st * KV_BYTES + c * KV_CHUNK, &tmap_v, c * 64, j * TK, bh, ku_smem(&v_full[st]));
+        if (j + 2 < nkv) load_k(j + 2);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // ---- MMA issuer ----
+      auto issue_s = [&](int j) {   // S_j = Q K_j^T, 128 x 64
+        const int st = j & 1;
+        ku_wait(ku_smem(&k_full[st]), (j >> 1) & 1, failed, status);
+        ku_wait(ku_smem(&s_free[st]), ((j >> 1) & 1) ^ 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          ku_mma(tmem_base + st * TK, ku_smem_desc(q_s + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                 ku_smem_desc(k_s + st * KV_BYTES + (kk >> 2) * KV_CHUNK + (kk & 3) * 32, 16, 1024), IDESC_S, kk != 0);
+        }
+        ku_mma_commit(ku_smem(&s_full[st]));
+        ku_mma_commit(ku_smem(&k_empty[st]));
+      };
+      ku_wait(ku_smem(q_full), 0, failed, status);
+      if (nkv > 0) issue_s(0);
+      for (int j = 0; j < nkv; ++j) {
+        if (j + 1 < nkv) issue_s(j + 1);
+        const int st = j & 1;
+        ku_wait(ku_smem(&v_full[st]), (j >> 1) & 1, failed, status);
+        ku_wait(ku_smem(p_ready), j & 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < TK / 16; ++kk) {   // O += P_j V_j: P K-major over its 64 keys, V MN-major (head dimension contiguous)
+          const unsigned long long ad = ku_smem_desc(p_s + kk * 32, 16, 1024);
+          const unsigned long long bd = ku_smem_desc(v_s + st * KV_BYTES + kk * 16 * 128, KV_CHUNK, 1024);
+          ku_mma(tmem_base + 128, ad, bd, IDESC_O, (j | kk) != 0);
+        }
+        ku_mma_commit(ku_smem(o_full));
+        ku_mma_commit(ku_smem(&v_empty[st]));
+      }
+    }
+  } else {  // ---- softmax: four warps, one thread per query row ----
+    const int q4 = warp & 3;                      // the TMEM lane quarter this warp may access
+    const int r = q4 * 32 + lane;                 // row of the tile == TMEM lane
+    const int qrow = qb * BQ + r;
+    const unsigned lane_addr = tmem_base + ((unsigned)(q4 * 32) << 16);
+    float m = -KU_INF, l = 0.0f;   // reference maximum (followed lazily, see the one-CTA kernel) and the row's sum
+    for (int j = 0; j < nkv; ++j) {
+      const int st = j & 1;
+      ku_wait(ku_smem(&s_full[st]), (j >> 1) & 1, failed, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool need_mask = (CAUSAL && j * TK + TK - 1 > qb * BQ) || (j * TK + TK > S);
+      float sc[TK];
+      ku_tmem_ld32_nowait(lane_addr + st * TK, sc);
+      ku_tmem_ld32_nowait(lane_addr + st * TK + 32, sc + 32);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < TK; ++c) asm volatile("" : "+f"(sc[c]));   // the values may only be read after the wait
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      ku_mbar_arrive(ku_smem(&s_free[st]));
+      float bm = -KU_INF;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < TK; ++c) {
+          const int key = j * TK + c;
+          sc[c] = ((CAUSAL && key > qrow) || key >= S) ? -KU_INF : sc[c] * SCALE_LOG2E;
+          bm = fmaxf(bm, sc[c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < TK; ++c) { sc[c] *= SCALE_LOG2E; bm = fmaxf(bm, sc[c]); }
+      }
+      const bool grow = bm > m + 8.0f || (m == -KU_INF && bm != -KU_INF);
+      const bool any_grow = __any_sync(0xffffffffu, grow);
+      const float alpha = grow ? ku_ex2(m - bm) : 1.0f;
+      if (grow) m = bm;
+      const float mref = (m == -KU_INF) ? 0.0f : m;
+      float bs = 0.0f;
+      uint4 pk[TK / 8];
+#pragma unroll
+      for (int c0 = 0; c0 < TK; c0 += 8) {
+        float e[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) { e[c] = ku_ex2(sc[c0 + c] - mref); bs += e[c]; }
+        pk[c0 >> 3].x = ku_pack2(e[0], e[1]); pk[c0 >> 3].y = ku_pack2(e[2], e[3]);
+        pk[c0 >> 3].z = ku_pack2(e[4], e[5]); pk[c0 >> 3].w = ku_pack2(e[6], e[7]);
+      }
+      if (j > 0) {   // the previous product must have retired before P is overwritten or O is touched
+        ku_wait(ku_smem(o_full), (j - 1) & 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+      if (any_grow) {
+        if (j > 0) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < DH; c0 += 32) {
+            float v[32];
+            ku_tmem_ld32(lane_addr + 128 + c0, v);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] *= alpha;
+            ku_tmem_st32(lane_addr + 128 + c0, v);
+          }
+        }
+        l *= alpha;
+      }
+#pragma unroll
+      for (int ch = 0; ch < TK / 8; ++ch) *(uint4*)(p_tile + r * 128 + ((ch ^ (r & 7)) << 4)) = pk[ch];
+      l += bs;
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      ku_mbar_arrive(ku_smem(p_ready));
+    }
+    if (nkv > 0) {
+      ku_wait(ku_smem(o_full), (nkv - 1) & 1, failed, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    const float inv = 1.0f / l;
+#pragma unroll 1
+    for (int c0 = 0; c0 < DH; c0 += 32) {
+      float o[32];
+      if (nkv > 0) {
+        ku_tmem_ld32(lane_addr + 128 + c0, o);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o[c] = 0.0f;
+      }
+      if (qrow < S) {
+        uint4* dst = (uint4*)((unsigned short*)Op + ((i64)bh * S + qrow) * DH + c0);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = ku_pack2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv); w.y = ku_pack2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
+          w.z = ku_pack2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv); w.w = ku_pack2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
+          dst[g] = w;
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+}
+#endif  // KU_TWIN
