@@ -354,7 +354,7 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   for (size_t i = 0; i + 2 < r; ++i) bh *= static_cast<int64_t>(shape[i]);
   const uint32_t fmt = dt == DType::BF16 ? 1u : 0u;
   // two CTAs per SM over key blocks of 64 by default; KURUMI_ATTENTION_ONE_CTA selects the one-CTA kernel (key blocks of 128)
-  const bool twin = std::getenv("KURUMI_ATTENTION_ONE_CTA") == nullptr;
+  const bool twin = std::getenv("KURUMI_ATTENTION_ONE_CTA") == nullptr && scale > 0.0f;   // the twin kernel scales the block maximum, which needs a positive scale
   const int64_t tk = twin ? 64 : 128;
   const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tk >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
   const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(dh >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
@@ -362,7 +362,9 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   std::snprintf(lit, sizeof(lit), "%.9gf", static_cast<double>(scale * 1.4426950408889634f));
   std::string src = device_prelude() +
                     defines({{"BH", bh}, {"S", s}, {"DH", dh}, {"CAUSAL", causal ? 1 : 0}, {"IDESC_S", static_cast<int64_t>(idesc_s)}, {"IDESC_O", static_cast<int64_t>(idesc_o)},
-                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", twin ? 1 : 0}}) +
+                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", twin ? 1 : 0},
+                             {"KU_PTMEM", std::getenv("KURUMI_ATTENTION_P_SMEM") ? 0 : 1},
+                             {"KU_POLY", std::getenv("KURUMI_ATTENTION_POLY") ? std::atoi(std::getenv("KURUMI_ATTENTION_POLY")) : 0}}) +
                     "#define SCALE_LOG2E " + lit + "\n" + kSrc_attention_tc;
   out->name = "attention_tc";
   out->kernel = load(src, twin ? "ku_attention_tc_twin" : "ku_attention_tc", true);

@@ -323,6 +323,27 @@ ku_attention_tc(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ K
 // K and V rings 2 x 16 KB each, P 16 KB, barriers: 112.25 KB per CTA, all of it dynamic (the swizzled tiles
 // need 1024-byte alignment, which the start of dynamic shared memory has when nothing static precedes it).
 #define TK 64
+#ifndef KU_POLY
+#define KU_POLY 0   // of every 8 exponentials, how many are computed on the FMA pipe instead of the special-function unit
+#endif
+// 2^x without the special-function unit: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic (relative
+// error 1.2e-4, below the 3.9e-3 rounding step of the bf16 probabilities it feeds), n added to the exponent field.
+// x is clamped at -127, where the result is exactly 0 (masked keys arrive as -inf).
+__device__ __forceinline__ float ku_ex2_fma(float x) {
+  x = fmaxf(x, -127.0f);
+  const float t = x + 12582912.0f;               // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
+  const float f = x - (t - 12582912.0f);
+  const float p = fmaf(fmaf(fmaf(0.05459282547f, f, 0.24221783876f), f, 0.69336861372f), f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+#ifndef KU_PTMEM
+#define KU_PTMEM 1   // P_j goes to tensor memory (over the scores it was computed from) and is the MMA's A operand from there
+#endif
+// D += A B with A in tensor memory (row i of A in lane i, two 16-bit elements per 32-bit column) and B through a shared-memory descriptor
+__device__ __forceinline__ void ku_mma_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 #define Q_BYTES (128 * 128 * DCH)
 #define KV_BYTES (TK * 128 * DCH)
 #define KV_CHUNK (TK * 128)
@@ -391,7 +412,11 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
       auto issue_s = [&](int j) {   // S_j = Q K_j^T, 128 x 64
         const int st = j & 1;
         ku_wait(ku_smem(&k_full[st]), (j >> 1) & 1, failed, status);
+#if !KU_PTMEM
         ku_wait(ku_smem(&s_free[st]), ((j >> 1) & 1) ^ 1, failed, status);
+#endif
+        // with P in tensor memory the buffer last held P_{j-2}: P V_{j-2} was issued before this MMA and MMAs execute in
+        // issue order, and that product was only issued once every softmax thread had read S_{j-2} and stored P_{j-2}
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
@@ -411,9 +436,12 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < TK / 16; ++kk) {   // O += P_j V_j: P K-major over its 64 keys, V MN-major (head dimension contiguous)
-          const unsigned long long ad = ku_smem_desc(p_s + kk * 32, 16, 1024);
           const unsigned long long bd = ku_smem_desc(v_s + st * KV_BYTES + kk * 16 * 128, KV_CHUNK, 1024);
-          ku_mma(tmem_base + 128, ad, bd, IDESC_O, (j | kk) != 0);
+#if KU_PTMEM
+          ku_mma_ts(tmem_base + 128, tmem_base + st * TK + kk * 8, bd, IDESC_O, (j | kk) != 0);   // 16 keys = 8 columns of packed P
+#else
+          ku_mma(tmem_base + 128, ku_smem_desc(p_s + kk * 32, 16, 1024), bd, IDESC_O, (j | kk) != 0);
+#endif
         }
         ku_mma_commit(ku_smem(o_full));
         ku_mma_commit(ku_smem(&v_empty[st]));
@@ -436,36 +464,51 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
       for (int c = 0; c < TK; ++c) asm volatile("" : "+f"(sc[c]));   // the values may only be read after the wait
+#if !KU_PTMEM
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       ku_mbar_arrive(ku_smem(&s_free[st]));
-      float bm = -KU_INF;
+#endif
+      // masked keys at -inf, then the block maximum over four independent chains (a single chain of 64 dependent
+      // maxima would leave the two warps of a scheduler waiting on latency); the scale is applied to the maximum
+      // and folded into the exponent's multiply-add (SCALE_LOG2E > 0)
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < TK; ++c) {
           const int key = j * TK + c;
-          sc[c] = ((CAUSAL && key > qrow) || key >= S) ? -KU_INF : sc[c] * SCALE_LOG2E;
-          bm = fmaxf(bm, sc[c]);
+          if ((CAUSAL && key > qrow) || key >= S) sc[c] = -KU_INF;
         }
-      } else {
-#pragma unroll
-        for (int c = 0; c < TK; ++c) { sc[c] *= SCALE_LOG2E; bm = fmaxf(bm, sc[c]); }
       }
+      float b4[4] = {sc[0], sc[1], sc[2], sc[3]};
+#pragma unroll
+      for (int c = 4; c < TK; ++c) b4[c & 3] = fmaxf(b4[c & 3], sc[c]);
+      const float bm = fmaxf(fmaxf(b4[0], b4[1]), fmaxf(b4[2], b4[3])) * SCALE_LOG2E;
       const bool grow = bm > m + 8.0f || (m == -KU_INF && bm != -KU_INF);
       const bool any_grow = __any_sync(0xffffffffu, grow);
       const float alpha = grow ? ku_ex2(m - bm) : 1.0f;
       if (grow) m = bm;
-      const float mref = (m == -KU_INF) ? 0.0f : m;
-      float bs = 0.0f;
+      const float nref = (m == -KU_INF) ? 0.0f : -m;
+      float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       uint4 pk[TK / 8];
 #pragma unroll
       for (int c0 = 0; c0 < TK; c0 += 8) {
         float e[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) { e[c] = ku_ex2(sc[c0 + c] - mref); bs += e[c]; }
+        for (int c = 0; c < 8; ++c) {
+          const float x = fmaf(sc[c0 + c], SCALE_LOG2E, nref);
+          e[c] = (c >= 8 - KU_POLY) ? ku_ex2_fma(x) : ku_ex2(x);
+          s4[c & 3] += e[c];
+        }
         pk[c0 >> 3].x = ku_pack2(e[0], e[1]); pk[c0 >> 3].y = ku_pack2(e[2], e[3]);
         pk[c0 >> 3].z = ku_pack2(e[4], e[5]); pk[c0 >> 3].w = ku_pack2(e[6], e[7]);
       }
+      const float bs = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+#if KU_PTMEM
+      // P_j overwrites the scores it came from (this lane's own columns), so only a rescale of O has to wait for the
+      // previous product; o_full can be at most one phase ahead of this wait because P V_j needs this thread's arrival
+      if (any_grow && j > 0) {
+#else
       if (j > 0) {   // the previous product must have retired before P is overwritten or O is touched
+#endif
         ku_wait(ku_smem(o_full), (j - 1) & 1, failed, status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       }
@@ -482,11 +525,16 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
         }
         l *= alpha;
       }
+      l += bs;
+#if KU_PTMEM
+      ku_tmem_st32(lane_addr + st * TK, (const float*)pk);   // 64 bf16 = 32 columns, waits for the store
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#else
 #pragma unroll
       for (int ch = 0; ch < TK / 8; ++ch) *(uint4*)(p_tile + r * 128 + ((ch ^ (r & 7)) << 4)) = pk[ch];
-      l += bs;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
       ku_mbar_arrive(ku_smem(p_ready));
     }
     if (nkv > 0) {
