@@ -344,6 +344,14 @@ __device__ __forceinline__ void ku_mma_ts(unsigned d_tmem, unsigned a_tmem, unsi
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+#ifndef KU_PHASES
+#define KU_PHASES 0   // 1: one CTA prints the clocks its softmax thread 0 and its MMA thread spent per phase (measurement builds only)
+#endif
+#if KU_PHASES
+#define KU_TICK(i) { long long t_; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_)); ph[i] += t_ - t_prev; t_prev = t_; }
+#else
+#define KU_TICK(i)
+#endif
 #define Q_BYTES (128 * 128 * DCH)
 #define KV_BYTES (TK * 128 * DCH)
 #define KV_CHUNK (TK * 128)
@@ -428,11 +436,18 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
       };
       ku_wait(ku_smem(q_full), 0, failed, status);
       if (nkv > 0) issue_s(0);
+#if KU_PHASES
+      long long ph[4] = {0, 0, 0, 0}, t_prev;
+      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_prev));
+#endif
       for (int j = 0; j < nkv; ++j) {
         if (j + 1 < nkv) issue_s(j + 1);
+        KU_TICK(0)
         const int st = j & 1;
         ku_wait(ku_smem(&v_full[st]), (j >> 1) & 1, failed, status);
+        KU_TICK(1)
         ku_wait(ku_smem(p_ready), j & 1, failed, status);
+        KU_TICK(2)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < TK / 16; ++kk) {   // O += P_j V_j: P K-major over its 64 keys, V MN-major (head dimension contiguous)
@@ -445,7 +460,12 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
         }
         ku_mma_commit(ku_smem(o_full));
         ku_mma_commit(ku_smem(&v_empty[st]));
+        KU_TICK(3)
       }
+#if KU_PHASES
+      if (blockIdx.x == 0 && blockIdx.y == 40)
+        printf("MMA thread, %d key blocks: issue S (incl. wait K) %lld, wait V %lld, wait P %lld, issue PV %lld\n", nkv, ph[0] / nkv, ph[1] / nkv, ph[2] / nkv, ph[3] / nkv);
+#endif
     }
   } else {  // ---- softmax: four warps, one thread per query row ----
     const int q4 = warp & 3;                      // the TMEM lane quarter this warp may access
@@ -453,9 +473,14 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
     const int qrow = qb * BQ + r;
     const unsigned lane_addr = tmem_base + ((unsigned)(q4 * 32) << 16);
     float m = -KU_INF, l = 0.0f;   // reference maximum (followed lazily, see the one-CTA kernel) and the row's sum
+#if KU_PHASES
+    long long ph[6] = {0, 0, 0, 0, 0, 0}, t_prev;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_prev));
+#endif
     for (int j = 0; j < nkv; ++j) {
       const int st = j & 1;
       ku_wait(ku_smem(&s_full[st]), (j >> 1) & 1, failed, status);
+      KU_TICK(0)
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool need_mask = (CAUSAL && j * TK + TK - 1 > qb * BQ) || (j * TK + TK > S);
       float sc[TK];
@@ -464,6 +489,7 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
       for (int c = 0; c < TK; ++c) asm volatile("" : "+f"(sc[c]));   // the values may only be read after the wait
+      KU_TICK(1)
 #if !KU_PTMEM
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       ku_mbar_arrive(ku_smem(&s_free[st]));
@@ -487,6 +513,7 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
       const float alpha = grow ? ku_ex2(m - bm) : 1.0f;
       if (grow) m = bm;
       const float nref = (m == -KU_INF) ? 0.0f : -m;
+      KU_TICK(2)
       float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       uint4 pk[TK / 8];
 #pragma unroll
@@ -502,6 +529,10 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
         pk[c0 >> 3].z = ku_pack2(e[4], e[5]); pk[c0 >> 3].w = ku_pack2(e[6], e[7]);
       }
       const float bs = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+#if KU_PHASES
+      asm volatile("" :: "f"(bs), "r"(pk[0].x), "r"(pk[7].w));
+#endif
+      KU_TICK(3)
 #if KU_PTMEM
       // P_j overwrites the scores it came from (this lane's own columns), so only a rescale of O has to wait for the
       // previous product; o_full can be at most one phase ahead of this wait because P V_j needs this thread's arrival
@@ -526,6 +557,7 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
         l *= alpha;
       }
       l += bs;
+      KU_TICK(4)
 #if KU_PTMEM
       ku_tmem_st32(lane_addr + st * TK, (const float*)pk);   // 64 bf16 = 32 columns, waits for the store
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -536,7 +568,13 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 #endif
       ku_mbar_arrive(ku_smem(p_ready));
+      KU_TICK(5)
     }
+#if KU_PHASES
+    if (blockIdx.x == 0 && blockIdx.y == 40 && threadIdx.x == 64)
+      printf("softmax thread, %d key blocks: wait S %lld, load %lld, max %lld, exp+pack %lld, rescale %lld, store+arrive %lld\n", nkv, ph[0] / nkv, ph[1] / nkv,
+             ph[2] / nkv, ph[3] / nkv, ph[4] / nkv, ph[5] / nkv);
+#endif
     if (nkv > 0) {
       ku_wait(ku_smem(o_full), (nkv - 1) & 1, failed, status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
