@@ -353,8 +353,16 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   int64_t bh = 1;
   for (size_t i = 0; i + 2 < r; ++i) bh *= static_cast<int64_t>(shape[i]);
   const uint32_t fmt = dt == DType::BF16 ? 1u : 0u;
-  // two CTAs per SM over key blocks of 64 by default; KURUMI_ATTENTION_ONE_CTA selects the one-CTA kernel (key blocks of 128)
-  const bool twin = std::getenv("KURUMI_ATTENTION_ONE_CTA") == nullptr && scale > 0.0f;   // the twin kernel scales the block maximum, which needs a positive scale
+  // Three arrangements of the same algorithm (KURUMI_ATTENTION_VARIANT = duo | twin | one; KURUMI_ATTENTION_ONE_CTA = one):
+  //   duo   one CTA per 256 queries: two query tiles share each K / V block of 128 keys, P in tensor memory (default)
+  //   twin  two CTAs of 128 queries per SM over key blocks of 64, P in tensor memory
+  //   one   one CTA of 128 queries per SM, key blocks of 128, P through shared memory
+  // duo and twin scale the block maximum instead of every score, which needs a positive scale.
+  const char* var = std::getenv("KURUMI_ATTENTION_VARIANT");
+  int variant = 2;
+  if (var && std::string(var) == "twin") variant = 1;
+  if ((var && std::string(var) == "one") || std::getenv("KURUMI_ATTENTION_ONE_CTA") || !(scale > 0.0f)) variant = 0;
+  const bool twin = variant == 1, duo = variant == 2;
   const int64_t tk = twin ? 64 : 128;
   const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tk >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
   const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(dh >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
@@ -362,16 +370,20 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   std::snprintf(lit, sizeof(lit), "%.9gf", static_cast<double>(scale * 1.4426950408889634f));
   std::string src = device_prelude() +
                     defines({{"BH", bh}, {"S", s}, {"DH", dh}, {"CAUSAL", causal ? 1 : 0}, {"IDESC_S", static_cast<int64_t>(idesc_s)}, {"IDESC_O", static_cast<int64_t>(idesc_o)},
-                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", twin ? 1 : 0},
+                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", variant},
                              {"KU_PTMEM", std::getenv("KURUMI_ATTENTION_P_SMEM") ? 0 : 1}, {"KU_PHASES", std::getenv("KURUMI_ATTENTION_PHASES") ? 1 : 0},
                              {"KU_POLY", std::getenv("KURUMI_ATTENTION_POLY") ? std::atoi(std::getenv("KURUMI_ATTENTION_POLY")) : 0}}) +
                     "#define SCALE_LOG2E " + lit + "\n" + kSrc_attention_tc;
   out->name = "attention_tc";
-  out->kernel = load(src, twin ? "ku_attention_tc_twin" : "ku_attention_tc", true);
-  out->grid[0] = static_cast<unsigned>((s + 127) / 128);
+  out->kernel = load(src, duo ? "ku_attention_tc_duo" : twin ? "ku_attention_tc_twin" : "ku_attention_tc", true);
+  out->grid[0] = static_cast<unsigned>(duo ? (s + 255) / 256 : (s + 127) / 128);
   out->grid[1] = static_cast<unsigned>(bh);
   const int64_t tile = 128 * 128 * (dh / 64);
-  if (twin) {
+  if (duo) {
+    out->block[0] = 320;   // TMA warp, MMA warp, a softmax warpgroup per query tile
+    // two Q tiles, two K and two V stages, barriers; at least 120 KB so that an SM (512 columns of tensor memory) holds one CTA
+    out->smem = static_cast<unsigned>(std::max<int64_t>(6 * tile + 256, 120 * 1024));
+  } else if (twin) {
     out->block[0] = 192;   // TMA warp, MMA warp, 4 softmax warps
     // Q, two K and two V stages of 64 keys, P, barriers; at least 80 KB so that no third CTA (which would wait for tensor memory) joins an SM
     out->smem = static_cast<unsigned>(std::max<int64_t>(tile + 4 * (tile / 2) + 128 * 128 + 128, 80 * 1024));

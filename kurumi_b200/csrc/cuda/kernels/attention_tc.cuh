@@ -356,6 +356,7 @@ __device__ __forceinline__ void ku_mma_ts(unsigned d_tmem, unsigned a_tmem, unsi
 #define KV_BYTES (TK * 128 * DCH)
 #define KV_CHUNK (TK * 128)
 
+#if KU_TWIN == 1
 extern "C" __global__ void __launch_bounds__(192, 2)
 ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ KuTmap tmap_k, const __grid_constant__ KuTmap tmap_v, void* __restrict__ Op,
                      int* __restrict__ status) {
@@ -605,4 +606,235 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
   __syncthreads();
   if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
 }
+#endif  // KU_TWIN == 1
+
+#if KU_TWIN == 2
+// ---- Two query tiles per CTA -------------------------------------------------------------------------------
+// One CTA per (head, 256 queries): two tiles of 128 query rows share every K_j / V_j block (128 keys), each with its
+// own softmax warpgroup, score buffer and accumulator in tensor memory:
+//   columns [0,128) S_0 (P_0 packed over its first 64 columns), [128,256) S_1 / P_1, [256,384) O_0, [384,512) O_1.
+// The MMA thread alternates between the tiles, P V of a tile followed at once by the tile's next score block:
+//   ... P_0 V_j, S_0 = Q_0 K_{j+1}^T, P_1 V_j, S_1 = Q_1 K_{j+1}^T, ...
+// so that one tile's exponentials run while the tensor core works for the other tile. MMAs execute in issue order,
+// which is what lets S_t(j+1) overwrite the P_t(j) that the product issued just before it reads.
+// Shared-memory traffic per 128 x 128 block (the bound of the smaller kernels, which re-read Q and P from shared
+// memory and load K / V per tile): Q K^T 64 KB + V 32 KB + half a K / V load 32 KB = 128 KB.
+// Shared memory (DH = 128): Q 2 x 32 KB, K and V rings 2 x 32 KB each = 192 KB + barriers, all dynamic.
+#define Q_BYTES TILE_BYTES
+
+__device__ __forceinline__ void ku_tmem_st32_nowait(unsigned taddr, const unsigned* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
+      "%24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]),
+        "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]),
+        "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+extern "C" __global__ void __launch_bounds__(320, 1)
+ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ KuTmap tmap_k, const __grid_constant__ KuTmap tmap_v, void* __restrict__ Op,
+                    int* __restrict__ status) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const unsigned q_s = ku_smem(smem), k_s = q_s + 2 * Q_BYTES, v_s = k_s + 2 * TILE_BYTES;
+  if (q_s & 1023u) {   // never seen; a misplaced tile would corrupt the MMA operands silently
+    if (threadIdx.x == 0) atomicExch(status, 7);
+    return;
+  }
+  unsigned long long* bars = (unsigned long long*)(smem + 2 * Q_BYTES + 4 * TILE_BYTES);
+  unsigned long long *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7, *s_full = bars + 9, *p_ready = bars + 11,
+                     *o_full = bars + 13;
+  unsigned* tmem_base_slot = (unsigned*)(bars + 15);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qp = (int)gridDim.x - 1 - (int)blockIdx.x;   // pair of query blocks (2 qp, 2 qp + 1); long (late) pairs first
+  const int bh = blockIdx.y;
+  const int kv_blocks = (S + BKV - 1) / BKV;
+  // key blocks per tile: under the causal mask tile 0 stops one block before tile 1
+  const int n0 = CAUSAL ? ((2 * qp + 1) < kv_blocks ? (2 * qp + 1) : kv_blocks) : kv_blocks;
+  const int n1 = CAUSAL ? ((2 * qp + 2) < kv_blocks ? (2 * qp + 2) : kv_blocks) : kv_blocks;
+
+  if (threadIdx.x == 0) {
+    ku_mbar_init(ku_smem(q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      ku_mbar_init(ku_smem(&k_full[i]), 1); ku_mbar_init(ku_smem(&k_empty[i]), 1); ku_mbar_init(ku_smem(&v_full[i]), 1); ku_mbar_init(ku_smem(&v_empty[i]), 1);
+      ku_mbar_init(ku_smem(&s_full[i]), 1); ku_mbar_init(ku_smem(&p_ready[i]), 128); ku_mbar_init(ku_smem(&o_full[i]), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ku_smem(tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_base_slot;
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer: both Q tiles once, then K_j / V_j for the longer tile's blocks ----
+      ku_mbar_expect(ku_smem(q_full), 2 * Q_BYTES);
+      for (int t = 0; t < 2; ++t)
+        for (int c = 0; c < DCH; ++c) ku_tma_3d(q_s + t * Q_BYTES + c * 16384, &tmap_q, c * 64, (2 * qp + t) * BQ, bh, ku_smem(q_full));
+      auto load_k = [&](int j) {
+        const int st = j & 1;
+        ku_wait(ku_smem(&k_empty[st]), ((j >> 1) & 1) ^ 1, failed, status);
+        ku_mbar_expect(ku_smem(&k_full[st]), TILE_BYTES);
+        for (int c = 0; c < DCH; ++c) ku_tma_3d(k_s + st * TILE_BYTES + c * 16384, &tmap_k, c * 64, j * BKV, bh, ku_smem(&k_full[st]));
+      };
+      load_k(0);
+      if (n1 > 1) load_k(1);
+      for (int j = 0; j < n1; ++j) {
+        const int st = j & 1;
+        ku_wait(ku_smem(&v_empty[st]), ((j >> 1) & 1) ^ 1, failed, status);
+        ku_mbar_expect(ku_smem(&v_full[st]), TILE_BYTES);
+        for (int c = 0; c < DCH; ++c) ku_tma_3d(v_s + st * TILE_BYTES + c * 16384, &tmap_v, c * 64, j * BKV, bh, ku_smem(&v_full[st]));
+        if (j + 2 < n1) load_k(j + 2);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // ---- MMA issuer ----
+      auto issue_s = [&](int t, int j) {   // S_t = Q_t K_j^T (K_j has been waited for by the caller)
+        const int st = j & 1;
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          const unsigned off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          ku_mma(tmem_base + t * 128, ku_smem_desc(q_s + t * Q_BYTES + off, 16, 1024), ku_smem_desc(k_s + st * TILE_BYTES + off, 16, 1024), IDESC_S, kk != 0);
+        }
+        ku_mma_commit(ku_smem(&s_full[t]));
+      };
+      auto issue_pv = [&](int t, int j) {   // O_t += P_t V_j: P_t from tensor memory (16 keys = 8 columns), V MN-major from shared memory
+        const int st = j & 1;
+        ku_wait(ku_smem(&p_ready[t]), j & 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          ku_mma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, ku_smem_desc(v_s + st * TILE_BYTES + kk * 16 * 128, 16384, 1024), IDESC_O, (j | kk) != 0);
+        ku_mma_commit(ku_smem(&o_full[t]));
+      };
+      ku_wait(ku_smem(q_full), 0, failed, status);
+      ku_wait(ku_smem(&k_full[0]), 0, failed, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      issue_s(0, 0);
+      issue_s(1, 0);
+      ku_mma_commit(ku_smem(&k_empty[0]));
+      for (int j = 0; j < n1; ++j) {
+        const int st = j & 1, nx = (j + 1) & 1;
+        ku_wait(ku_smem(&v_full[st]), (j >> 1) & 1, failed, status);
+        if (j < n0) issue_pv(0, j);
+        if (j + 1 < n1) ku_wait(ku_smem(&k_full[nx]), ((j + 1) >> 1) & 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (j + 1 < n0) issue_s(0, j + 1);
+        issue_pv(1, j);
+        ku_mma_commit(ku_smem(&v_empty[st]));
+        if (j + 1 < n1) {
+          issue_s(1, j + 1);
+          ku_mma_commit(ku_smem(&k_empty[nx]));
+        }
+      }
+    }
+  } else {  // ---- softmax: a warpgroup per tile, one thread per query row ----
+    const int t = (warp - 2) >> 2;                // the tile
+    const int q4 = warp & 3;                      // the TMEM lane quarter this warp may access
+    const int r = q4 * 32 + lane;                 // row of the tile == TMEM lane
+    const int qb = 2 * qp + t;
+    const int qrow = qb * BQ + r;
+    const int nkv = t ? n1 : n0;
+    const unsigned s_addr = tmem_base + ((unsigned)(q4 * 32) << 16) + t * 128;
+    const unsigned o_addr = tmem_base + ((unsigned)(q4 * 32) << 16) + 256 + t * 128;
+    float m = -KU_INF, l = 0.0f;   // reference maximum (followed lazily, see the one-CTA kernel) and the row's sum
+    for (int j = 0; j < nkv; ++j) {
+      ku_wait(ku_smem(&s_full[t]), j & 1, failed, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool need_mask = (CAUSAL && j == qb) || (j * BKV + BKV > S);
+      float sc[BKV];
+#pragma unroll
+      for (int c0 = 0; c0 < BKV; c0 += 32) ku_tmem_ld32_nowait(s_addr + c0, sc + c0);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < BKV; ++c) asm volatile("" : "+f"(sc[c]));   // the values may only be read after the wait
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < BKV; ++c) {
+          const int key = j * BKV + c;
+          if ((CAUSAL && key > qrow) || key >= S) sc[c] = -KU_INF;
+        }
+      }
+      float b4[4] = {sc[0], sc[1], sc[2], sc[3]};
+#pragma unroll
+      for (int c = 4; c < BKV; ++c) b4[c & 3] = fmaxf(b4[c & 3], sc[c]);
+      const float bm = fmaxf(fmaxf(b4[0], b4[1]), fmaxf(b4[2], b4[3])) * SCALE_LOG2E;   // SCALE_LOG2E > 0
+      const bool grow = bm > m + 8.0f || (m == -KU_INF && bm != -KU_INF);
+      const bool any_grow = __any_sync(0xffffffffu, grow);
+      const float alpha = grow ? ku_ex2(m - bm) : 1.0f;
+      if (grow) m = bm;
+      const float nref = (m == -KU_INF) ? 0.0f : -m;
+      float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      // the probabilities, 64 keys (32 packed columns) at a time, over the first half of the scores they came from
+      // (all of this lane's scores are in registers by now)
+#pragma unroll
+      for (int h = 0; h < BKV / 64; ++h) {
+        unsigned pk[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          const float e0 = ku_ex2(fmaf(sc[h * 64 + c], SCALE_LOG2E, nref));
+          const float e1 = ku_ex2(fmaf(sc[h * 64 + c + 1], SCALE_LOG2E, nref));
+          s4[(c >> 1) & 3] += e0 + e1;
+          pk[c >> 1] = ku_pack2(e0, e1);
+        }
+        ku_tmem_st32_nowait(s_addr + h * 32, pk);
+      }
+      // only a rescale of O has to wait for the tile's previous product (its score block was issued after that
+      // product, so the wait is over by now; o_full can be at most one phase ahead of it)
+      if (any_grow) {
+        if (j > 0) {
+          ku_wait(ku_smem(&o_full[t]), (j - 1) & 1, failed, status);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+          for (int c0 = 0; c0 < DH; c0 += 32) {
+            float v[32];
+            ku_tmem_ld32(o_addr + c0, v);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] *= alpha;
+            ku_tmem_st32(o_addr + c0, v);
+          }
+        }
+        l *= alpha;
+      }
+      l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      ku_mbar_arrive(ku_smem(&p_ready[t]));
+    }
+    if (nkv > 0) {
+      ku_wait(ku_smem(&o_full[t]), (nkv - 1) & 1, failed, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    const float inv = 1.0f / l;
+#pragma unroll 1
+    for (int c0 = 0; c0 < DH; c0 += 32) {
+      float o[32];
+      if (nkv > 0) {
+        ku_tmem_ld32(o_addr + c0, o);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o[c] = 0.0f;
+      }
+      if (qrow < S) {
+        uint4* dst = (uint4*)((unsigned short*)Op + ((i64)bh * S + qrow) * DH + c0);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = ku_pack2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv); w.y = ku_pack2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
+          w.z = ku_pack2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv); w.w = ku_pack2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
+          dst[g] = w;
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+}
+#endif  // KU_TWIN == 2
 #endif  // KU_TWIN

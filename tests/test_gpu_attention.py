@@ -15,7 +15,7 @@ def bf16(rng, shape, scale=1.0):
 
 
 @pytest.mark.parametrize("shape,causal", [((2, 3, 256, 128), True), ((1, 2, 384, 64), True), ((2, 200, 128), True), ((1, 1, 128, 128), False),
-                                          ((3, 130, 64), False), ((1, 4, 1, 128), True), ((1, 2, 640, 128), True)])
+                                          ((3, 130, 64), False), ((1, 4, 1, 128), True), ((1, 2, 640, 128), True), ((2, 1100, 64), True), ((1, 2, 1000, 128), False)])
 def test_fused_attention_matches_oracle(oracle_lib, cuda_lib, cpu, cpu64, gpu, shape, causal):
     rng = np.random.default_rng(40)
     p = Pair(oracle_lib, cuda_lib)
@@ -31,6 +31,19 @@ def test_fused_attention_matches_oracle(oracle_lib, cuda_lib, cpu, cpu64, gpu, s
     if causal:   # query 0 attends to key 0 only (kurumi_core/tests/ops.rs:258-270)
         vv = util.to_f64(p.feeds[v][0], api.BF16)
         assert np.array_equal(got[..., 0, :], vv[..., 0, :])
+
+
+@pytest.mark.parametrize("variant", ["duo", "twin", "one"])
+def test_every_arrangement_of_the_kernel(oracle_lib, cuda_lib, cpu64, gpu, monkeypatch, variant):
+    """The three arrangements (two query tiles per CTA, two CTAs per SM, one CTA per SM) compute the same attention."""
+    monkeypatch.setenv("KURUMI_ATTENTION_VARIANT", variant)
+    rng = np.random.default_rng(43)
+    for shape, causal in (((2, 2, 900, 128), True), ((1, 3, 520, 64), False), ((1, 1, 257, 128), True)):
+        p = Pair(oracle_lib, cuda_lib)
+        q, k, v = (p.feed(shape, api.BF16, bf16(rng, shape, 2.0)) for _ in range(3))
+        out = p.sdpa_fused(q, k, v, causal)
+        w, c, dts = p.run(cpu64, gpu, [out])
+        util.assert_close(w[0], util.to_f64(c[0], dts[0]), 2e-2, 2e-2 * np.abs(w[0]).max(), f"{variant} {shape}")
 
 
 def test_decomposed_attention_and_auto_selection(oracle_lib, cuda_lib, cpu, cpu64, gpu):
