@@ -363,6 +363,13 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   if (var && std::string(var) == "twin") variant = 1;
   if ((var && std::string(var) == "one") || std::getenv("KURUMI_ATTENTION_ONE_CTA") || !(scale > 0.0f)) variant = 0;
   const bool twin = variant == 1, duo = variant == 2;
+  // duo: stages of the K and V rings (KURUMI_ATTENTION_STAGES=k,v, 2 or 3 each, at most 5 together at DH = 128 where a stage is 32 KB).
+  // Two each by default: 2 + 3 and 3 + 2 measured the same on the causal 4096-key configuration, the loads are not what the MMA thread waits for.
+  int64_t nks = 2, nvs = 2;
+  if (const char* e = std::getenv("KURUMI_ATTENTION_STAGES")) {
+    int a = 0, b = 0;
+    if (std::sscanf(e, "%d,%d", &a, &b) == 2 && a >= 2 && a <= 3 && b >= 2 && b <= 3 && (dh == 64 || a + b <= 5)) { nks = a; nvs = b; }
+  }
   const int64_t tk = twin ? 64 : 128;
   const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tk >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
   const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(dh >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
@@ -370,7 +377,7 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   std::snprintf(lit, sizeof(lit), "%.9gf", static_cast<double>(scale * 1.4426950408889634f));
   std::string src = device_prelude() +
                     defines({{"BH", bh}, {"S", s}, {"DH", dh}, {"CAUSAL", causal ? 1 : 0}, {"IDESC_S", static_cast<int64_t>(idesc_s)}, {"IDESC_O", static_cast<int64_t>(idesc_o)},
-                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", variant},
+                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", variant}, {"NKS", nks}, {"NVS", nvs},
                              {"KU_PTMEM", std::getenv("KURUMI_ATTENTION_P_SMEM") ? 0 : 1}, {"KU_PHASES", std::getenv("KURUMI_ATTENTION_PHASES") ? 1 : 0},
                              {"KU_POLY", std::getenv("KURUMI_ATTENTION_POLY") ? std::atoi(std::getenv("KURUMI_ATTENTION_POLY")) : 0}}) +
                     "#define SCALE_LOG2E " + lit + "\n" + kSrc_attention_tc;
@@ -382,7 +389,7 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   if (duo) {
     out->block[0] = 320;   // TMA warp, MMA warp, a softmax warpgroup per query tile
     // two Q tiles, two K and two V stages, barriers; at least 120 KB so that an SM (512 columns of tensor memory) holds one CTA
-    out->smem = static_cast<unsigned>(std::max<int64_t>(6 * tile + 256, 120 * 1024));
+    out->smem = static_cast<unsigned>(std::max<int64_t>((2 + nks + nvs) * tile + 256, 120 * 1024));
   } else if (twin) {
     out->block[0] = 192;   // TMA warp, MMA warp, 4 softmax warps
     // Q, two K and two V stages of 64 keys, P, barriers; at least 80 KB so that no third CTA (which would wait for tensor memory) joins an SM

@@ -619,7 +619,15 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
 // which is what lets S_t(j+1) overwrite the P_t(j) that the product issued just before it reads.
 // Shared-memory traffic per 128 x 128 block (the bound of the smaller kernels, which re-read Q and P from shared
 // memory and load K / V per tile): Q K^T 64 KB + V 32 KB + half a K / V load 32 KB = 128 KB.
-// Shared memory (DH = 128): Q 2 x 32 KB, K and V rings 2 x 32 KB each = 192 KB + barriers, all dynamic.
+// Shared memory (DH = 128): Q 2 x 32 KB, a K ring of NKS and a V ring of NVS stages of 32 KB (2 + 2: 192 KB) + barriers,
+// all dynamic. The load into a stage is requested when the MMAs that read its previous content have retired.
+#ifndef NKS
+#define NKS 2
+#endif
+#ifndef NVS
+#define NVS 2
+#endif
+#undef Q_BYTES
 #define Q_BYTES TILE_BYTES
 
 __device__ __forceinline__ void ku_tmem_st32_nowait(unsigned taddr, const unsigned* r) {
@@ -636,15 +644,15 @@ extern "C" __global__ void __launch_bounds__(320, 1)
 ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ KuTmap tmap_k, const __grid_constant__ KuTmap tmap_v, void* __restrict__ Op,
                     int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  const unsigned q_s = ku_smem(smem), k_s = q_s + 2 * Q_BYTES, v_s = k_s + 2 * TILE_BYTES;
+  const unsigned q_s = ku_smem(smem), k_s = q_s + 2 * Q_BYTES, v_s = k_s + NKS * TILE_BYTES;
   if (q_s & 1023u) {   // never seen; a misplaced tile would corrupt the MMA operands silently
     if (threadIdx.x == 0) atomicExch(status, 7);
     return;
   }
-  unsigned long long* bars = (unsigned long long*)(smem + 2 * Q_BYTES + 4 * TILE_BYTES);
-  unsigned long long *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7, *s_full = bars + 9, *p_ready = bars + 11,
-                     *o_full = bars + 13;
-  unsigned* tmem_base_slot = (unsigned*)(bars + 15);
+  unsigned long long* bars = (unsigned long long*)(smem + 2 * Q_BYTES + (NKS + NVS) * TILE_BYTES);
+  unsigned long long *q_full = bars, *k_full = bars + 1, *k_empty = k_full + NKS, *v_full = k_empty + NKS, *v_empty = v_full + NVS, *s_full = v_empty + NVS,
+                     *p_ready = s_full + 2, *o_full = p_ready + 2;
+  unsigned* tmem_base_slot = (unsigned*)(o_full + 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qp = (int)gridDim.x - 1 - (int)blockIdx.x;   // pair of query blocks (2 qp, 2 qp + 1); long (late) pairs first
   const int bh = blockIdx.y;
@@ -655,10 +663,9 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     ku_mbar_init(ku_smem(q_full), 1);
-    for (int i = 0; i < 2; ++i) {
-      ku_mbar_init(ku_smem(&k_full[i]), 1); ku_mbar_init(ku_smem(&k_empty[i]), 1); ku_mbar_init(ku_smem(&v_full[i]), 1); ku_mbar_init(ku_smem(&v_empty[i]), 1);
-      ku_mbar_init(ku_smem(&s_full[i]), 1); ku_mbar_init(ku_smem(&p_ready[i]), 128); ku_mbar_init(ku_smem(&o_full[i]), 1);
-    }
+    for (int i = 0; i < NKS; ++i) { ku_mbar_init(ku_smem(&k_full[i]), 1); ku_mbar_init(ku_smem(&k_empty[i]), 1); }
+    for (int i = 0; i < NVS; ++i) { ku_mbar_init(ku_smem(&v_full[i]), 1); ku_mbar_init(ku_smem(&v_empty[i]), 1); }
+    for (int i = 0; i < 2; ++i) { ku_mbar_init(ku_smem(&s_full[i]), 1); ku_mbar_init(ku_smem(&p_ready[i]), 128); ku_mbar_init(ku_smem(&o_full[i]), 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -677,25 +684,34 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
       for (int t = 0; t < 2; ++t)
         for (int c = 0; c < DCH; ++c) ku_tma_3d(q_s + t * Q_BYTES + c * 16384, &tmap_q, c * 64, (2 * qp + t) * BQ, bh, ku_smem(q_full));
       auto load_k = [&](int j) {
-        const int st = j & 1;
-        ku_wait(ku_smem(&k_empty[st]), ((j >> 1) & 1) ^ 1, failed, status);
+        const int st = j % NKS;
+        ku_wait(ku_smem(&k_empty[st]), ((j / NKS) & 1) ^ 1, failed, status);
         ku_mbar_expect(ku_smem(&k_full[st]), TILE_BYTES);
         for (int c = 0; c < DCH; ++c) ku_tma_3d(k_s + st * TILE_BYTES + c * 16384, &tmap_k, c * 64, j * BKV, bh, ku_smem(&k_full[st]));
       };
-      load_k(0);
-      if (n1 > 1) load_k(1);
-      for (int j = 0; j < n1; ++j) {
-        const int st = j & 1;
-        ku_wait(ku_smem(&v_empty[st]), ((j >> 1) & 1) ^ 1, failed, status);
+      auto load_v = [&](int j) {
+        const int st = j % NVS;
+        ku_wait(ku_smem(&v_empty[st]), ((j / NVS) & 1) ^ 1, failed, status);
         ku_mbar_expect(ku_smem(&v_full[st]), TILE_BYTES);
         for (int c = 0; c < DCH; ++c) ku_tma_3d(v_s + st * TILE_BYTES + c * 16384, &tmap_v, c * 64, j * BKV, bh, ku_smem(&v_full[st]));
-        if (j + 2 < n1) load_k(j + 2);
+      };
+      // K_0 first (the first scores need it), then the rings are filled; after that block j's turn requests K_{j+NKS}
+      // (free once both tiles' scores of block j have retired) and V_{j+NVS-1} (free since the products of block j-1)
+      load_k(0);
+      for (int j = 0; j < NVS - 1 && j < n1; ++j) load_v(j);
+      for (int j = 1; j < NKS && j < n1; ++j) load_k(j);
+      for (int j = 0; j < n1; ++j) {
+        if (j + NKS < n1) load_k(j + NKS);
+        if (j + NVS - 1 < n1) load_v(j + NVS - 1);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer ----
+#if KU_PHASES
+      long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t_prev = 0;
+#endif
       auto issue_s = [&](int t, int j) {   // S_t = Q_t K_j^T (K_j has been waited for by the caller)
-        const int st = j & 1;
+        const int st = j % NKS;
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
           const unsigned off = (kk >> 2) * 16384 + (kk & 3) * 32;
@@ -704,8 +720,9 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
         ku_mma_commit(ku_smem(&s_full[t]));
       };
       auto issue_pv = [&](int t, int j) {   // O_t += P_t V_j: P_t from tensor memory (16 keys = 8 columns), V MN-major from shared memory
-        const int st = j & 1;
+        const int st = j % NVS;
         ku_wait(ku_smem(&p_ready[t]), j & 1, failed, status);
+        KU_TICK(1 + 4 * t)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk)
@@ -718,20 +735,38 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
       issue_s(0, 0);
       issue_s(1, 0);
       ku_mma_commit(ku_smem(&k_empty[0]));
+#if KU_PHASES
+      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_prev));
+      for (int i = 0; i < 8; ++i) ph[i] = 0;
+#endif
       for (int j = 0; j < n1; ++j) {
-        const int st = j & 1, nx = (j + 1) & 1;
-        ku_wait(ku_smem(&v_full[st]), (j >> 1) & 1, failed, status);
+        const int st = j % NVS, nx = (j + 1) % NKS;
+#if KU_PHASES
+        if (j == 4) { for (int i = 0; i < 8; ++i) ph[i] = 0; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_prev)); }
+#endif
+        ku_wait(ku_smem(&v_full[st]), (j / NVS) & 1, failed, status);
+        KU_TICK(0)
         if (j < n0) issue_pv(0, j);
-        if (j + 1 < n1) ku_wait(ku_smem(&k_full[nx]), ((j + 1) >> 1) & 1, failed, status);
+        KU_TICK(2)
+        if (j + 1 < n1) ku_wait(ku_smem(&k_full[nx]), ((j + 1) / NKS) & 1, failed, status);
+        KU_TICK(3)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (j + 1 < n0) issue_s(0, j + 1);
+        KU_TICK(4)
         issue_pv(1, j);
         ku_mma_commit(ku_smem(&v_empty[st]));
+        KU_TICK(6)
         if (j + 1 < n1) {
           issue_s(1, j + 1);
           ku_mma_commit(ku_smem(&k_empty[nx]));
         }
+        KU_TICK(7)
       }
+#if KU_PHASES
+      if (blockIdx.x == 0 && blockIdx.y == 40)
+        printf("MMA thread, %d key blocks (from the fifth on): wait V %lld, wait P0 %lld, issue PV0 %lld, wait K %lld, issue S0 %lld, wait P1 %lld, issue PV1 %lld, issue S1 %lld\n", n1,
+               ph[0] / (n1 - 4), ph[1] / (n1 - 4), ph[2] / (n1 - 4), ph[3] / (n1 - 4), ph[4] / (n1 - 4), ph[5] / (n1 - 4), ph[6] / (n1 - 4), ph[7] / (n1 - 4));
+#endif
     }
   } else {  // ---- softmax: a warpgroup per tile, one thread per query row ----
     const int t = (warp - 2) >> 2;                // the tile
@@ -743,8 +778,16 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
     const unsigned s_addr = tmem_base + ((unsigned)(q4 * 32) << 16) + t * 128;
     const unsigned o_addr = tmem_base + ((unsigned)(q4 * 32) << 16) + 256 + t * 128;
     float m = -KU_INF, l = 0.0f;   // reference maximum (followed lazily, see the one-CTA kernel) and the row's sum
+#if KU_PHASES
+    long long ph[6] = {0, 0, 0, 0, 0, 0}, t_prev;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_prev));
+#endif
     for (int j = 0; j < nkv; ++j) {
+#if KU_PHASES
+      if (j == 4) { for (int i = 0; i < 6; ++i) ph[i] = 0; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_prev)); }
+#endif
       ku_wait(ku_smem(&s_full[t]), j & 1, failed, status);
+      KU_TICK(0)
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool need_mask = (CAUSAL && j == qb) || (j * BKV + BKV > S);
       float sc[BKV];
@@ -753,6 +796,7 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
       for (int c = 0; c < BKV; ++c) asm volatile("" : "+f"(sc[c]));   // the values may only be read after the wait
+      KU_TICK(1)
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < BKV; ++c) {
@@ -760,7 +804,7 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
           if ((CAUSAL && key > qrow) || key >= S) sc[c] = -KU_INF;
         }
       }
-      float b4[4] = {sc[0], sc[1], sc[2], sc[3]};
+      float b4[4] = {sc[0], sc[1], sc[2], sc[3]};   // four independent chains
 #pragma unroll
       for (int c = 4; c < BKV; ++c) b4[c & 3] = fmaxf(b4[c & 3], sc[c]);
       const float bm = fmaxf(fmaxf(b4[0], b4[1]), fmaxf(b4[2], b4[3])) * SCALE_LOG2E;   // SCALE_LOG2E > 0
@@ -769,6 +813,7 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
       const float alpha = grow ? ku_ex2(m - bm) : 1.0f;
       if (grow) m = bm;
       const float nref = (m == -KU_INF) ? 0.0f : -m;
+      KU_TICK(2)
       float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       // the probabilities, 64 keys (32 packed columns) at a time, over the first half of the scores they came from
       // (all of this lane's scores are in registers by now)
@@ -777,13 +822,15 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
         unsigned pk[32];
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
-          const float e0 = ku_ex2(fmaf(sc[h * 64 + c], SCALE_LOG2E, nref));
-          const float e1 = ku_ex2(fmaf(sc[h * 64 + c + 1], SCALE_LOG2E, nref));
+          const float x0 = fmaf(sc[h * 64 + c], SCALE_LOG2E, nref), x1 = fmaf(sc[h * 64 + c + 1], SCALE_LOG2E, nref);
+          const float e0 = ((c & 7) >= 8 - KU_POLY) ? ku_ex2_fma(x0) : ku_ex2(x0);
+          const float e1 = (((c + 1) & 7) >= 8 - KU_POLY) ? ku_ex2_fma(x1) : ku_ex2(x1);
           s4[(c >> 1) & 3] += e0 + e1;
           pk[c >> 1] = ku_pack2(e0, e1);
         }
         ku_tmem_st32_nowait(s_addr + h * 32, pk);
       }
+      KU_TICK(3)
       // only a rescale of O has to wait for the tile's previous product (its score block was issued after that
       // product, so the wait is over by now; o_full can be at most one phase ahead of it)
       if (any_grow) {
@@ -802,10 +849,17 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
         l *= alpha;
       }
       l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      KU_TICK(4)
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       ku_mbar_arrive(ku_smem(&p_ready[t]));
+      KU_TICK(5)
     }
+#if KU_PHASES
+    if (blockIdx.x == 0 && blockIdx.y == 40 && lane == 0 && q4 == 2)
+      printf("softmax thread of tile %d, %d key blocks (from the fifth on): wait S %lld, load %lld, max %lld, exp+pack+store %lld, rescale %lld, wait store+arrive %lld\n", t, nkv,
+             ph[0] / (nkv - 4), ph[1] / (nkv - 4), ph[2] / (nkv - 4), ph[3] / (nkv - 4), ph[4] / (nkv - 4), ph[5] / (nkv - 4));
+#endif
     if (nkv > 0) {
       ku_wait(ku_smem(&o_full[t]), (nkv - 1) & 1, failed, status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
