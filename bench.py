@@ -41,7 +41,7 @@ NCU_TRAFFIC = {
     ("c2_transposed_softmax", "softmax_groups_tma"): 481.4e6,
     ("c2_transposed_softmax", "softmax_panels_tma"): 535.7e6,
     ("c3_gemm_bias_gelu", "gemm_tc"): 1231e6,
-    ("c4_causal_attention", "attention_tc"): 1056e6,
+    ("c4_causal_attention", "attention_tc"): 1057e6,
     ("c5_fp8_weight_gemm", "gemm_tc_f8"): 3556e6,
 }
 

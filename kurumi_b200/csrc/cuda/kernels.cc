@@ -363,6 +363,8 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   if (var && std::string(var) == "twin") variant = 1;
   if ((var && std::string(var) == "one") || std::getenv("KURUMI_ATTENTION_ONE_CTA") || !(scale > 0.0f)) variant = 0;
   const bool twin = variant == 1, duo = variant == 2;
+  // duo: KURUMI_ATTENTION_ISSUERS=2 gives each query tile its own MMA-issuing thread and makes the tiles' softmax warpgroups take turns
+  const int64_t issuers = (std::getenv("KURUMI_ATTENTION_ISSUERS") && std::atoi(std::getenv("KURUMI_ATTENTION_ISSUERS")) == 2) ? 2 : 1;
   // duo: stages of the K and V rings (KURUMI_ATTENTION_STAGES=k,v, 2 or 3 each, at most 5 together at DH = 128 where a stage is 32 KB).
   // Two each by default: 2 + 3 and 3 + 2 measured the same on the causal 4096-key configuration, the loads are not what the MMA thread waits for.
   int64_t nks = 2, nvs = 2;
@@ -377,7 +379,7 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   std::snprintf(lit, sizeof(lit), "%.9gf", static_cast<double>(scale * 1.4426950408889634f));
   std::string src = device_prelude() +
                     defines({{"BH", bh}, {"S", s}, {"DH", dh}, {"CAUSAL", causal ? 1 : 0}, {"IDESC_S", static_cast<int64_t>(idesc_s)}, {"IDESC_O", static_cast<int64_t>(idesc_o)},
-                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", variant}, {"NKS", nks}, {"NVS", nvs},
+                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", variant}, {"NKS", nks}, {"NVS", nvs}, {"KU_ISSUERS", issuers}, {"KU_TURNS", (issuers == 2 && !std::getenv("KURUMI_ATTENTION_NO_TURNS")) ? 1 : 0},
                              {"KU_PTMEM", std::getenv("KURUMI_ATTENTION_P_SMEM") ? 0 : 1}, {"KU_PHASES", std::getenv("KURUMI_ATTENTION_PHASES") ? 1 : 0},
                              {"KU_POLY", std::getenv("KURUMI_ATTENTION_POLY") ? std::atoi(std::getenv("KURUMI_ATTENTION_POLY")) : 0}}) +
                     "#define SCALE_LOG2E " + lit + "\n" + kSrc_attention_tc;
@@ -387,7 +389,7 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   out->grid[1] = static_cast<unsigned>(bh);
   const int64_t tile = 128 * 128 * (dh / 64);
   if (duo) {
-    out->block[0] = 320;   // TMA warp, MMA warp, a softmax warpgroup per query tile
+    out->block[0] = issuers == 2 ? 352 : 320;   // TMA warp, MMA warp (of tile 0), a softmax warpgroup per query tile[, MMA warp of tile 1]
     // two Q tiles, two K and two V stages, barriers; at least 120 KB so that an SM (512 columns of tensor memory) holds one CTA
     out->smem = static_cast<unsigned>(std::max<int64_t>((2 + nks + nvs) * tile + 256, 120 * 1024));
   } else if (twin) {

@@ -613,10 +613,10 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
 // One CTA per (head, 256 queries): two tiles of 128 query rows share every K_j / V_j block (128 keys), each with its
 // own softmax warpgroup, score buffer and accumulator in tensor memory:
 //   columns [0,128) S_0 (P_0 packed over its first 64 columns), [128,256) S_1 / P_1, [256,384) O_0, [384,512) O_1.
-// The MMA thread alternates between the tiles, P V of a tile followed at once by the tile's next score block:
-//   ... P_0 V_j, S_0 = Q_0 K_{j+1}^T, P_1 V_j, S_1 = Q_1 K_{j+1}^T, ...
-// so that one tile's exponentials run while the tensor core works for the other tile. MMAs execute in issue order,
-// which is what lets S_t(j+1) overwrite the P_t(j) that the product issued just before it reads.
+// Each tile has its own MMA-issuing thread (warps 1 and 10), P V of a block followed at once by the tile's next scores:
+//   ... P_t V_j, S_t = Q_t K_{j+1}^T, P_t V_{j+1}, ...
+// so that one tile's exponentials run while the tensor core works for the other tile. A thread's MMAs execute in
+// issue order, which is what lets S_t(j+1) overwrite the P_t(j) that the product issued just before it reads.
 // Shared-memory traffic per 128 x 128 block (the bound of the smaller kernels, which re-read Q and P from shared
 // memory and load K / V per tile): Q K^T 64 KB + V 32 KB + half a K / V load 32 KB = 128 KB.
 // Shared memory (DH = 128): Q 2 x 32 KB, a K ring of NKS and a V ring of NVS stages of 32 KB (2 + 2: 192 KB) + barriers,
@@ -626,6 +626,12 @@ ku_attention_tc_twin(const __grid_constant__ KuTmap tmap_q, const __grid_constan
 #endif
 #ifndef NVS
 #define NVS 2
+#endif
+#ifndef KU_ISSUERS
+#define KU_ISSUERS 1   // 2: a second MMA-issuing warp (warp 10) for tile 1
+#endif
+#ifndef KU_TURNS
+#define KU_TURNS (KU_ISSUERS == 2)   // the tiles' warpgroups take turns at the exponentials
 #endif
 #undef Q_BYTES
 #define Q_BYTES TILE_BYTES
@@ -640,7 +646,7 @@ __device__ __forceinline__ void ku_tmem_st32_nowait(unsigned taddr, const unsign
       : "memory");
 }
 
-extern "C" __global__ void __launch_bounds__(320, 1)
+extern "C" __global__ void __launch_bounds__(320 + 32 * (KU_ISSUERS - 1), 1)
 ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant__ KuTmap tmap_k, const __grid_constant__ KuTmap tmap_v, void* __restrict__ Op,
                     int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -663,8 +669,8 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     ku_mbar_init(ku_smem(q_full), 1);
-    for (int i = 0; i < NKS; ++i) { ku_mbar_init(ku_smem(&k_full[i]), 1); ku_mbar_init(ku_smem(&k_empty[i]), 1); }
-    for (int i = 0; i < NVS; ++i) { ku_mbar_init(ku_smem(&v_full[i]), 1); ku_mbar_init(ku_smem(&v_empty[i]), 1); }
+    for (int i = 0; i < NKS; ++i) { ku_mbar_init(ku_smem(&k_full[i]), 1); ku_mbar_init(ku_smem(&k_empty[i]), KU_ISSUERS); }   // released by every MMA issuer
+    for (int i = 0; i < NVS; ++i) { ku_mbar_init(ku_smem(&v_full[i]), 1); ku_mbar_init(ku_smem(&v_empty[i]), KU_ISSUERS); }
     for (int i = 0; i < 2; ++i) { ku_mbar_init(ku_smem(&s_full[i]), 1); ku_mbar_init(ku_smem(&p_ready[i]), 128); ku_mbar_init(ku_smem(&o_full[i]), 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -705,6 +711,50 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
         if (j + NVS - 1 < n1) load_v(j + NVS - 1);
       }
     }
+#if KU_ISSUERS == 2
+  } else if (warp == 1 || warp == 10) {
+    if (lane == 0) {  // ---- MMA issuers: warp 1 for tile 0, warp 10 for tile 1 ----
+      // One thread sustained an MMA every ~75 clocks, against the 64 clocks a 128 x 128 x 16 MMA executes in, and the tensor
+      // pipe idled between them; two issuing threads halve the instructions each has to prepare. The tiles' MMAs are
+      // independent (own score buffer and accumulator), every ordering the algorithm needs is inside one tile.
+      const int t = warp == 1 ? 0 : 1;
+      const int nt = t ? n1 : n0;
+      auto issue_s = [&](int j) {   // S_t = Q_t K_j^T
+        const int st = j % NKS;
+        ku_wait(ku_smem(&k_full[st]), (j / NKS) & 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          const unsigned off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          ku_mma(tmem_base + t * 128, ku_smem_desc(q_s + t * Q_BYTES + off, 16, 1024), ku_smem_desc(k_s + st * TILE_BYTES + off, 16, 1024), IDESC_S, kk != 0);
+        }
+        ku_mma_commit(ku_smem(&s_full[t]));
+      };
+      auto issue_pv = [&](int j) {   // O_t += P_t V_j: P_t from tensor memory (16 keys = 8 columns), V MN-major from shared memory
+        const int st = j % NVS;
+        ku_wait(ku_smem(&v_full[st]), (j / NVS) & 1, failed, status);
+        ku_wait(ku_smem(&p_ready[t]), j & 1, failed, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          ku_mma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, ku_smem_desc(v_s + st * TILE_BYTES + kk * 16 * 128, 16384, 1024), IDESC_O, (j | kk) != 0);
+        ku_mma_commit(ku_smem(&o_full[t]));
+      };
+      ku_wait(ku_smem(q_full), 0, failed, status);
+      issue_s(0);
+      ku_mma_commit(ku_smem(&k_empty[0]));
+      // a stage is released by both issuers, also for a block the shorter tile does not compute (a commit with nothing
+      // outstanding arrives at once)
+      for (int j = 0; j < n1; ++j) {
+        if (j < nt) issue_pv(j);
+        ku_mma_commit(ku_smem(&v_empty[j % NVS]));
+        if (j + 1 < n1) {
+          if (j + 1 < nt) issue_s(j + 1);
+          ku_mma_commit(ku_smem(&k_empty[(j + 1) % NKS]));
+        }
+      }
+    }
+#else
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer ----
 #if KU_PHASES
@@ -768,6 +818,7 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
                ph[0] / (n1 - 4), ph[1] / (n1 - 4), ph[2] / (n1 - 4), ph[3] / (n1 - 4), ph[4] / (n1 - 4), ph[5] / (n1 - 4), ph[6] / (n1 - 4), ph[7] / (n1 - 4));
 #endif
     }
+#endif
   } else {  // ---- softmax: a warpgroup per tile, one thread per query row ----
     const int t = (warp - 2) >> 2;                // the tile
     const int q4 = warp & 3;                      // the TMEM lane quarter this warp may access
@@ -781,6 +832,9 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
 #if KU_PHASES
     long long ph[6] = {0, 0, 0, 0, 0, 0}, t_prev;
     asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_prev));
+#endif
+#if KU_TURNS
+    if (t == 1) asm volatile("bar.arrive 1, 256;" ::: "memory");   // tile 0 goes first (n0 >= 1)
 #endif
     for (int j = 0; j < nkv; ++j) {
 #if KU_PHASES
@@ -814,6 +868,13 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
       if (grow) m = bm;
       const float nref = (m == -KU_INF) ? 0.0f : -m;
       KU_TICK(2)
+      // The tiles take turns at the exponentials (named barriers 1 and 2: one warpgroup arrives, the other waits):
+      // tile 0 block j, tile 1 block j, tile 0 block j+1, ... Left alone both warpgroups reach this phase together,
+      // share the special-function unit for twice as long and then leave it idle together while their MMAs run.
+#if KU_TURNS
+      if (t == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else if (j < n0) asm volatile("bar.sync 2, 256;" ::: "memory");
+#endif
       float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       // the probabilities, 64 keys (32 packed columns) at a time, over the first half of the scores they came from
       // (all of this lane's scores are in registers by now)
@@ -830,6 +891,10 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
         }
         ku_tmem_st32_nowait(s_addr + h * 32, pk);
       }
+#if KU_TURNS
+      if (t == 0) asm volatile("bar.arrive 2, 256;" ::: "memory");
+      else if (j + 1 < n0) asm volatile("bar.arrive 1, 256;" ::: "memory");
+#endif
       KU_TICK(3)
       // only a rescale of O has to wait for the tile's previous product (its score block was issued after that
       // product, so the wait is over by now; o_full can be at most one phase ahead of it)
