@@ -379,7 +379,7 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   std::snprintf(lit, sizeof(lit), "%.9gf", static_cast<double>(scale * 1.4426950408889634f));
   std::string src = device_prelude() +
                     defines({{"BH", bh}, {"S", s}, {"DH", dh}, {"CAUSAL", causal ? 1 : 0}, {"IDESC_S", static_cast<int64_t>(idesc_s)}, {"IDESC_O", static_cast<int64_t>(idesc_o)},
-                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", variant}, {"NKS", nks}, {"NVS", nvs}, {"KU_ISSUERS", issuers}, {"KU_TURNS", (issuers == 2 && !std::getenv("KURUMI_ATTENTION_NO_TURNS")) ? 1 : 0},
+                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", variant}, {"NKS", nks}, {"NVS", nvs}, {"KU_ISSUERS", issuers}, {"KU_TURNS", issuers != 2 || std::getenv("KURUMI_ATTENTION_NO_TURNS") ? 0 : (std::getenv("KURUMI_ATTENTION_STAGGER") ? 2 : 1)},
                              {"KU_PTMEM", std::getenv("KURUMI_ATTENTION_P_SMEM") ? 0 : 1}, {"KU_PHASES", std::getenv("KURUMI_ATTENTION_PHASES") ? 1 : 0},
                              {"KU_POLY", std::getenv("KURUMI_ATTENTION_POLY") ? std::atoi(std::getenv("KURUMI_ATTENTION_POLY")) : 0}}) +
                     "#define SCALE_LOG2E " + lit + "\n" + kSrc_attention_tc;

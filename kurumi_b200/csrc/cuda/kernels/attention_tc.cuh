@@ -833,7 +833,7 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
     long long ph[6] = {0, 0, 0, 0, 0, 0}, t_prev;
     asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_prev));
 #endif
-#if KU_TURNS
+#if KU_TURNS == 1
     if (t == 1) asm volatile("bar.arrive 1, 256;" ::: "memory");   // tile 0 goes first (n0 >= 1)
 #endif
     for (int j = 0; j < nkv; ++j) {
@@ -871,9 +871,11 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
       // The tiles take turns at the exponentials (named barriers 1 and 2: one warpgroup arrives, the other waits):
       // tile 0 block j, tile 1 block j, tile 0 block j+1, ... Left alone both warpgroups reach this phase together,
       // share the special-function unit for twice as long and then leave it idle together while their MMAs run.
-#if KU_TURNS
+#if KU_TURNS == 1
       if (t == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
       else if (j < n0) asm volatile("bar.sync 2, 256;" ::: "memory");
+#elif KU_TURNS == 2   // only the first block is ordered: tile 1 starts one exponential phase behind tile 0, then both run free
+      if (t == 1 && j == 0) asm volatile("bar.sync 2, 256;" ::: "memory");
 #endif
       float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       // the probabilities, 64 keys (32 packed columns) at a time, over the first half of the scores they came from
@@ -891,9 +893,11 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
         }
         ku_tmem_st32_nowait(s_addr + h * 32, pk);
       }
-#if KU_TURNS
+#if KU_TURNS == 1
       if (t == 0) asm volatile("bar.arrive 2, 256;" ::: "memory");
       else if (j + 1 < n0) asm volatile("bar.arrive 1, 256;" ::: "memory");
+#elif KU_TURNS == 2
+      if (t == 0 && j == 0) asm volatile("bar.arrive 2, 256;" ::: "memory");
 #endif
       KU_TICK(3)
       // only a rescale of O has to wait for the tile's previous product (its score block was issued after that
