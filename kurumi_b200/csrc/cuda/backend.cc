@@ -80,7 +80,10 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
         break;
       }
       case Slot::Temp:
-        if (!c.temp_ptrs[i]) c.temp_ptrs[i] = rt_.alloc(std::max<size_t>(s.bytes, 1));
+        if (!c.temp_ptrs[i]) {
+          c.temp_ptrs[i] = rt_.alloc(std::max<size_t>(s.bytes, 1));
+          if (s.zero_init && s.bytes) cuda_check(cudaMemsetAsync(c.temp_ptrs[i], 0, s.bytes, rt_.stream()), "cudaMemsetAsync(scratch)");
+        }
         ptr[i] = c.temp_ptrs[i];
         break;
       case Slot::Out: ptr[i] = rt_.alloc(std::max<size_t>(s.bytes, 1)); break;
@@ -109,6 +112,8 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
         vals[a] = rt_.status_word();
         argv[a] = &vals[a];
         uses_status_ = true;
+      } else if (A.kind == Arg::Epoch) {
+        argv[a] = &L.epoch;
       } else if (A.kind == Arg::Bytes) {
         argv[a] = const_cast<uint8_t*>(A.bytes.data());
       } else {
@@ -135,6 +140,7 @@ std::vector<DevTensor*> CudaBackend::eval_device(const Graph& g, const std::vect
     } else {
       // A cooperative grid is sized from an occupancy query; if the device can hold fewer CTAs at launch time (another
       // context shares it) the driver refuses the launch: drop whole CTA groups until it fits.
+      ++L.epoch;
       for (;;) {
         try {
           rt_.launch(L.kernel, L.grid, L.block, L.cluster, L.smem, argv.data(), L.cooperative);

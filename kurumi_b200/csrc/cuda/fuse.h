@@ -67,6 +67,7 @@ struct Slot {
   NodeId node = 0;     // Const / Feed: the graph node
   DType dtype = DType::F32;
   Shape shape;
+  bool zero_init = false;   // Temp: cleared once, when the slot's memory is allocated
 };
 
 struct TmapSpec {  // a tensor map over a slot, encoded once the slot's address is known
@@ -81,7 +82,9 @@ struct TmapSpec {  // a tensor map over a slot, encoded once the slot's address 
 };
 
 struct Arg {
-  enum Kind : uint8_t { SlotPtr, Bytes, Tmap, Status } kind = SlotPtr;  // Status: the backend's device status word
+  // Status: the backend's device status word. Epoch: a 32-bit count of this launch's issues (1 on the first), for
+  // kernels whose scratch words carry the parity of the launch that wrote them
+  enum Kind : uint8_t { SlotPtr, Bytes, Tmap, Status, Epoch } kind = SlotPtr;
   int slot = -1;
   int64_t byte_offset = 0;
   std::vector<uint8_t> bytes;
@@ -105,6 +108,7 @@ struct Launch {
   size_t zero_bytes = 0;
   int fill_byte = 0;
   double algo_bytes = 0, flops = 0;  // algorithmic traffic / work of this launch
+  uint32_t epoch = 0;       // how many times this launch has been issued (Arg::Epoch)
 };
 
 struct Program {

@@ -85,7 +85,6 @@ bool build_gemm_tc(const KernelLoader& load, const GemmDesc& d, const Fused* epi
   return true;
 }
 extern const std::string kSrc_softmax_transposed;
-extern const std::string kSrc_softmax_transposed_tma;
 
 
 size_t softmax_two_pass_scratch_bytes(size_t lines, size_t len);
@@ -173,34 +172,30 @@ bool build_quant_gemv(const KernelLoader& load, DType act, int64_t m, int64_t n,
 
 extern const std::string kSrc_softmax_groups_tma;
 
-bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args, size_t* scratch_bytes, size_t* zero_bytes) {
+bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args, size_t* scratch_bytes) {
   if (f.dtype() != DType::F32 || std::getenv("KURUMI_SMT_NO_GROUPS")) return false;
   std::string src_fn;
   int64_t R = 0, C = 0;
   bool transposed = false;
   LineLeaf big;
   if (!emit_line_source_fn(f, axis, &src_fn, leaf_args, &R, &C, &transposed, &big) || !transposed || big.leaf < 0) return false;
-  auto env = [](const char* name, int64_t dflt) { const char* e = std::getenv(name); return e ? static_cast<int64_t>(std::atoi(e)) : dflt; };
-  // slabs of 32 lines (128-byte tile rows); slabs of 16 (64-byte rows, 256-thread CTAs, twice the groups) measured 7 % slower
-  const int64_t lw = env("KURUMI_SMG_LW", 32) == 16 ? 16 : 32;
-  const int64_t p = 16, nt = lw == 32 ? 512 : 256, nw = nt / 32, rsn = 128 / lw;
-  if (sm_count < p || R < lw * 8 || C < 1024 || R * C < (int64_t(1) << 22) || R >= (int64_t(1) << 30) || C >= (int64_t(1) << 30) || (big.base * 4) % 16 != 0) return false;
-  int64_t cj = (C + p - 1) / p;
-  cj = (cj + rsn * nw - 1) / (rsn * nw) * (rsn * nw);      // every warp gets whole groups of tile rows (rsn * nw = 64: also whole 32-position strips)
-  int64_t nbuf = std::min<int64_t>(4, std::max<int64_t>(1, env("KURUMI_SMG_NBUF", 1)));
-  while (nbuf > 1 && nbuf * cj * lw * 4 + 1024 > 220 * 1024) --nbuf;
-  if (nbuf * cj * lw * 4 + 1024 > 220 * 1024) return false;   // lines too long for a ring of tiles in shared memory
-  const int64_t boxj = cj % 256 == 0 ? 256 : cj % 128 == 0 ? 128 : cj % 64 == 0 ? 64 : 32;
+  // A group of P CTAs shares a slab of 32 lines; a CTA keeps CJ positions of it, V = CJ / 64 float4 values per thread,
+  // in registers. V <= 8 keeps the kernel at 64 registers (two CTAs of 512 threads per SM), so a line has at most
+  // 32 * 512 positions; longer lines take the panel kernel.
+  const int64_t lw = 32, nt = 512;
+  const int64_t p = std::max<int64_t>(2, (C + 511) / 512);
+  if (p > 32 || sm_count * 2 < p || R < lw * 8 || C < 1024 || R * C < (int64_t(1) << 22) || R >= (int64_t(1) << 30) || (big.base * 4) % 16 != 0) return false;
+  const int64_t cj = ((C + p - 1) / p + 63) / 64 * 64;
+  const int64_t boxj = cj % 256 == 0 ? 256 : cj % 128 == 0 ? 128 : 64;
   const int64_t slabs = (R + lw - 1) / lw;
   std::string src = device_prelude() + src_fn +
-                    defines({{"R", R}, {"C", C}, {"LW", lw}, {"P", p}, {"CJ", cj}, {"BOXJ", boxj}, {"NBUF", nbuf}, {"NT", nt}, {"NSLABS", slabs}, {"KU_OUT_F32", 1},
-                             {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
+                    defines({{"R", R}, {"C", C}, {"P", p}, {"CJ", cj}, {"BOXJ", boxj}, {"NT", nt}, {"NSLABS", slabs}, {"KU_OUT_F32", 1}, {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
                     kSrc_softmax_groups_tma;
   out->name = "softmax_groups_tma";
   out->kernel = load(src, "ku_softmax_groups_tma", false);
-  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(slabs, 8 * sm_count / p) * p);
+  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(slabs, 2 * sm_count / p) * p);
   out->block[0] = static_cast<unsigned>(nt);
-  out->smem = static_cast<unsigned>(nbuf * cj * lw * 4 + 1024);   // 1024 bytes of slack: the ring is placed on a 1024-byte boundary
+  out->smem = static_cast<unsigned>(cj * lw * 4 + 1024);   // 1024 bytes of slack: the tile is placed on a 1024-byte boundary
   out->persistent_clusters = -1;                               // cap the grid at the co-resident CTA count on first launch,
   out->grid_multiple = static_cast<unsigned>(p);               // in whole groups,
   out->cooperative = true;                                     // and have the driver hold the launch to it
@@ -213,10 +208,9 @@ bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis,
   tm.tm.dims[0] = static_cast<uint64_t>(R); tm.tm.dims[1] = static_cast<uint64_t>(C);
   tm.tm.strides[0] = static_cast<uint64_t>(big.ld) * 4;
   tm.tm.box[0] = static_cast<uint32_t>(lw); tm.tm.box[1] = static_cast<uint32_t>(boxj);
-  tm.tm.swz = lw == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  tm.tm.swz = CU_TENSOR_MAP_SWIZZLE_128B;
   out->args.push_back(tm);
-  *zero_bytes = static_cast<size_t>((slabs * 4 + 255) / 256 * 256);   // the per-slab counters
-  *scratch_bytes = *zero_bytes + static_cast<size_t>(slabs * p * lw * 8);
+  *scratch_bytes = static_cast<size_t>(slabs * 2 * p * lw * 8);   // one 64-bit (max, sum, parity) word per slab, CTA, warp half and line
   return true;
 }
 
@@ -235,18 +229,15 @@ bool build_softmax_panels(const KernelLoader& load, const Fused& f, size_t axis,
   LineLeaf big;
   if (!emit_line_source_fn(f, axis, &src_fn, leaf_args, &R, &C, &transposed, &big) || !transposed || big.leaf < 0) return false;
   if (R < 64 || C < 256 || R * C < (int64_t(1) << 20) || (R + 255) / 256 > 1024 || C >= (int64_t(1) << 30)) return false;
-  auto env = [](const char* name, int64_t dflt) { const char* e = std::getenv(name); return e ? static_cast<int64_t>(std::atoi(e)) : dflt; };
-  const int64_t jt = env("KURUMI_SMP_JT", 256) == 128 ? 128 : 256;
-  const int64_t nbuf = std::min<int64_t>(6, std::max<int64_t>(1, env("KURUMI_SMP_NBUF", 2)));
-  const int64_t la = std::min<int64_t>(8, std::max<int64_t>(2, env("KURUMI_SMP_LA", 4)));
-  const int64_t lc = std::min<int64_t>(la - 1, std::max<int64_t>(1, env("KURUMI_SMP_LC", 2)));
+  // tile height, ring depth, how far statistics (la) and merges (lc) run ahead of the output tiles: the measured best
+  const int64_t jt = 256, nbuf = 2, la = 4, lc = 2;
   const int64_t npb = la + 2;
   std::string src = device_prelude() + src_fn +
-                    defines({{"R", R}, {"C", C}, {"JT", jt}, {"NBUF", nbuf}, {"LA", la}, {"LC", lc}, {"NPB", npb}, {"KU_L2_HINTS", env("KURUMI_SMP_HINTS", 1)}, {"KU_OUT_F32", 1}, {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
+                    defines({{"R", R}, {"C", C}, {"JT", jt}, {"NBUF", nbuf}, {"LA", la}, {"LC", lc}, {"NPB", npb}, {"KU_L2_HINTS", 1}, {"KU_OUT_F32", 1}, {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
                     kSrc_softmax_panels_tma;
   out->name = "softmax_panels_tma";
   out->kernel = load(src, "ku_softmax_panels_tma", false);
-  out->grid[0] = static_cast<unsigned>(sm_count * std::min<int64_t>(8, std::max<int64_t>(1, env("KURUMI_SMP_CTAS", 8))));
+  out->grid[0] = static_cast<unsigned>(sm_count * 8);
   out->block[0] = 256;
   out->smem = static_cast<unsigned>(nbuf * jt * 128 + 1024);   // 1024 bytes of slack: the ring is placed on a 1024-byte boundary
   out->persistent_clusters = -1;                               // cap the grid at the co-resident CTA count on first launch
@@ -273,57 +264,14 @@ bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t a
   LineLeaf big;
   if (!emit_line_source_fn(f, axis, &src_fn, leaf_args, &R, &C, &transposed, &big) || !transposed) return false;
   if (R < 32 || C < 256) return false;
-  // fast path: persistent clusters of 16 fed by TMA, when one plain f32 buffer dominates the reads
-  if (big.leaf >= 0 && C >= 2048 && f.dtype() == DType::F32 && !std::getenv("KURUMI_SMT_NO_TMA")) {
-    const int64_t cl = 16;
-    int64_t cj = (C + cl - 1) / cl;
-    cj = (cj + 31) / 32 * 32;
-    const int64_t boxj = cj % 256 == 0 ? 256 : cj % 128 == 0 ? 128 : cj % 64 == 0 ? 64 : 32;
-    // one tile per CTA and as many CTAs per SM as shared memory holds: co-resident CTAs of different
-    // clusters overlap each other's exchange latency better than a deeper ring in one CTA does
-    int64_t nbuf = 1;
-    if (const char* e = std::getenv("KURUMI_SMT_NBUF")) nbuf = std::atoi(e);
-    if (nbuf >= 1 && R < (int64_t(1) << 30) && C < (int64_t(1) << 30)) {
-      int64_t nt = 512;
-      if (const char* e = std::getenv("KURUMI_SMT_NT")) nt = std::max<int64_t>(32 * cl, std::atoi(e));  // one warp per cluster peer at least
-      const int64_t slabs = (R + 31) / 32;
-      std::string src = device_prelude() + src_fn +
-                        defines({{"R", R}, {"C", C}, {"CL", cl}, {"CJ", cj}, {"BOXJ", boxj}, {"NBUF", nbuf}, {"NT", nt}, {"NSLABS", slabs}, {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
-                        kSrc_softmax_transposed_tma;
-      out->name = "softmax_transposed_tma";
-      out->kernel = load(src, "ku_softmax_transposed_tma", false);
-      out->grid[0] = static_cast<unsigned>(slabs * cl);
-      out->block[0] = static_cast<unsigned>(nt);
-      out->cluster[0] = static_cast<unsigned>(cl);
-      out->smem = static_cast<unsigned>(nbuf * cj * 128);  // the kernel's static shared memory is a multiple of 1024 bytes, so the ring starts aligned
-      out->persistent_clusters = -1;                              // cap the grid at the co-resident cluster count on first launch
-      Arg tm;
-      tm.kind = Arg::Tmap;
-      tm.tm.slot = f.leaves[static_cast<size_t>(big.leaf)].slot;
-      tm.tm.byte_offset = big.base * 4;
-      tm.tm.dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-      tm.tm.rank = 2;
-      tm.tm.dims[0] = static_cast<uint64_t>(R); tm.tm.dims[1] = static_cast<uint64_t>(C);
-      tm.tm.strides[0] = static_cast<uint64_t>(big.ld) * 4;
-      tm.tm.box[0] = 32; tm.tm.box[1] = static_cast<uint32_t>(boxj);
-      tm.tm.swz = CU_TENSOR_MAP_SWIZZLE_128B;
-      out->args.push_back(tm);
-      out->status_arg = true;   // the kernel's last parameter is the device status word
-      return true;
-    }
-  }
   // cluster size: the smallest power of two whose per-CTA share of a line fits shared memory
   const int64_t max_cj = (200 * 1024) / (33 * 4);
   int64_t cl = 1;
   while (cl < 16 && (C + cl - 1) / cl > max_cj) cl *= 2;
   while (cl < 8 && (C + cl - 1) / cl > 1024) cl *= 2;   // spread a slab over more SMs: more loads in flight per line
-  if (const char* e = std::getenv("KURUMI_SMT_CL")) cl = std::atoi(e);
   const int64_t cj = (C + cl - 1) / cl;
   if (cj > max_cj) return false;
-  int64_t nt = cj >= 512 ? 1024 : 256;
-  int64_t unr = 8;
-  if (const char* e = std::getenv("KURUMI_SMT_NT")) nt = std::atoi(e);
-  if (const char* e = std::getenv("KURUMI_SMT_UNR")) unr = std::atoi(e);
+  const int64_t nt = cj >= 512 ? 1024 : 256, unr = 8;
   std::string src = device_prelude() + src_fn + defines({{"R", R}, {"C", C}, {"CL", cl}, {"CJ", cj}, {"NT", nt}, {"UNR", unr}}) + kSrc_softmax_transposed;
   out->name = "softmax_transposed";
   out->kernel = load(src, "ku_softmax_transposed", false);

@@ -14,12 +14,12 @@ bool build_gemm_tc(const KernelLoader& load, const GemmDesc& d, const Fused* epi
 // (a softmax consumed through a transpose view). Returns false when the pattern does not apply.
 bool build_softmax_transposed(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args);
 
-// The same softmax in a single pass: groups of 16 co-resident CTAs keep a 32-line slab in shared memory and
-// exchange per-line (max, sum) pairs through global scratch (kernels/softmax_groups_tma.cuh). After the leaf
-// arguments the kernel takes {output, scratch, status}; the caller creates the scratch slot of
-// `*scratch_bytes` bytes and has its first `*zero_bytes` bytes cleared before each launch.
-bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args, size_t* scratch_bytes,
-                          size_t* zero_bytes);
+// The same softmax in a single pass: groups of P co-resident CTAs hold a 32-line slab on chip (the tile goes from
+// shared memory into registers) and exchange per-line (max, sum) pairs through global scratch
+// (kernels/softmax_groups_tma.cuh). After the leaf arguments the kernel takes {output, scratch, launch counter,
+// status}; the caller creates the scratch slot of `*scratch_bytes` bytes, zero when allocated and never cleared
+// again (the words carry the parity of the launch counter).
+bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis, int sm_count, Launch* out, std::vector<int>* leaf_args, size_t* scratch_bytes);
 
 // The same softmax as two passes inside one persistent TMA-fed kernel whose second pass reads from L2
 // (kernels/softmax_panels_tma.cuh). After the leaf arguments the kernel takes {output, scratch, status};

@@ -1,31 +1,44 @@
-// Single-pass softmax through a transpose view: every input byte crosses HBM and L2 once, because a
-// tile stays in shared memory between the statistics and the write-out.
+// Single-pass softmax through a transpose view: every input byte crosses HBM and L2 once, and every
+// element is read from shared memory once: a tile is lifted into registers as soon as it lands, so the
+// shared-memory tile is free for the next slab's TMA load while this slab's statistics are exchanged
+// and its output is written.
 //
 // The dominant input is a plain f32 buffer read as in[j * ld + i] (i = line, j = position along the
-// softmax axis). A slab is 32 lines. A GROUP of P co-resident CTAs shares a slab: CTA r keeps positions
-// [r*CJ, r*CJ + CJ) of it as a [CJ][32] f32 tile (TMA, 128-byte swizzled rows) in a ring of NBUF tiles.
-// Groups walk the slabs with a fixed stride; there are no clusters, so any number of groups up to
-// (resident CTAs / P) runs, and the launch is cooperative so that a group's CTAs really are co-resident.
-// Per slab a CTA
-//   1. reduces its tile to one (max, sum) pair per line, writes the 32 pairs to global scratch and bumps
-//      the slab's counter (release);
-//   2. waits until the counter shows all P CTAs (acquire; one polling thread per CTA), merges the P x 32
-//      pairs, and writes its tile out transposed: out[line][position] = exp2(x * log2e - (max * log2e + log2 sum)).
-// With NBUF = 1 (one tile per CTA, several CTAs of different groups per SM) the steps follow each other
-// and the neighbours on the SM fill the waits; with a deeper ring step 2 of a slab runs after step 1 of the next.
-// Every wait is bounded: a CTA that gives up records it in *status and carries on.
+// softmax axis). A slab is 32 lines. A GROUP of P co-resident CTAs shares a slab: CTA r loads positions
+// [r*CJ, r*CJ + CJ) of it as a [CJ][32] f32 tile (TMA, 128-byte swizzled rows). Groups walk the slabs
+// with a fixed stride; there are no clusters, so any number of groups up to (resident CTAs / P) runs, and
+// the launch is cooperative so that a group's CTAs really are co-resident. Two CTAs of 512 threads fit an
+// SM: 2 x 64 KB of tiles being filled by TMA and 2 x 64 KB of tiles held in registers.
 //
-// Spliced in by the host: R, C, LW (lines per slab: 32 or 16), P, CJ (multiple of (128 / LW) * NT / 32), BOXJ, NBUF, NT, NSLABS,
-// KU_OUT_F32, KU_SRC_IDENTITY and
+// Thread layout (the same for the statistics and for the write-out, so the values never leave their
+// registers): warp w owns the 16-byte chunk q = w % 8 of the tile rows (lines 4q .. 4q+3) and the
+// 32-position strips h, h + 2, h + 4, ... (h = w / 8); lane = position inside a strip. A thread holds
+// V = CJ / 64 float4 values: 4 lines at V positions. A warp-wide store then writes 128 contiguous bytes
+// of one output line.
+//
+// Per slab a CTA
+//   1. waits for its tile, copies it to registers (one conflict-free 16-byte shared-memory load per
+//      float4, the fused producer applied on the way) and releases the tile to the next TMA load;
+//   2. per warp: line maxima over its positions (redux.sync), e = exp2(x * log2e - k) in place with k the
+//      WARP's maximum in log2 units, line sums by a 6-shuffle butterfly; the warp's (max, sum) pairs go
+//      to global scratch as one 64-bit word each, whose top bit (the sign bit of the sum, which is never
+//      negative) carries the launch parity: data and "ready" flag travel in one store, no fence, no counter;
+//   3. polls the 2P words of each of the 32 lines (every warp polls its share, bounded), merges them to
+//      c = max + log2(sum) per line and writes out[line][position] = e * exp2(k - c).
+// One exp2 per element, plus a handful per thread. Every wait is bounded: a CTA that gives up records it
+// in *status and carries on (its results are then invalid, the host reports it).
+//
+// Spliced in by the host: R, C, P, CJ (multiple of 64), BOXJ, NT (512), NSLABS, KU_OUT_F32, KU_SRC_IDENTITY and
 //   float ku_src_t(float lval, idx i, idx j KU_SRC_PARAMS) - the fused producer given the loaded value.
+#define LW 32                  /* lines per slab: a tile row is 128 bytes */
 #define NW (NT / 32)
-#define ROWB (LW * 4)          /* bytes of a tile row: LW lines at one position */
-#define CHUNKS (LW / 4)        /* 16-byte chunks (4 lines) per tile row */
-#define RSN (32 / CHUNKS)      /* tile rows a warp reads with one 16-byte load per lane */
+#define V (CJ / 64)            /* float4 values per thread */
+#define NPART (2 * P)          /* (max, sum) pairs per line and slab: one per CTA and warp half */
+#define NE ((NPART + NW - 1) / NW)   /* pairs of a line a warp polls */
 #define KU_LOG2E 1.4426950408889634f
-#define TILE_BYTES (CJ * ROWB)
+#define TILE_BYTES (CJ * 128)
 #define SPIN_LIMIT (1u << 22)
-#define RPW (CJ / NW)   /* tile rows per warp */
+#define POLL_LIMIT (1u << 20)
 #if KU_OUT_F32
 #define KU_STORE(p, v) __stcs((p), (v))   // the output is not read again: stream it through L2
 #else
@@ -35,16 +48,10 @@
 struct alignas(64) KuTmap { unsigned long long opaque[16]; };
 
 __device__ __forceinline__ float ku_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float ku_warp_max(float x) { float y; asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ unsigned ku_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-// byte offset of 16-byte chunk q (lines 4q .. 4q+3) of tile row jj: rows are ROWB bytes, swizzled as the TMA wrote them
-// (128-byte rows: chunk ^ (row & 7); 64-byte rows: chunk ^ ((row >> 1) & 3))
-__device__ __forceinline__ unsigned ku_chunk_off(int jj, int q) {
-#if LW == 32
-  return (unsigned)(jj * ROWB + ((q ^ (jj & 7)) << 4));
-#else
-  return (unsigned)(jj * ROWB + ((q ^ ((jj >> 1) & 3)) << 4));
-#endif
-}
+// byte offset of 16-byte chunk q (lines 4q .. 4q+3) of tile row jj: rows are 128 bytes, swizzled as the TMA wrote them
+__device__ __forceinline__ unsigned ku_chunk_off(int jj, int q) { return (unsigned)(jj * 128 + ((q ^ (jj & 7)) << 4)); }
 __device__ __forceinline__ void ku_mbar_init(unsigned a, unsigned n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(n)); }
 __device__ __forceinline__ void ku_mbar_expect(unsigned a, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
@@ -58,182 +65,179 @@ __device__ __forceinline__ void ku_tma_2d(unsigned dst, const KuTmap* map, int x
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(mbar) : "memory");
 }
-__device__ __forceinline__ unsigned ku_ld_acquire(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ku_ld_relaxed(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-// (max, sum) pairs in log2 units: merge b into a
-__device__ __forceinline__ void ku_merge(float& m, float& sum, float om, float osum) {
-  const float mn = fmaxf(m, om);
-  const float a0 = (m == -KU_INF) ? sum : sum * ku_ex2(m - mn);      // a sum is 0 or NaN while its max is -inf
-  const float a1 = (om == -KU_INF) ? osum : osum * ku_ex2(om - mn);
-  sum = a0 + a1;
-  m = mn;
+__device__ __forceinline__ void ku_st_relaxed(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// sums of four values over the warp with six shuffles: on return every lane holds the total of value (lane & 3)
+__device__ __forceinline__ float ku_sum4(float a0, float a1, float a2, float a3, int lane) {
+  const bool b1 = lane & 2, b0 = lane & 1;
+  const float r0 = __shfl_xor_sync(0xffffffffu, b1 ? a0 : a2, 2), r1 = __shfl_xor_sync(0xffffffffu, b1 ? a1 : a3, 2);
+  const float c0 = (b1 ? a2 : a0) + r0, c1 = (b1 ? a3 : a1) + r1;          // values 2*b1 and 2*b1 + 1 over the lane pair
+  float s = (b0 ? c1 : c0) + __shfl_xor_sync(0xffffffffu, b0 ? c0 : c1, 1);   // value (lane & 3) over four lanes
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  s += __shfl_xor_sync(0xffffffffu, s, 8);
+  s += __shfl_xor_sync(0xffffffffu, s, 16);
+  return s;
 }
 
-extern "C" __global__ void __launch_bounds__(NT)
-ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD void* __restrict__ out, void* __restrict__ scratch, int* __restrict__ status) {
-  extern __shared__ __align__(1024) unsigned char tiles_raw[];  // NBUF tiles of [CJ][32] f32, 128-byte swizzled rows
-  __shared__ __align__(8) unsigned long long full[NBUF];
-  __shared__ __align__(16) float2 s_part[NW][LW];
-  __shared__ __align__(16) float line_c[LW];
-  __shared__ int s_failed;
+extern "C" __global__ void __launch_bounds__(NT, 2)
+ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD void* __restrict__ out, void* __restrict__ scratch, unsigned epoch, int* __restrict__ status) {
+  extern __shared__ __align__(1024) unsigned char tiles_raw[];  // one tile of [CJ][32] f32, 128-byte swizzled rows
+  __shared__ __align__(8) unsigned long long full;
+  __shared__ __align__(16) float2 s_x[NPART][LW];               // the slab's (max, sum) pairs, as polled
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int group = blockIdx.x / P, ngroups = gridDim.x / P, rank = blockIdx.x % P;
   const int j0 = rank * CJ;
-  unsigned* counters = (unsigned*)scratch;                                  // [NSLABS], cleared by the host before the launch
-  float2* partials = (float2*)((char*)scratch + (((size_t)NSLABS * 4 + 255) / 256) * 256);   // [NSLABS][P][LW]
-  // the swizzle pattern is a function of the shared-memory address: tiles start on a 1024-byte boundary
-  // (the host sizes the ring with 1024 bytes of slack)
-  unsigned char* tiles = tiles_raw + ((1024u - (ku_smem(tiles_raw) & 1023u)) & 1023u);
-  const unsigned tiles_s = ku_smem(tiles);
+  unsigned long long* partials = (unsigned long long*)scratch;   // [NSLABS][NPART][LW]; zero when allocated, parity flips per launch
+  const unsigned par = epoch & 1u;
+  // the swizzle pattern is a function of the shared-memory address: the tile starts on a 1024-byte boundary
+  // (the host sizes the allocation with 1024 bytes of slack)
+  unsigned char* tile = tiles_raw + ((1024u - (ku_smem(tiles_raw) & 1023u)) & 1023u);
+  const unsigned tile_s = ku_smem(tile), mb = ku_smem(&full);
   if (blockIdx.x >= (unsigned)(ngroups * P)) return;   // CTAs beyond the last whole group have no work
 
-  auto issue = [&](int slab, int b) {  // one thread: stream this CTA's share of a slab into tile b
-    const unsigned mb = ku_smem(&full[b]);
+  auto issue = [&](int slab) {  // one thread: stream this CTA's share of a slab into the tile
     ku_mbar_expect(mb, TILE_BYTES);
-    for (int k = 0; k < CJ / BOXJ; ++k) ku_tma_2d(tiles_s + b * TILE_BYTES + k * BOXJ * ROWB, &tmap, slab * LW, j0 + k * BOXJ, mb);
+    for (int k = 0; k < CJ / BOXJ; ++k) ku_tma_2d(tile_s + k * BOXJ * 128, &tmap, slab * LW, j0 + k * BOXJ, mb);
   };
   if (threadIdx.x == 0) {
-    s_failed = 0;
-    for (int b = 0; b < NBUF; ++b) ku_mbar_init(ku_smem(&full[b]), 1);
+    ku_mbar_init(mb, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    for (int b = 0; b < NBUF; ++b)
-      if (group + b * ngroups < NSLABS) issue(group + b * ngroups, b);
+    if (group < NSLABS) issue(group);
   }
   __syncthreads();
 
-  // step 1 of the n-th slab of this CTA
-  auto stats = [&](int n, int slab) {
-    const int b = n % NBUF;
-    const unsigned parity = (unsigned)((n / NBUF) & 1), mb = ku_smem(&full[b]);
-    unsigned spins = 0;
-    while (!ku_mbar_try(mb, parity)) {
-      if (++spins > SPIN_LIMIT) { atomicExch(status, 1); break; }
-    }
-    const unsigned char* tile = tiles + b * TILE_BYTES;
-    const int i0 = slab * LW;
-    // thread = (4 lines: chunk q of the row, row group rs); a warp owns RPW consecutive rows of the tile
-    const int q = lane % CHUNKS, rs = lane / CHUNKS;
-    // two passes over the warp's rows of the tile (16-byte shared-memory loads are cheap; registers are not)
-    auto load = [&](int it) {
-      const int row = warp * RPW + it * RSN + rs, j = j0 + row;
-      float4 v = *(const float4*)(tile + ku_chunk_off(row, q));
-#if !KU_SRC_IDENTITY
-      v.x = ku_src_t(v.x, i0 + q * 4 + 0, j KU_SRC_ARGS);
-      v.y = ku_src_t(v.y, i0 + q * 4 + 1, j KU_SRC_ARGS);
-      v.z = ku_src_t(v.z, i0 + q * 4 + 2, j KU_SRC_ARGS);
-      v.w = ku_src_t(v.w, i0 + q * 4 + 3, j KU_SRC_ARGS);
-#endif
-      if ((C % CJ != 0) && j >= C) v = make_float4(-KU_INF, -KU_INF, -KU_INF, -KU_INF);
-      return v;
-    };
-    float4 m = load(0);
-#pragma unroll 4
-    for (int it = 1; it < RPW / RSN; ++it) { const float4 v = load(it); m.x = fmaxf(m.x, v.x); m.y = fmaxf(m.y, v.y); m.z = fmaxf(m.z, v.z); m.w = fmaxf(m.w, v.w); }
-#pragma unroll
-    for (int o = CHUNKS; o <= 16; o <<= 1) {
-      m.x = fmaxf(m.x, __shfl_xor_sync(0xffffffffu, m.x, o)); m.y = fmaxf(m.y, __shfl_xor_sync(0xffffffffu, m.y, o));
-      m.z = fmaxf(m.z, __shfl_xor_sync(0xffffffffu, m.z, o)); m.w = fmaxf(m.w, __shfl_xor_sync(0xffffffffu, m.w, o));
-    }
-    // exp2(x*log2e - max*log2e); lines that are all -inf so far subtract 0 and sum zeros
-    const float4 k = make_float4(m.x == -KU_INF ? 0.0f : m.x * KU_LOG2E, m.y == -KU_INF ? 0.0f : m.y * KU_LOG2E,
-                                 m.z == -KU_INF ? 0.0f : m.z * KU_LOG2E, m.w == -KU_INF ? 0.0f : m.w * KU_LOG2E);
-    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-    for (int it = 0; it < RPW / RSN; ++it) {
-      const float4 v = load(it);
-      sum.x += ku_ex2(__fmaf_rn(v.x, KU_LOG2E, -k.x)); sum.y += ku_ex2(__fmaf_rn(v.y, KU_LOG2E, -k.y));
-      sum.z += ku_ex2(__fmaf_rn(v.z, KU_LOG2E, -k.z)); sum.w += ku_ex2(__fmaf_rn(v.w, KU_LOG2E, -k.w));
-    }
-#pragma unroll
-    for (int o = CHUNKS; o <= 16; o <<= 1) {
-      sum.x += __shfl_xor_sync(0xffffffffu, sum.x, o); sum.y += __shfl_xor_sync(0xffffffffu, sum.y, o);
-      sum.z += __shfl_xor_sync(0xffffffffu, sum.z, o); sum.w += __shfl_xor_sync(0xffffffffu, sum.w, o);
-    }
-    if (rs == 0) {   // the warp's pairs for lines 4q .. 4q+3, max in log2 units
-      *(float4*)&s_part[warp][q * 4] = make_float4(m.x * KU_LOG2E, sum.x, m.y * KU_LOG2E, sum.y);
-      *(float4*)&s_part[warp][q * 4 + 2] = make_float4(m.z * KU_LOG2E, sum.z, m.w * KU_LOG2E, sum.w);
-    }
-    __syncthreads();
-    if (warp == 0) {
-      if (lane < LW) {
-        float mm = s_part[0][lane].x, tot = s_part[0][lane].y;
-#pragma unroll
-        for (int w = 1; w < NW; ++w) ku_merge(mm, tot, s_part[w][lane].x, s_part[w][lane].y);
-        partials[((size_t)slab * P + rank) * LW + lane] = make_float2(mm, tot);
-      }
-      __syncwarp();
-      // the warp's 32 stores are ordered before this release by the warp barrier above
-      if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counters + slab) : "memory");
-    }
-    __syncthreads();   // s_part is free again
-  };
-
-  // step 2 of the n-th slab of this CTA
-  auto finish = [&](int n, int slab) {
-    const int b = n % NBUF;
-    const unsigned char* tile = tiles + b * TILE_BYTES;
-    const int i0 = slab * LW;
-    if (warp == 0) {
-      if (lane == 0) {   // one poller per CTA: the counter is shared by the whole group
-        unsigned spins = 0;
-        bool bad = s_failed != 0;
-        while (!bad && ku_ld_acquire(counters + slab) < (unsigned)P) {
-          if (++spins > SPIN_LIMIT || *(volatile int*)status != 0) { atomicExch(status, 3); bad = true; }
-          __nanosleep(20);
-        }
-        if (bad) s_failed = 1;
-      }
-      __syncwarp();   // orders the other lanes' loads of the pairs after lane 0's acquire
-      if (lane < LW) {
-        const float2* src = partials + (size_t)slab * P * LW + lane;
-        float2 pr[P];
-#pragma unroll
-        for (int c = 0; c < P; ++c) pr[c] = __ldcg(src + c * LW);
-        float mm = pr[0].x, tot = pr[0].y;
-#pragma unroll
-        for (int c = 1; c < P; ++c) ku_merge(mm, tot, pr[c].x, pr[c].y);
-        line_c[lane] = (mm == -KU_INF) ? __int_as_float(0x7fc00000) : mm + log2f(tot);
-      }
-    }
-    __syncthreads();
-    // lane = position within a 32-position strip; one 16-byte load gives 4 lines at that position,
-    // then 4 warp-wide stores of 128 contiguous bytes each
-#pragma unroll 4
-    for (int t = warp; t < CHUNKS * (CJ / 32); t += NW) {
-      const int q = t % CHUNKS, js = t / CHUNKS;
-      const int jj = js * 32 + lane, j = j0 + jj;
-      float4 v = *(const float4*)(tile + ku_chunk_off(jj, q));
-      const float4 c4 = *(const float4*)&line_c[q * 4];
-      if ((C % CJ == 0) || j < C) {
-#if !KU_SRC_IDENTITY
-        v.x = ku_src_t(v.x, i0 + q * 4 + 0, j KU_SRC_ARGS);
-        v.y = ku_src_t(v.y, i0 + q * 4 + 1, j KU_SRC_ARGS);
-        v.z = ku_src_t(v.z, i0 + q * 4 + 2, j KU_SRC_ARGS);
-        v.w = ku_src_t(v.w, i0 + q * 4 + 3, j KU_SRC_ARGS);
-#endif
-        ku_out_t* o = (ku_out_t*)out + (i64)(i0 + q * 4) * C + j;
-        if ((R % LW == 0) || i0 + q * 4 + 0 < R) KU_STORE(&o[0], KU_ENC(ku_ex2(__fmaf_rn(v.x, KU_LOG2E, -c4.x))));
-        if ((R % LW == 0) || i0 + q * 4 + 1 < R) KU_STORE(&o[(i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.y, KU_LOG2E, -c4.y))));
-        if ((R % LW == 0) || i0 + q * 4 + 2 < R) KU_STORE(&o[2 * (i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.z, KU_LOG2E, -c4.z))));
-        if ((R % LW == 0) || i0 + q * 4 + 3 < R) KU_STORE(&o[3 * (i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.w, KU_LOG2E, -c4.w))));
-      }
-    }
-    __syncthreads();  // every thread is done with tile b and with line_c
-    const int next = slab + NBUF * ngroups;
-    if (threadIdx.x == 0 && next < NSLABS) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy reads of the tile precede the async refill
-      issue(next, b);
-    }
-  };
-
+  const int q = warp & 7, h = warp >> 3;
+  const int ls = lane & 3, part = lane >> 2;
   int n = 0;
   for (int slab = group; slab < NSLABS; slab += ngroups, ++n) {
-    stats(n, slab);
-    if (NBUF == 1) finish(n, slab);                    // one tile: nothing to overlap inside the CTA, its neighbours on the SM do
-    else if (n > 0) finish(n - 1, slab - ngroups);     // the previous slab's exchange has had a whole statistics pass to complete
+    const int i0 = slab * LW;
+    {
+      unsigned spins = 0;
+      while (!ku_mbar_try(mb, (unsigned)(n & 1))) {
+        if (++spins > SPIN_LIMIT) { atomicExch(status, 1); break; }
+      }
+    }
+    // 1. tile -> registers
+    float4 x[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const int jj = (h + (NW / 8) * k) * 32 + lane, j = j0 + jj;
+      float4 v = *(const float4*)(tile + ku_chunk_off(jj, q));
+#if !KU_SRC_IDENTITY
+      {   // operands other than the staged one are read at coordinates clamped into the tensor: the padding is masked below
+        const int jc = (C % CJ != 0 && j >= C) ? C - 1 : j, ic = i0 + q * 4;
+        v.x = ku_src_t(v.x, (R % LW != 0 && ic + 0 >= R) ? R - 1 : ic + 0, jc KU_SRC_ARGS);
+        v.y = ku_src_t(v.y, (R % LW != 0 && ic + 1 >= R) ? R - 1 : ic + 1, jc KU_SRC_ARGS);
+        v.z = ku_src_t(v.z, (R % LW != 0 && ic + 2 >= R) ? R - 1 : ic + 2, jc KU_SRC_ARGS);
+        v.w = ku_src_t(v.w, (R % LW != 0 && ic + 3 >= R) ? R - 1 : ic + 3, jc KU_SRC_ARGS);
+      }
+#endif
+      if ((C % CJ != 0) && j >= C) v = make_float4(-KU_INF, -KU_INF, -KU_INF, -KU_INF);
+      x[k] = v;
+    }
+    __syncthreads();   // every thread has its part of the tile; s_x of the previous slab is no longer read
+    {
+      const int next = slab + ngroups;
+      if (threadIdx.x == 0 && next < NSLABS) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy reads of the tile precede the async refill
+        issue(next);
+      }
+    }
+    // 2. the warp's statistics of its four lines
+    float4 m = x[0];
+#pragma unroll
+    for (int k = 1; k < V; ++k) { m.x = fmaxf(m.x, x[k].x); m.y = fmaxf(m.y, x[k].y); m.z = fmaxf(m.z, x[k].z); m.w = fmaxf(m.w, x[k].w); }
+    m.x = ku_warp_max(m.x); m.y = ku_warp_max(m.y); m.z = ku_warp_max(m.z); m.w = ku_warp_max(m.w);
+    // exp2(x*log2e - max*log2e); lines that are all -inf here subtract 0 and sum zeros
+    const float4 kk = make_float4(m.x == -KU_INF ? 0.0f : m.x * KU_LOG2E, m.y == -KU_INF ? 0.0f : m.y * KU_LOG2E,
+                                  m.z == -KU_INF ? 0.0f : m.z * KU_LOG2E, m.w == -KU_INF ? 0.0f : m.w * KU_LOG2E);
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      x[k].x = ku_ex2(__fmaf_rn(x[k].x, KU_LOG2E, -kk.x)); sum.x += x[k].x;
+      x[k].y = ku_ex2(__fmaf_rn(x[k].y, KU_LOG2E, -kk.y)); sum.y += x[k].y;
+      x[k].z = ku_ex2(__fmaf_rn(x[k].z, KU_LOG2E, -kk.z)); sum.z += x[k].z;
+      x[k].w = ku_ex2(__fmaf_rn(x[k].w, KU_LOG2E, -kk.w)); sum.w += x[k].w;
+    }
+    const float tot = ku_sum4(sum.x, sum.y, sum.z, sum.w, lane);   // line 4q + (lane & 3)
+    if (lane < 4) {
+      const float ml = (ls == 0 ? m.x : ls == 1 ? m.y : ls == 2 ? m.z : m.w) * KU_LOG2E;   // -inf stays -inf
+      const unsigned long long w = ((unsigned long long)((__float_as_uint(tot) & 0x7fffffffu) | (par << 31)) << 32) | __float_as_uint(ml);
+      ku_st_relaxed(partials + ((size_t)slab * NPART + (rank * 2 + h)) * LW + q * 4 + lane, w);
+    }
+    // 3. gather the slab's pairs: warp w polls pairs w, w + NW, ... of every line (lane = line)
+    {
+      unsigned long long w[NE];
+      bool ok[NE];
+#pragma unroll
+      for (int t = 0; t < NE; ++t) ok[t] = warp + t * NW >= NPART;
+      unsigned spins = 0;
+      for (;;) {
+        bool pending = false;
+#pragma unroll
+        for (int t = 0; t < NE; ++t)
+          if (!ok[t]) w[t] = ku_ld_relaxed(partials + ((size_t)slab * NPART + warp + t * NW) * LW + lane);
+#pragma unroll
+        for (int t = 0; t < NE; ++t)
+          if (!ok[t]) {
+            if ((unsigned)(w[t] >> 63) == par) {
+              ok[t] = true;
+              s_x[warp + t * NW][lane] = make_float2(__uint_as_float((unsigned)w[t]), __uint_as_float((unsigned)(w[t] >> 32) & 0x7fffffffu));
+            } else {
+              pending = true;
+            }
+          }
+        if (!pending) break;
+        if (++spins > POLL_LIMIT) { atomicExch(status, 3); break; }
+        __nanosleep(40);
+      }
+    }
+    __syncthreads();
+    // the warp merges the pairs of its four lines: lane = (line lane & 3, pairs part, part + 8, ...)
+    float4 f;
+    {
+      const int line = q * 4 + ls;
+      float M = -KU_INF;
+#pragma unroll
+      for (int e = part; e < NPART; e += 8) M = fmaxf(M, s_x[e][line].x);
+      M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 4));
+      M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 8));
+      M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
+      float t = 0.0f;
+#pragma unroll
+      for (int e = part; e < NPART; e += 8) {
+        const float2 pr = s_x[e][line];
+        t += (pr.x == -KU_INF) ? pr.y : pr.y * ku_ex2(pr.x - M);   // a sum is 0 or NaN while its max is -inf
+      }
+      t += __shfl_xor_sync(0xffffffffu, t, 4);
+      t += __shfl_xor_sync(0xffffffffu, t, 8);
+      t += __shfl_xor_sync(0xffffffffu, t, 16);
+      const float c = (M == -KU_INF) ? __int_as_float(0x7fc00000) : M + log2f(t);
+      const float4 c4 = make_float4(__shfl_sync(0xffffffffu, c, 0), __shfl_sync(0xffffffffu, c, 1), __shfl_sync(0xffffffffu, c, 2), __shfl_sync(0xffffffffu, c, 3));
+      // e was taken against the warp's own maximum k <= c: the factor is at most 1. Where the warp saw only -inf, e is 0
+      // and k is 0: the factor must not overflow (0 * inf), but a NaN line stays NaN.
+      f.x = (m.x == -KU_INF) ? c4.x * 0.0f : ku_ex2(kk.x - c4.x);
+      f.y = (m.y == -KU_INF) ? c4.y * 0.0f : ku_ex2(kk.y - c4.y);
+      f.z = (m.z == -KU_INF) ? c4.z * 0.0f : ku_ex2(kk.z - c4.z);
+      f.w = (m.w == -KU_INF) ? c4.w * 0.0f : ku_ex2(kk.w - c4.w);
+    }
+    // write-out: a warp-wide store is 128 contiguous bytes of one line
+    ku_out_t* o = (ku_out_t*)out + (i64)(i0 + q * 4) * C + j0 + lane;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const int jj = (h + (NW / 8) * k) * 32;
+      if ((C % CJ == 0) || j0 + jj + lane < C) {
+        if ((R % LW == 0) || i0 + q * 4 + 0 < R) KU_STORE(&o[jj], KU_ENC(x[k].x * f.x));
+        if ((R % LW == 0) || i0 + q * 4 + 1 < R) KU_STORE(&o[(i64)C + jj], KU_ENC(x[k].y * f.y));
+        if ((R % LW == 0) || i0 + q * 4 + 2 < R) KU_STORE(&o[2 * (i64)C + jj], KU_ENC(x[k].z * f.z));
+        if ((R % LW == 0) || i0 + q * 4 + 3 < R) KU_STORE(&o[3 * (i64)C + jj], KU_ENC(x[k].w * f.w));
+      }
+    }
   }
-  if (NBUF > 1 && n > 0) finish(n - 1, group + (n - 1) * ngroups);
 }

@@ -28,6 +28,10 @@
 #define STRIPS (PWL / 32)
 #define NCI (PWL / 16)
 #define KU_LOG2E 1.4426950408889634f
+// the fused producer reads its other operands at coordinates clamped into the tensor: tiles overhang the last
+// lines / positions, and what is computed there is masked or never stored
+#define KU_CI(i) ((R % 32 != 0 && (i) >= R) ? R - 1 : (i))
+#define KU_CJ(j) ((C % JT != 0 && (j) >= C) ? C - 1 : (j))
 #define TILE_BYTES (JT * 128)
 #define SPIN_LIMIT (1u << 22)
 #define NJ ((C + JT - 1) / JT)
@@ -233,10 +237,10 @@ ku_softmax_panels_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
         const int row = it * 32 + warp * 4 + rs, j = j0 + row;
         float4 v = *(const float4*)(tile + row * 128 + ((q ^ (row & 7)) << 4));
 #if !KU_SRC_IDENTITY
-        v.x = ku_src_t(v.x, i0 + q * 4 + 0, j KU_SRC_ARGS);
-        v.y = ku_src_t(v.y, i0 + q * 4 + 1, j KU_SRC_ARGS);
-        v.z = ku_src_t(v.z, i0 + q * 4 + 2, j KU_SRC_ARGS);
-        v.w = ku_src_t(v.w, i0 + q * 4 + 3, j KU_SRC_ARGS);
+        v.x = ku_src_t(v.x, KU_CI(i0 + q * 4 + 0), KU_CJ(j) KU_SRC_ARGS);
+        v.y = ku_src_t(v.y, KU_CI(i0 + q * 4 + 1), KU_CJ(j) KU_SRC_ARGS);
+        v.z = ku_src_t(v.z, KU_CI(i0 + q * 4 + 2), KU_CJ(j) KU_SRC_ARGS);
+        v.w = ku_src_t(v.w, KU_CI(i0 + q * 4 + 3), KU_CJ(j) KU_SRC_ARGS);
 #endif
         if ((C % JT != 0) && j >= C) v = make_float4(-KU_INF, -KU_INF, -KU_INF, -KU_INF);
         x[it] = v;
@@ -320,10 +324,10 @@ ku_softmax_panels_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
         float4 v = *(const float4*)(tile + jj * 128 + ((q ^ (jj & 7)) << 4));
         if ((C % JT == 0) || j < C) {
 #if !KU_SRC_IDENTITY
-          v.x = ku_src_t(v.x, i0 + q * 4 + 0, j KU_SRC_ARGS);
-          v.y = ku_src_t(v.y, i0 + q * 4 + 1, j KU_SRC_ARGS);
-          v.z = ku_src_t(v.z, i0 + q * 4 + 2, j KU_SRC_ARGS);
-          v.w = ku_src_t(v.w, i0 + q * 4 + 3, j KU_SRC_ARGS);
+          v.x = ku_src_t(v.x, KU_CI(i0 + q * 4 + 0), KU_CJ(j) KU_SRC_ARGS);
+          v.y = ku_src_t(v.y, KU_CI(i0 + q * 4 + 1), KU_CJ(j) KU_SRC_ARGS);
+          v.z = ku_src_t(v.z, KU_CI(i0 + q * 4 + 2), KU_CJ(j) KU_SRC_ARGS);
+          v.w = ku_src_t(v.w, KU_CI(i0 + q * 4 + 3), KU_CJ(j) KU_SRC_ARGS);
 #endif
           ku_out_t* o = (ku_out_t*)out + (i64)(i0 + q * 4) * C + j;
           if ((R % 32 == 0) || i0 + q * 4 + 0 < R) KU_STORE(&o[0], KU_ENC(ku_ex2(__fmaf_rn(v.x, KU_LOG2E, -c4.x))));

@@ -272,15 +272,14 @@ Fused Scheduler::softmax(OpKind k, const Fused& f0, size_t axis, float eps) {
     Launch L;
     std::vector<int> leaf_args;
     size_t scratch = 0;
-    size_t zero = 0;
-    if (k == OpKind::Softmax && build_softmax_groups(*load_, f, axis, sm_, &L, &leaf_args, &scratch, &zero)) {
+    if (k == OpKind::Softmax && build_softmax_groups(*load_, f, axis, sm_, &L, &leaf_args, &scratch)) {
       const int sslot = new_slot(Slot::Temp, DType::U8, {scratch});
+      prog_.slots[static_cast<size_t>(sslot)].zero_init = true;
       for (int li : leaf_args) { Arg a; a.kind = Arg::SlotPtr; a.slot = f.leaves[static_cast<size_t>(li)].slot; L.args.push_back(a); }
       Arg o; o.kind = Arg::SlotPtr; o.slot = slot; L.args.push_back(o);
       Arg sc; sc.kind = Arg::SlotPtr; sc.slot = sslot; L.args.push_back(sc);
+      Arg ep; ep.kind = Arg::Epoch; L.args.push_back(ep);
       Arg st; st.kind = Arg::Status; L.args.push_back(st);
-      L.zero_slot = sslot;
-      L.zero_bytes = zero;
       L.algo_bytes = leaf_bytes(f) + static_cast<double>(prog_.slots[static_cast<size_t>(slot)].bytes);
       prog_.launches.push_back(std::move(L));
     } else if (k == OpKind::Softmax && (L = Launch(), leaf_args.clear(), build_softmax_panels(*load_, f, axis, sm_, &L, &leaf_args, &scratch))) {

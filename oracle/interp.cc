@@ -531,10 +531,62 @@ Val dot_f32(const Val& a, const Val& b, const Op& op) {
   return o;
 }
 
+// The f64 run of a GEMM-shaped contraction (leading batch axes in order, one contract axis per operand): the same
+// sums as dot_num<double> - per output element, products added in ascending k - walked in a cache-friendly order
+// (rows of B streamed, or eight output columns at a time), so that the full-size parity samples finish in seconds.
+// The f64 run is this test suite's tolerance reference, not a timed path.
+bool dgemm_shaped(const double* a, const Shape& as, const double* b, const Shape& bs, const Op& op, double* out) {
+  const size_t ra = as.size(), rb = bs.size(), nb = op.lb.size();
+  if (ra != nb + 2 || rb != nb + 2 || op.lc.size() != 1 || op.rc.size() != 1 || op.rb.size() != nb) return false;
+  for (size_t i = 0; i < nb; ++i) if (op.lb[i] != i || op.rb[i] != i) return false;
+  const size_t lc = op.lc[0], rc = op.rc[0];
+  if (lc < nb || rc < nb) return false;
+  const size_t lf = lc == nb ? nb + 1 : nb, rf = rc == nb ? nb + 1 : nb;
+  const auto a_st = row_major_strides(as), b_st = row_major_strides(bs);
+  const size_t m = as[lf], k = as[lc], n = bs[rf];
+  size_t batch = 1;
+  for (size_t i = 0; i < nb; ++i) batch *= as[i];
+  const size_t a_fs = a_st[lf], a_cs = a_st[lc], b_fs = b_st[rf], b_cs = b_st[rc];
+  for (size_t bi = 0; bi < batch; ++bi) {
+    const double* A = a + bi * m * k;
+    const double* B = b + bi * k * n;
+    double* O = out + bi * m * n;
+    if (b_fs == 1) {   // B is [k][n]: stream its rows
+      std::fill(O, O + m * n, 0.0);
+      for (size_t i = 0; i < m; ++i)
+        for (size_t kk = 0; kk < k; ++kk) {
+          const double av = A[i * a_fs + kk * a_cs];
+          const double* brow = B + kk * b_cs;
+          double* orow = O + i * n;
+          for (size_t j = 0; j < n; ++j) orow[j] += av * brow[j];
+        }
+    } else {           // B is [n][k]: eight independent dot products at a time
+      for (size_t i = 0; i < m; ++i) {
+        size_t j = 0;
+        for (; j + 8 <= n; j += 8) {
+          double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (size_t kk = 0; kk < k; ++kk) {
+            const double av = A[i * a_fs + kk * a_cs];
+            for (size_t u = 0; u < 8; ++u) acc[u] += av * B[(j + u) * b_fs + kk * b_cs];
+          }
+          for (size_t u = 0; u < 8; ++u) O[i * n + j + u] = acc[u];
+        }
+        for (; j < n; ++j) {
+          double acc = 0;
+          for (size_t kk = 0; kk < k; ++kk) acc += A[i * a_fs + kk * a_cs] * B[j * b_fs + kk * b_cs];
+          O[i * n + j] = acc;
+        }
+      }
+    }
+  }
+  return true;
+}
+
 Val dot_val(const Val& a, const Val& b, const Op& op) {
   if (a.wide) {
     Val o = make_val(a.dtype, dot_out_shape(a.shape, b.shape, op), true);
-    dot_num<double>(wd(a), a.shape, wd(b), b.shape, op, wd(o));
+    if (!(numel(o.shape) && dgemm_shaped(wd(a), a.shape, wd(b), b.shape, op, wd(o))))
+      dot_num<double>(wd(a), a.shape, wd(b), b.shape, op, wd(o));
     return o;
   }
   if (a.dtype == DType::F32) return dot_f32(a, b, op);

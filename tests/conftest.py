@@ -57,3 +57,21 @@ def gpu(cuda_lib):
     """The CUDA backend. Fails loudly (no skip, no fallback) when the device or library is missing."""
     from kurumi_b200 import api
     return api.CudaBackend(cuda_lib, 0)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Achieved errors of the narrow-format parity checks (relative where the relative band applies, and in units of
+    the row scale), and a copy under gpurun_out/ for the results table."""
+    from tests import util
+    if not util.PARITY_LOG:
+        return
+    terminalreporter.write_line("achieved parity errors (what: max rel err, max err / row scale)")
+    lines = [f"  {what}: {rel:.3e}, {scaled:.3e}" for what, rel, scaled in util.PARITY_LOG]
+    for ln in lines:
+        terminalreporter.write_line(ln)
+    try:
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        with open(os.path.join(ROOT, "gpurun_out", "parity_errors.txt"), "w") as f:
+            f.write("\n".join(lines) + "\n")
+    except OSError:
+        pass

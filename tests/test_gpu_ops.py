@@ -259,10 +259,9 @@ def test_softmax_through_transpose_and_bias(oracle_lib, cuda_lib, cpu, cpu64, gp
         assert c[0].shape == (m, n)
 
 
-@pytest.mark.parametrize("family,env", [("softmax_groups_tma", {}), ("softmax_panels_tma", {"KURUMI_SMT_NO_GROUPS": "1"}),
-                                        ("softmax_transposed_tma", {"KURUMI_SMT_NO_GROUPS": "1", "KURUMI_SMT_NO_PANELS": "1"})])
+@pytest.mark.parametrize("family,env", [("softmax_groups_tma", {}), ("softmax_panels_tma", {"KURUMI_SMT_NO_GROUPS": "1"})])
 def test_large_transposed_softmax_ragged_and_special_lines(oracle_lib, cuda_lib, cpu64, gpu, monkeypatch, family, env):
-    """Each of the three large-problem kernels on a shape that divides into nothing (2100 positions, 2052 lines),
+    """Each of the two large-problem kernels on a shape that divides into nothing (2100 positions, 2052 lines),
     with lines that are all -inf, hold a NaN, hold +inf, or a single finite entry."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)

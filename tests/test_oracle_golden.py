@@ -260,3 +260,28 @@ def test_narrow_float_conversions_match_torch(oracle_lib):
     oracle_lib.lib.ko_cast(C.c_uint32(api.F8E4M3), codes.ctypes.data_as(C.c_void_p), C.c_size_t(256), C.c_uint32(api.F32), back.ctypes.data_as(C.c_void_p))
     assert np.array_equal(back, torch.from_numpy(codes).view(torch.float8_e4m3fn).to(torch.float32).numpy(), equal_nan=True)
     assert np.array_equal(api.e4m3_to_f32(codes), back, equal_nan=True)
+
+
+def test_f64_run_contractions_in_gemm_shape(oracle_lib, cpu64):
+    """The f64 interpreter run walks GEMM-shaped contractions in a cache-friendly order; the sums are the ones
+    kurumi_core/src/interp/contract.rs:101-166 defines (products added in ascending k, per output element)."""
+    rng = np.random.default_rng(5)
+    g = api.Graph(oracle_lib)
+    a, b = rng.standard_normal((5, 7)), rng.standard_normal((7, 9))
+    q, k = rng.standard_normal((2, 3, 5, 4)), rng.standard_normal((2, 3, 11, 4))
+    v = rng.standard_normal((2, 3, 11, 6))
+    na, nb_, nq, nk, nv = (g.constant(x, api.F64) for x in (a, b, q, k, v))
+    nodes = [g.matmul(na, nb_), g.dot_general(nq, nk, [3], [3], [0, 1], [0, 1]), g.dot_general(g.dot_general(nq, nk, [3], [3], [0, 1], [0, 1]), nv, [3], [2], [0, 1], [0, 1]),
+             g.dot_general(nb_, na, [0], [1])]
+    got = [cpu64.eval(g, n).numpy() for n in nodes]
+    s = np.einsum("bhqd,bhkd->bhqk", q, k)
+    want = [a @ b, s, np.einsum("bhqk,bhkd->bhqd", s, v), (a @ b).T]
+    for w, x in zip(want, got):
+        assert x.shape == w.shape
+        assert np.abs(x - w).max() <= 1e-12 * np.abs(w).max()
+    # ascending-k order exactly: a sum whose result depends on the order of its terms
+    big = np.array([[1e16, 1.0, -1e16, 1.0]])
+    ones = np.ones((4, 8))
+    n1, n2 = g.constant(big, api.F64), g.constant(ones, api.F64)
+    assert (cpu64.eval(g, g.matmul(n1, n2)).numpy() == 1.0).all()          # ((1e16 + 1) - 1e16) + 1 = 1
+    assert (cpu64.eval(g, g.dot_general(n1, g.constant(np.ones((8, 4)), api.F64), [1], [1])).numpy() == 1.0).all()

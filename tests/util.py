@@ -90,6 +90,28 @@ def assert_close(o, c, rel, abs_=0.0, what=""):
     assert (err <= tol).all(), f"{what}: max err {err.max():.3e} (rel {np.max(err / np.maximum(np.abs(o[ok]), 1e-30)):.3e}), {int((err > tol).sum())} of {err.size} outside rel {rel} abs {abs_}"
 
 
+PARITY_LOG = []   # (what, max relative error outside the floor, max error in units of the row scale), printed at session end
+
+
+def assert_band(o, c, rel, step, what=""):
+    """The stated band for narrow-format contractions and attention: |got - want| <= rel * |want| for every element, with
+    the format's own resolution as the floor near zero: `step` (2^-8 for bf16: one unit in the last place of a value at
+    the row's scale) times the largest |want| of the element's row (last axis). Records the achieved errors."""
+    o, c = np.asarray(o, np.float64), np.asarray(c, np.float64)
+    assert o.shape == c.shape, (what, o.shape, c.shape)
+    assert np.isfinite(o).all() and np.isfinite(c).all(), f"{what}: non-finite values"
+    scale = np.abs(o).max(axis=-1, keepdims=True)
+    floor = step * scale
+    err = np.abs(o - c)
+    tol = np.maximum(rel * np.abs(o), floor)
+    above = np.abs(o) * rel > floor            # elements whose relative band is the wider one
+    max_rel = float((err[above] / np.abs(o)[above]).max()) if above.any() else 0.0
+    max_scaled = float((err / np.maximum(scale, 1e-300)).max())
+    PARITY_LOG.append((what, max_rel, max_scaled))
+    bad = err > tol
+    assert not bad.any(), f"{what}: {int(bad.sum())} of {err.size} outside rel {rel} / floor {step} x row scale; max rel {max_rel:.3e}, max err / row scale {max_scaled:.3e}"
+
+
 def threefry_np(key: int, ctr: np.ndarray) -> np.ndarray:
     """threefry2x32-20 (kurumi_core/src/rng.rs:10-26) over an array of 64-bit counters -> u64."""
     rot = [13, 15, 26, 6, 17, 29, 16, 24]
