@@ -1,34 +1,36 @@
 // Single-pass softmax through a transpose view: every input byte crosses HBM and L2 once, and every
 // element is read from shared memory once: a tile is lifted into registers as soon as it lands, so the
-// shared-memory tile is free for the next slab's TMA load while this slab's statistics are exchanged
-// and its output is written.
+// shared-memory ring only ever holds tiles in flight, and the exchange of line statistics between CTAs is
+// hidden behind the next slab's work.
 //
 // The dominant input is a plain f32 buffer read as in[j * ld + i] (i = line, j = position along the
 // softmax axis). A slab is 32 lines. A GROUP of P co-resident CTAs shares a slab: CTA r loads positions
-// [r*CJ, r*CJ + CJ) of it as a [CJ][32] f32 tile (TMA, 128-byte swizzled rows). Groups walk the slabs
-// with a fixed stride; there are no clusters, so any number of groups up to (resident CTAs / P) runs, and
-// the launch is cooperative so that a group's CTAs really are co-resident. Two CTAs of 512 threads fit an
-// SM: 2 x 64 KB of tiles being filled by TMA and 2 x 64 KB of tiles held in registers.
+// [r*CJ, r*CJ + CJ) of it as a [CJ][32] f32 tile (TMA, 128-byte swizzled rows) into a ring of NBUF tiles.
+// Groups walk the slabs with a fixed stride; there are no clusters, so any number of groups up to
+// (resident CTAs / P) runs, and the launch is cooperative so that a group's CTAs really are co-resident.
+// One CTA of 512 threads per SM: up to NBUF x 64 KB of tiles being filled by TMA and 2 x 64 KB of tiles
+// held in registers (128 registers per thread).
 //
 // Thread layout (the same for the statistics and for the write-out, so the values never leave their
 // registers): warp w owns the 16-byte chunk q = w % 8 of the tile rows (lines 4q .. 4q+3) and the
 // 32-position strips h, h + 2, h + 4, ... (h = w / 8); lane = position inside a strip. A thread holds
-// V = CJ / 64 float4 values: 4 lines at V positions. A warp-wide store then writes 128 contiguous bytes
-// of one output line.
+// V = CJ / 64 float4 values per tile: 4 lines at V positions. A warp-wide store then writes 128 contiguous
+// bytes of one output line.
 //
 // Per slab a CTA
 //   1. waits for its tile, copies it to registers (one conflict-free 16-byte shared-memory load per
-//      float4, the fused producer applied on the way) and releases the tile to the next TMA load;
+//      float4, the fused producer applied on the way) and hands the tile's buffer to the next TMA load;
 //   2. per warp: line maxima over its positions (redux.sync), e = exp2(x * log2e - k) in place with k the
 //      WARP's maximum in log2 units, line sums by a 6-shuffle butterfly; the warp's (max, sum) pairs go
 //      to global scratch as one 64-bit word each, whose top bit (the sign bit of the sum, which is never
 //      negative) carries the launch parity: data and "ready" flag travel in one store, no fence, no counter;
-//   3. polls the 2P words of each of the 32 lines (every warp polls its share, bounded), merges them to
+//   3. one slab later (steps 1 and 2 of the next slab come first, into the other register tile): polls the 2P
+//      words of each of the 32 lines (every warp polls its share, bounded), merges them to
 //      c = max + log2(sum) per line and writes out[line][position] = e * exp2(k - c).
 // One exp2 per element, plus a handful per thread. Every wait is bounded: a CTA that gives up records it
 // in *status and carries on (its results are then invalid, the host reports it).
 //
-// Spliced in by the host: R, C, P, CJ (multiple of 64), BOXJ, NT (512), NSLABS, KU_OUT_F32, KU_SRC_IDENTITY and
+// Spliced in by the host: R, C, P, CJ (multiple of 64), BOXJ, NBUF, NT (512), NSLABS, KU_OUT_F32, KU_SRC_IDENTITY and
 //   float ku_src_t(float lval, idx i, idx j KU_SRC_PARAMS) - the fused producer given the loaded value.
 #define LW 32                  /* lines per slab: a tile row is 128 bytes */
 #define NW (NT / 32)
@@ -85,46 +87,52 @@ __device__ __forceinline__ float ku_sum4(float a0, float a1, float a2, float a3,
   return s;
 }
 
-extern "C" __global__ void __launch_bounds__(NT, 2)
+extern "C" __global__ void __launch_bounds__(NT, 1)
 ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD void* __restrict__ out, void* __restrict__ scratch, unsigned epoch, int* __restrict__ status) {
-  extern __shared__ __align__(1024) unsigned char tiles_raw[];  // one tile of [CJ][32] f32, 128-byte swizzled rows
-  __shared__ __align__(8) unsigned long long full;
-  __shared__ __align__(16) float2 s_x[NPART][LW];               // the slab's (max, sum) pairs, as polled
+  extern __shared__ __align__(1024) unsigned char tiles_raw[];  // NBUF tiles of [CJ][32] f32, 128-byte swizzled rows
+  __shared__ __align__(8) unsigned long long full[NBUF];
+  // the slab's (max, sum) pairs, as polled. Rows are padded by four pairs (a row stride of 8 banks modulo 32): the
+  // merge reads pairs e, e + 1, e + 2, e + 3 of four neighbouring lines in one half-warp access, conflict-free
+  __shared__ __align__(16) float2 s_x[NPART][LW + 4];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int group = blockIdx.x / P, ngroups = gridDim.x / P, rank = blockIdx.x % P;
   const int j0 = rank * CJ;
   unsigned long long* partials = (unsigned long long*)scratch;   // [NSLABS][NPART][LW]; zero when allocated, parity flips per launch
   const unsigned par = epoch & 1u;
-  // the swizzle pattern is a function of the shared-memory address: the tile starts on a 1024-byte boundary
+  // the swizzle pattern is a function of the shared-memory address: the tiles start on a 1024-byte boundary
   // (the host sizes the allocation with 1024 bytes of slack)
-  unsigned char* tile = tiles_raw + ((1024u - (ku_smem(tiles_raw) & 1023u)) & 1023u);
-  const unsigned tile_s = ku_smem(tile), mb = ku_smem(&full);
+  unsigned char* tiles = tiles_raw + ((1024u - (ku_smem(tiles_raw) & 1023u)) & 1023u);
+  const unsigned tiles_s = ku_smem(tiles);
   if (blockIdx.x >= (unsigned)(ngroups * P)) return;   // CTAs beyond the last whole group have no work
 
-  auto issue = [&](int slab) {  // one thread: stream this CTA's share of a slab into the tile
+  auto issue = [&](int slab, int b) {  // one thread: stream this CTA's share of a slab into tile b
+    const unsigned mb = ku_smem(&full[b]);
     ku_mbar_expect(mb, TILE_BYTES);
-    for (int k = 0; k < CJ / BOXJ; ++k) ku_tma_2d(tile_s + k * BOXJ * 128, &tmap, slab * LW, j0 + k * BOXJ, mb);
+    for (int k = 0; k < CJ / BOXJ; ++k) ku_tma_2d(tiles_s + b * TILE_BYTES + k * BOXJ * 128, &tmap, slab * LW, j0 + k * BOXJ, mb);
   };
   if (threadIdx.x == 0) {
-    ku_mbar_init(mb, 1);
+    for (int b = 0; b < NBUF; ++b) ku_mbar_init(ku_smem(&full[b]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    if (group < NSLABS) issue(group);
+    for (int b = 0; b < NBUF; ++b)
+      if (group + b * ngroups < NSLABS) issue(group + b * ngroups, b);
   }
   __syncthreads();
 
   const int q = warp & 7, h = warp >> 3;
   const int ls = lane & 3, part = lane >> 2;
-  int n = 0;
-  for (int slab = group; slab < NSLABS; slab += ngroups, ++n) {
-    const int i0 = slab * LW;
+
+  // Steps 1 and 2 of the n-th slab of this CTA: tile -> registers x, the warp's statistics, e in place, pairs published.
+  // kk receives the warp's line maxima in log2 units (0 where the warp saw only -inf, flagged in minf).
+  auto take = [&](float4 (&x)[V], float4& kk, unsigned& minf, int n, int slab) {
+    const int b = n % NBUF, i0 = slab * LW;
+    const unsigned char* tile = tiles + b * TILE_BYTES;
     {
+      const unsigned mb = ku_smem(&full[b]), parity = (unsigned)((n / NBUF) & 1);
       unsigned spins = 0;
-      while (!ku_mbar_try(mb, (unsigned)(n & 1))) {
+      while (!ku_mbar_try(mb, parity)) {
         if (++spins > SPIN_LIMIT) { atomicExch(status, 1); break; }
       }
     }
-    // 1. tile -> registers
-    float4 x[V];
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       const int jj = (h + (NW / 8) * k) * 32 + lane, j = j0 + jj;
@@ -141,22 +149,21 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
       if ((C % CJ != 0) && j >= C) v = make_float4(-KU_INF, -KU_INF, -KU_INF, -KU_INF);
       x[k] = v;
     }
-    __syncthreads();   // every thread has its part of the tile; s_x of the previous slab is no longer read
+    __syncthreads();   // every thread has its part of the tile; s_x of the slab finished before is no longer read
     {
-      const int next = slab + ngroups;
+      const int next = slab + NBUF * ngroups;
       if (threadIdx.x == 0 && next < NSLABS) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy reads of the tile precede the async refill
-        issue(next);
+        issue(next, b);
       }
     }
-    // 2. the warp's statistics of its four lines
     float4 m = x[0];
 #pragma unroll
     for (int k = 1; k < V; ++k) { m.x = fmaxf(m.x, x[k].x); m.y = fmaxf(m.y, x[k].y); m.z = fmaxf(m.z, x[k].z); m.w = fmaxf(m.w, x[k].w); }
     m.x = ku_warp_max(m.x); m.y = ku_warp_max(m.y); m.z = ku_warp_max(m.z); m.w = ku_warp_max(m.w);
+    minf = (m.x == -KU_INF ? 1u : 0u) | (m.y == -KU_INF ? 2u : 0u) | (m.z == -KU_INF ? 4u : 0u) | (m.w == -KU_INF ? 8u : 0u);
     // exp2(x*log2e - max*log2e); lines that are all -inf here subtract 0 and sum zeros
-    const float4 kk = make_float4(m.x == -KU_INF ? 0.0f : m.x * KU_LOG2E, m.y == -KU_INF ? 0.0f : m.y * KU_LOG2E,
-                                  m.z == -KU_INF ? 0.0f : m.z * KU_LOG2E, m.w == -KU_INF ? 0.0f : m.w * KU_LOG2E);
+    kk = make_float4((minf & 1u) ? 0.0f : m.x * KU_LOG2E, (minf & 2u) ? 0.0f : m.y * KU_LOG2E, (minf & 4u) ? 0.0f : m.z * KU_LOG2E, (minf & 8u) ? 0.0f : m.w * KU_LOG2E);
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < V; ++k) {
@@ -171,8 +178,14 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
       const unsigned long long w = ((unsigned long long)((__float_as_uint(tot) & 0x7fffffffu) | (par << 31)) << 32) | __float_as_uint(ml);
       ku_st_relaxed(partials + ((size_t)slab * NPART + (rank * 2 + h)) * LW + q * 4 + lane, w);
     }
-    // 3. gather the slab's pairs: warp w polls pairs w, w + NW, ... of every line (lane = line)
-    {
+  };
+
+  // Step 3 of a slab whose pairs this CTA published a whole slab earlier: gather, merge, write out from registers.
+  // `guard`: no take() ran since the previous finish(), so its barrier has to be made up for before s_x is rewritten.
+  auto finish = [&](const float4 (&x)[V], const float4& kk, unsigned minf, int slab, bool guard) {
+    const int i0 = slab * LW;
+    if (guard) __syncthreads();
+    {   // warp w polls pairs w, w + NW, ... of every line (lane = line)
       unsigned long long w[NE];
       bool ok[NE];
 #pragma unroll
@@ -222,10 +235,10 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
       const float4 c4 = make_float4(__shfl_sync(0xffffffffu, c, 0), __shfl_sync(0xffffffffu, c, 1), __shfl_sync(0xffffffffu, c, 2), __shfl_sync(0xffffffffu, c, 3));
       // e was taken against the warp's own maximum k <= c: the factor is at most 1. Where the warp saw only -inf, e is 0
       // and k is 0: the factor must not overflow (0 * inf), but a NaN line stays NaN.
-      f.x = (m.x == -KU_INF) ? c4.x * 0.0f : ku_ex2(kk.x - c4.x);
-      f.y = (m.y == -KU_INF) ? c4.y * 0.0f : ku_ex2(kk.y - c4.y);
-      f.z = (m.z == -KU_INF) ? c4.z * 0.0f : ku_ex2(kk.z - c4.z);
-      f.w = (m.w == -KU_INF) ? c4.w * 0.0f : ku_ex2(kk.w - c4.w);
+      f.x = (minf & 1u) ? c4.x * 0.0f : ku_ex2(kk.x - c4.x);
+      f.y = (minf & 2u) ? c4.y * 0.0f : ku_ex2(kk.y - c4.y);
+      f.z = (minf & 4u) ? c4.z * 0.0f : ku_ex2(kk.z - c4.z);
+      f.w = (minf & 8u) ? c4.w * 0.0f : ku_ex2(kk.w - c4.w);
     }
     // write-out: a warp-wide store is 128 contiguous bytes of one line
     ku_out_t* o = (ku_out_t*)out + (i64)(i0 + q * 4) * C + j0 + lane;
@@ -239,5 +252,25 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
         if ((R % LW == 0) || i0 + q * 4 + 3 < R) KU_STORE(&o[3 * (i64)C + jj], KU_ENC(x[k].w * f.w));
       }
     }
+  };
+
+  // Two register tiles: while slab n waits for its group's pairs, slab n + 1 is lifted, reduced and published, so the
+  // exchange has a whole slab's worth of time to complete and CTAs of a group may drift apart by that much.
+  float4 xa[V], xb[V], ka, kb;
+  unsigned fa = 0, fb = 0;
+  int slab = group, n = 0;
+  if (slab >= NSLABS) return;
+  take(xa, ka, fa, 0, slab);
+  for (;;) {
+    const int s1 = slab + ngroups;
+    if (s1 < NSLABS) take(xb, kb, fb, n + 1, s1);
+    finish(xa, ka, fa, slab, s1 >= NSLABS && n > 0);
+    if (s1 >= NSLABS) break;
+    const int s2 = s1 + ngroups;
+    if (s2 < NSLABS) take(xa, ka, fa, n + 2, s2);
+    finish(xb, kb, fb, s1, s2 >= NSLABS);
+    if (s2 >= NSLABS) break;
+    slab = s2;
+    n += 2;
   }
 }
