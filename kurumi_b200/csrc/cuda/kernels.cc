@@ -179,22 +179,24 @@ bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis,
   bool transposed = false;
   LineLeaf big;
   if (!emit_line_source_fn(f, axis, &src_fn, leaf_args, &R, &C, &transposed, &big) || !transposed || big.leaf < 0) return false;
-  // A group of P CTAs shares a slab of 32 lines; a CTA keeps CJ positions of it, V = CJ / 64 float4 values per thread,
-  // in registers, for two slabs at a time. V <= 8 keeps the kernel at 128 registers (one CTA of 512 threads per SM), so a
-  // line has at most 32 * 512 positions; longer lines take the panel kernel.
-  const int64_t lw = 32, nt = 512;
-  const int64_t p = std::max<int64_t>(2, (C + 511) / 512);
-  if (p > 32 || sm_count < p || R < lw * 8 || C < 1024 || R * C < (int64_t(1) << 22) || R >= (int64_t(1) << 30) || (big.base * 4) % 16 != 0) return false;
-  const int64_t cj = ((C + p - 1) / p + 63) / 64 * 64;
-  const int64_t boxj = cj % 256 == 0 ? 256 : cj % 128 == 0 ? 128 : 64;
+  // A group of P CTAs shares a slab of 32 lines; a CTA keeps CJ positions of it, eight float4 values per thread at most,
+  // in registers, for two slabs at a time (128 registers per thread). Two CTAs of 256 threads per SM (CJ <= 256) while a
+  // group then has at most 32 CTAs, else one CTA of 512 threads (CJ <= 512); lines beyond 32 * 512 positions take the
+  // panel kernel.
+  const int64_t lw = 32;
+  const int64_t nt = (C + 255) / 256 <= 32 ? 256 : 512, span = nt;   // positions per CTA at eight values per thread
+  const int64_t p = std::max<int64_t>(2, (C + span - 1) / span), per_sm = 512 / nt, unit = nt / 8;
+  if (p > 32 || sm_count * per_sm < p || R < lw * 8 || C < 1024 || R * C < (int64_t(1) << 22) || R >= (int64_t(1) << 30) || (big.base * 4) % 16 != 0) return false;
+  const int64_t cj = ((C + p - 1) / p + unit - 1) / unit * unit;
+  const int64_t boxj = cj % 256 == 0 ? 256 : cj % 128 == 0 ? 128 : cj % 64 == 0 ? 64 : 32;
   const int64_t slabs = (R + lw - 1) / lw;
-  const int64_t nbuf = std::min<int64_t>(3, (200 * 1024) / (cj * lw * 4));   // tiles in flight per CTA
+  const int64_t nbuf = std::min<int64_t>(3, (200 * 1024 / per_sm) / (cj * lw * 4));   // tiles in flight per CTA
   std::string src = device_prelude() + src_fn +
                     defines({{"R", R}, {"C", C}, {"P", p}, {"CJ", cj}, {"BOXJ", boxj}, {"NBUF", nbuf}, {"NT", nt}, {"NSLABS", slabs}, {"KU_OUT_F32", 1}, {"KU_SRC_IDENTITY", big.identity ? 1 : 0}}) +
                     kSrc_softmax_groups_tma;
   out->name = "softmax_groups_tma";
   out->kernel = load(src, "ku_softmax_groups_tma", false);
-  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(slabs, sm_count / p) * p);
+  out->grid[0] = static_cast<unsigned>(std::min<int64_t>(slabs, per_sm * sm_count / p) * p);
   out->block[0] = static_cast<unsigned>(nt);
   out->smem = static_cast<unsigned>(nbuf * cj * lw * 4 + 1024);   // 1024 bytes of slack: the ring is placed on a 1024-byte boundary
   out->persistent_clusters = -1;                               // cap the grid at the co-resident CTA count on first launch,
@@ -211,7 +213,7 @@ bool build_softmax_groups(const KernelLoader& load, const Fused& f, size_t axis,
   tm.tm.box[0] = static_cast<uint32_t>(lw); tm.tm.box[1] = static_cast<uint32_t>(boxj);
   tm.tm.swz = CU_TENSOR_MAP_SWIZZLE_128B;
   out->args.push_back(tm);
-  *scratch_bytes = static_cast<size_t>(slabs * 2 * p * lw * 8);   // one 64-bit (max, sum, parity) word per slab, CTA, warp half and line
+  *scratch_bytes = static_cast<size_t>(slabs * (nt / 256) * p * lw * 8);   // one 64-bit (max, sum, parity) word per slab, CTA, warp of a chunk and line
   return true;
 }
 

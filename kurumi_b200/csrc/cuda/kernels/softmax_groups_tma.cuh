@@ -8,13 +8,14 @@
 // [r*CJ, r*CJ + CJ) of it as a [CJ][32] f32 tile (TMA, 128-byte swizzled rows) into a ring of NBUF tiles.
 // Groups walk the slabs with a fixed stride; there are no clusters, so any number of groups up to
 // (resident CTAs / P) runs, and the launch is cooperative so that a group's CTAs really are co-resident.
-// One CTA of 512 threads per SM: up to NBUF x 64 KB of tiles being filled by TMA and 2 x 64 KB of tiles
-// held in registers (128 registers per thread).
+// 512 threads per SM at 128 registers each, as one CTA or as two CTAs of 256 (of different groups, so that one's
+// exp2 phase overlaps the other's stores): a ring of NBUF tiles being filled by TMA per CTA, and two tiles per
+// CTA held in registers.
 //
 // Thread layout (the same for the statistics and for the write-out, so the values never leave their
 // registers): warp w owns the 16-byte chunk q = w % 8 of the tile rows (lines 4q .. 4q+3) and the
-// 32-position strips h, h + 2, h + 4, ... (h = w / 8); lane = position inside a strip. A thread holds
-// V = CJ / 64 float4 values per tile: 4 lines at V positions. A warp-wide store then writes 128 contiguous
+// 32-position strips h, h + HALVES, ... (h = w / 8, HALVES = warps / 8); lane = position inside a strip. A thread
+// holds V = CJ / (32 HALVES) float4 values per tile: 4 lines at V positions. A warp-wide store then writes 128 contiguous
 // bytes of one output line.
 //
 // Per slab a CTA
@@ -24,18 +25,19 @@
 //      WARP's maximum in log2 units, line sums by a 6-shuffle butterfly; the warp's (max, sum) pairs go
 //      to global scratch as one 64-bit word each, whose top bit (the sign bit of the sum, which is never
 //      negative) carries the launch parity: data and "ready" flag travel in one store, no fence, no counter;
-//   3. one slab later (steps 1 and 2 of the next slab come first, into the other register tile): polls the 2P
+//   3. one slab later (steps 1 and 2 of the next slab come first, into the other register tile): polls the HALVES x P
 //      words of each of the 32 lines (every warp polls its share, bounded), merges them to
 //      c = max + log2(sum) per line and writes out[line][position] = e * exp2(k - c).
 // One exp2 per element, plus a handful per thread. Every wait is bounded: a CTA that gives up records it
 // in *status and carries on (its results are then invalid, the host reports it).
 //
-// Spliced in by the host: R, C, P, CJ (multiple of 64), BOXJ, NBUF, NT (512), NSLABS, KU_OUT_F32, KU_SRC_IDENTITY and
+// Spliced in by the host: R, C, P, CJ (multiple of NT / 8), BOXJ, NBUF, NT (256 or 512), NSLABS, KU_OUT_F32, KU_SRC_IDENTITY and
 //   float ku_src_t(float lval, idx i, idx j KU_SRC_PARAMS) - the fused producer given the loaded value.
 #define LW 32                  /* lines per slab: a tile row is 128 bytes */
 #define NW (NT / 32)
-#define V (CJ / 64)            /* float4 values per thread */
-#define NPART (2 * P)          /* (max, sum) pairs per line and slab: one per CTA and warp half */
+#define HALVES (NW / 8)        /* warps that share a 16-byte chunk of the tile rows */
+#define V (CJ / (32 * HALVES)) /* float4 values per thread and tile */
+#define NPART (HALVES * P)     /* (max, sum) pairs per line and slab: one per CTA and warp of a chunk */
 #define NE ((NPART + NW - 1) / NW)   /* pairs of a line a warp polls */
 #define KU_LOG2E 1.4426950408889634f
 #define TILE_BYTES (CJ * 128)
@@ -87,7 +89,7 @@ __device__ __forceinline__ float ku_sum4(float a0, float a1, float a2, float a3,
   return s;
 }
 
-extern "C" __global__ void __launch_bounds__(NT, 1)
+extern "C" __global__ void __launch_bounds__(NT, 512 / NT)
 ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD void* __restrict__ out, void* __restrict__ scratch, unsigned epoch, int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char tiles_raw[];  // NBUF tiles of [CJ][32] f32, 128-byte swizzled rows
   __shared__ __align__(8) unsigned long long full[NBUF];
@@ -135,7 +137,7 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
     }
 #pragma unroll
     for (int k = 0; k < V; ++k) {
-      const int jj = (h + (NW / 8) * k) * 32 + lane, j = j0 + jj;
+      const int jj = (h + HALVES * k) * 32 + lane, j = j0 + jj;
       float4 v = *(const float4*)(tile + ku_chunk_off(jj, q));
 #if !KU_SRC_IDENTITY
       {   // operands other than the staged one are read at coordinates clamped into the tensor: the padding is masked below
@@ -176,7 +178,7 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
     if (lane < 4) {
       const float ml = (ls == 0 ? m.x : ls == 1 ? m.y : ls == 2 ? m.z : m.w) * KU_LOG2E;   // -inf stays -inf
       const unsigned long long w = ((unsigned long long)((__float_as_uint(tot) & 0x7fffffffu) | (par << 31)) << 32) | __float_as_uint(ml);
-      ku_st_relaxed(partials + ((size_t)slab * NPART + (rank * 2 + h)) * LW + q * 4 + lane, w);
+      ku_st_relaxed(partials + ((size_t)slab * NPART + (rank * HALVES + h)) * LW + q * 4 + lane, w);
     }
   };
 
@@ -244,7 +246,7 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
     ku_out_t* o = (ku_out_t*)out + (i64)(i0 + q * 4) * C + j0 + lane;
 #pragma unroll
     for (int k = 0; k < V; ++k) {
-      const int jj = (h + (NW / 8) * k) * 32;
+      const int jj = (h + HALVES * k) * 32;
       if ((C % CJ == 0) || j0 + jj + lane < C) {
         if ((R % LW == 0) || i0 + q * 4 + 0 < R) KU_STORE(&o[jj], KU_ENC(x[k].x * f.x));
         if ((R % LW == 0) || i0 + q * 4 + 1 < R) KU_STORE(&o[(i64)C + jj], KU_ENC(x[k].y * f.y));
