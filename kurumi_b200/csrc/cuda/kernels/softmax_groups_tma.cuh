@@ -187,28 +187,20 @@ ku_softmax_groups_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
   auto finish = [&](const float4 (&x)[V], const float4& kk, unsigned minf, int slab, bool guard) {
     const int i0 = slab * LW;
     if (guard) __syncthreads();
-    {   // warp w polls pairs w, w + NW, ... of every line (lane = line)
-      unsigned long long w[NE];
-      bool ok[NE];
+    // warp w polls pairs w, w + NW, ... of every line (lane = line), two loads in flight at a time
 #pragma unroll
-      for (int t = 0; t < NE; ++t) ok[t] = warp + t * NW >= NPART;
+    for (int t0 = 0; t0 < NE; t0 += 2) {
+      const int e0 = warp + t0 * NW, e1 = e0 + NW;
+      const unsigned long long* p0 = partials + ((size_t)slab * NPART + e0) * LW + lane;
+      bool ok0 = e0 >= NPART, ok1 = (t0 + 1 >= NE) || e1 >= NPART;
       unsigned spins = 0;
-      for (;;) {
-        bool pending = false;
-#pragma unroll
-        for (int t = 0; t < NE; ++t)
-          if (!ok[t]) w[t] = ku_ld_relaxed(partials + ((size_t)slab * NPART + warp + t * NW) * LW + lane);
-#pragma unroll
-        for (int t = 0; t < NE; ++t)
-          if (!ok[t]) {
-            if ((unsigned)(w[t] >> 63) == par) {
-              ok[t] = true;
-              s_x[warp + t * NW][lane] = make_float2(__uint_as_float((unsigned)w[t]), __uint_as_float((unsigned)(w[t] >> 32) & 0x7fffffffu));
-            } else {
-              pending = true;
-            }
-          }
-        if (!pending) break;
+      while (!(ok0 && ok1)) {
+        unsigned long long w0 = 0, w1 = 0;
+        if (!ok0) w0 = ku_ld_relaxed(p0);
+        if (!ok1) w1 = ku_ld_relaxed(p0 + (size_t)NW * LW);
+        if (!ok0 && (unsigned)(w0 >> 63) == par) { ok0 = true; s_x[e0][lane] = make_float2(__uint_as_float((unsigned)w0), __uint_as_float((unsigned)(w0 >> 32) & 0x7fffffffu)); }
+        if (!ok1 && (unsigned)(w1 >> 63) == par) { ok1 = true; s_x[e1][lane] = make_float2(__uint_as_float((unsigned)w1), __uint_as_float((unsigned)(w1 >> 32) & 0x7fffffffu)); }
+        if (ok0 && ok1) break;
         if (++spins > POLL_LIMIT) { atomicExch(status, 3); break; }
         __nanosleep(40);
       }
