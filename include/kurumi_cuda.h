@@ -94,6 +94,18 @@ int32_t ku_cuda_softmax_lines_f32(const KuBackend *b, const float *in, const flo
  * can overlap on the GPU (different streams, no dependency) race on it. No cudaMalloc / cudaFree. */
 int32_t ku_cuda_softmax_lines_f32_noalloc(const float *in, const float *bias, float *out, size_t lines, size_t len, size_t ld, void *stream);
 
+/* Row splitting: a new graph whose root yields rows [c, c + 1) * rows / parts (axis 0) of `root`, for any part c, given
+ * the matching slice of every input the root depends on row-wise and all of the others. Writes the part graph's root
+ * to *part_root, the number of Input nodes in the root's cone to *n_inputs and, for the first `cap` of them, the
+ * original node, the part graph's node and the axis to slice (-1: the part needs the whole tensor). NULL with a reason
+ * in ku_last_error() when the evaluation does not separate by rows (a reduction or softmax along the split axis,
+ * attention split over its queries, ...) or the extents do not divide. Free the result with ku_graph_free. The CUDA
+ * backend uses the same analysis inside ku_eval_with to pipeline large host-buffer evaluations, and callers use it to
+ * shard one evaluation over several GPUs. The reference evaluates a graph in one piece on one device
+ * (kurumi_core/src/backend.rs:14-31): no counterpart. Pure graph code: the test oracle exports it too. */
+KuGraph *ku_graph_row_split(const KuGraph *g, KuNode root, size_t parts, KuNode *part_root, KuNode *orig_inputs, KuNode *part_inputs, int32_t *axes, size_t cap,
+                            size_t *n_inputs);
+
 /* Compile every kernel the evaluation of ids[0..n] needs to an sm_100a cubin, without a GPU.
  * Writes the kernel family of each launch, one per line, into out (no NUL); returns the full
  * length, or (size_t)-1 on error. */

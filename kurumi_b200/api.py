@@ -542,6 +542,20 @@ class CudaBackend(Backend):
         return res
 
 
+def row_split(g: Graph, root: int, parts: int):
+    """(part graph, part root, [(original input node, part input node, axis or None)]) of core/split.h; raises Error
+    with the reason when the evaluation does not separate by rows."""
+    L = g.lib.lib
+    L.ku_graph_row_split.restype = C.c_void_p
+    cap = 256
+    proot, n = C.c_uint32(0), C.c_size_t(0)
+    orig, part, axes = (C.c_uint32 * cap)(), (C.c_uint32 * cap)(), (C.c_int32 * cap)()
+    h = L.ku_graph_row_split(g.h, C.c_uint32(root), C.c_size_t(parts), C.byref(proot), orig, part, axes, C.c_size_t(cap), C.byref(n))
+    if not h:
+        raise Error(g.lib.last_error())
+    return Graph(g.lib, h), int(proot.value), [(int(orig[i]), int(part[i]), None if axes[i] < 0 else int(axes[i])) for i in range(min(n.value, cap))]
+
+
 def compile_check(lib: Library, g: Graph, nodes) -> list:
     """NVRTC-compile every kernel the evaluation needs (no GPU). Returns the kernel families."""
     lib.lib.ku_cuda_compile_check.restype = C.c_size_t

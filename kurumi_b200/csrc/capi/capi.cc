@@ -8,6 +8,7 @@
 #include <cstring>
 
 #include "handles.h"
+#include "../core/split.h"
 
 using namespace ku;
 
@@ -333,6 +334,24 @@ size_t ku_runnable_entry_input_name(const KuRunnable* h, size_t i, size_t j, uin
   return write_name(e->inputs[j].name, out, cap);
 }
 void ku_runnable_free(KuRunnable* h) { delete h; }
+
+// ---- row splitting (core/split.h) ---------------------------------------------------------------
+KuGraph* ku_graph_row_split(const KuGraph* g, KuNode root, size_t parts, KuNode* part_root, KuNode* orig_inputs, KuNode* part_inputs, int32_t* axes, size_t cap, size_t* n_inputs) {
+  if (!g) { set_err("ku_graph_row_split: null graph handle"); return nullptr; }
+  return guard<KuGraph*>(nullptr, [&]() -> KuGraph* {
+    ku::SplitPlan plan;
+    std::string why;
+    if (!ku::row_split(g->g, root, parts, &plan, &why)) { set_err("ku_graph_row_split: " + why); return nullptr; }
+    if (part_root) *part_root = plan.root;
+    if (n_inputs) *n_inputs = plan.inputs.size();
+    for (size_t i = 0; i < plan.inputs.size() && i < cap; ++i) {
+      if (orig_inputs) orig_inputs[i] = plan.inputs[i].orig;
+      if (part_inputs) part_inputs[i] = plan.inputs[i].part;
+      if (axes) axes[i] = plan.inputs[i].axis;
+    }
+    return new KuGraph{std::move(plan.graph)};
+  });
+}
 
 // ---- feeds ------------------------------------------------------------------------------------
 KuFeeds* ku_feeds_new(void) { return new KuFeeds(); }
