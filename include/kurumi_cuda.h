@@ -94,6 +94,24 @@ int32_t ku_cuda_softmax_lines_f32(const KuBackend *b, const float *in, const flo
  * can overlap on the GPU (different streams, no dependency) race on it. No cudaMalloc / cudaFree. */
 int32_t ku_cuda_softmax_lines_f32_noalloc(const float *in, const float *bias, float *out, size_t lines, size_t len, size_t ld, void *stream);
 
+/* Everything the backend caches for a graph - compiled programs with their scratch buffers, uploaded constants,
+ * chunk pipelines with their device buffers - lives until the backend is freed or until this call; call it before
+ * ku_graph_free in a process that records many graphs. Reference analogue: the Metal backend's per-graph caches,
+ * kurumi_metal/src/backend.rs:95-109, which die with the backend. */
+void ku_cuda_release_graph(const KuBackend *b, const KuGraph *g);
+
+/* Assembly of a row-sharded result over NCCL (NVLink / NVSwitch), one process per GPU: rank 0 makes a 128-byte id
+ * (ku_cuda_comm_unique_id) and hands it to the other ranks by any host channel; every rank then calls
+ * ku_cuda_comm_init (collective) on its backend. ku_cuda_all_gather_rows returns, on every rank, a new device tensor
+ * [world * rows, ...] holding the ranks' shards in rank order; it is queued on the backend's stream. Shards must have
+ * the same shape on every rank. The sharded evaluation itself needs no exchange (each rank evaluates the part graph of
+ * ku_graph_row_split on its slices); this is only for callers that want the whole result on one device. 0 / non-NULL
+ * ok, -1 / NULL error. No counterpart in the reference, which is single-device (kurumi_core/src/backend.rs:14-31). */
+int32_t ku_cuda_comm_unique_id(uint8_t *out128);
+int32_t ku_cuda_comm_init(const KuBackend *b, const uint8_t *id128, int32_t rank, int32_t world);
+void ku_cuda_comm_free(const KuBackend *b);
+KuDevTensor *ku_cuda_all_gather_rows(const KuBackend *b, const KuDevTensor *shard);
+
 /* Row splitting: a new graph whose root yields rows [c, c + 1) * rows / parts (axis 0) of `root`, for any part c, given
  * the matching slice of every input the root depends on row-wise and all of the others. Writes the part graph's root
  * to *part_root, the number of Input nodes in the root's cone to *n_inputs and, for the first `cap` of them, the

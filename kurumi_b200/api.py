@@ -113,6 +113,20 @@ class Tensor:
         self.lib.lib.ku_tensor_shape(self.h, out)
         return tuple(out[i] for i in range(r))
 
+    @property
+    def nbytes(self) -> int:
+        return int(self.lib.lib.ku_tensor_nbytes(self.h))
+
+    def copy_into(self, ptr: int):
+        """ku_tensor_bytes into a caller-owned buffer of at least nbytes."""
+        self.lib.lib.ku_tensor_bytes(self.h, C.c_void_p(ptr))
+
+    def free(self):
+        """Give the storage back now instead of at garbage collection."""
+        if self.h:
+            self.lib.lib.ku_tensor_free(self.h)
+            self.h = None
+
     def numpy(self) -> np.ndarray:
         """Values as numpy; bf16 / fp8 come back as raw bit patterns (uint16 / uint8)."""
         n = self.lib.lib.ku_tensor_nbytes(self.h)
@@ -123,7 +137,8 @@ class Tensor:
 
     def __del__(self):
         try:
-            self.lib.lib.ku_tensor_free(self.h)
+            if self.h:
+                self.lib.lib.ku_tensor_free(self.h)
         except Exception:
             pass
 
@@ -518,6 +533,27 @@ class CudaBackend(Backend):
     def sync(self):
         if self.lib.lib.ku_cuda_sync(self.h) != 0:
             raise Error(self.lib.last_error())
+
+    def release_graph(self, g: Graph):
+        self.lib.lib.ku_cuda_release_graph(self.h, g.h)
+
+    def comm_unique_id(self) -> bytes:
+        buf = (C.c_uint8 * 128)()
+        if self.lib.lib.ku_cuda_comm_unique_id(buf) != 0:
+            raise Error(self.lib.last_error())
+        return bytes(buf)
+
+    def comm_init(self, uid: bytes, rank: int, world: int):
+        buf = (C.c_uint8 * 128)(*uid)
+        if self.lib.lib.ku_cuda_comm_init(self.h, buf, C.c_int32(rank), C.c_int32(world)) != 0:
+            raise Error(self.lib.last_error())
+
+    def comm_free(self):
+        self.lib.lib.ku_cuda_comm_free(self.h)
+
+    def all_gather_rows(self, shard: "DevTensor") -> "DevTensor":
+        self.lib.lib.ku_cuda_all_gather_rows.restype = C.c_void_p
+        return DevTensor(self, self.lib.lib.ku_cuda_all_gather_rows(self.h, shard.h))
 
     @property
     def stream(self) -> int:

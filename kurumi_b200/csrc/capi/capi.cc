@@ -374,7 +374,8 @@ KuTensor* ku_tensor_new(uint32_t dtype, const uint8_t* data, size_t nbytes, cons
     Tensor t;
     t.dtype = dt;
     t.shape = to_shape(shape, rank);
-    t.bytes.assign(data, data + nbytes);
+    t.bytes.resize(nbytes);
+    ku::HostMem::copy(t.bytes.data(), data, nbytes);
     if (dt == DType::BOOL) for (auto& b : t.bytes) b = b ? 1 : 0;
     return new KuTensor{std::make_shared<const Tensor>(std::move(t))};
   });
@@ -397,7 +398,7 @@ ptrdiff_t ku_tensor_data_f32(const KuTensor* t, float* out, size_t cap) {
 size_t ku_tensor_nbytes(const KuTensor* t) { return t ? t->t->bytes.size() : 0; }
 void ku_tensor_bytes(const KuTensor* t, uint8_t* out) {
   if (!t || !out) return;
-  std::memcpy(out, t->t->bytes.data(), t->t->bytes.size());
+  ku::HostMem::copy(out, t->t->bytes.data(), t->t->bytes.size());
 }
 
 }  // extern "C"

@@ -31,6 +31,10 @@ const char* op_name(OpKind k) {
 }
 
 static std::atomic<uint64_t> g_graph_counter{1};
+
+void* (*HostMem::alloc)(size_t) = [](size_t bytes) -> void* { return std::malloc(bytes ? bytes : 1); };
+void (*HostMem::release)(void*, size_t) = [](void* p, size_t) { std::free(p); };
+void (*HostMem::copy)(void*, const void*, size_t) = [](void* dst, const void* src, size_t bytes) { if (bytes) std::memcpy(dst, src, bytes); };
 Graph::Graph() : id_(g_graph_counter.fetch_add(1)) {}
 
 const Node& Graph::node(NodeId i) const {

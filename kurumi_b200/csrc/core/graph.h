@@ -13,6 +13,7 @@
 #include <array>
 #include <cstdint>
 #include <memory>
+#include <new>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -28,16 +29,46 @@ inline size_t numel(const Shape& s) { size_t n = 1; for (size_t d : s) n *= d; r
 std::string shape_str(const Shape& s);
 std::vector<size_t> row_major_strides(const Shape& s);
 
+// Host storage of tensors is obtained through two hooks, so that a device backend can hand out page-locked memory
+// (a copy between such memory and the device runs at the full rate of the link and overlaps with kernels). The
+// defaults are malloc and free. Elements are left uninitialised by resize(); assign(n, 0) still clears.
+struct HostMem {
+  static void* (*alloc)(size_t bytes);
+  static void (*release)(void* p, size_t bytes);
+  static void (*copy)(void* dst, const void* src, size_t bytes);   // large host-to-host copies (default: memcpy)
+};
+template <typename T>
+struct HostAlloc {
+  using value_type = T;
+  HostAlloc() = default;
+  template <typename U> HostAlloc(const HostAlloc<U>&) {}
+  T* allocate(size_t n) {
+    void* p = HostMem::alloc(n * sizeof(T));
+    if (!p) throw std::bad_alloc();
+    return static_cast<T*>(p);
+  }
+  void deallocate(T* p, size_t n) { HostMem::release(p, n * sizeof(T)); }
+  template <typename U> void construct(U* p) noexcept { ::new (static_cast<void*>(p)) U; }
+  template <typename U, typename... A> void construct(U* p, A&&... a) { ::new (static_cast<void*>(p)) U(std::forward<A>(a)...); }
+  template <typename U> bool operator==(const HostAlloc<U>&) const { return true; }
+  template <typename U> bool operator!=(const HostAlloc<U>&) const { return false; }
+};
+using Bytes = std::vector<uint8_t, HostAlloc<uint8_t>>;
+
 // Host tensor (the reference's TensorVal): row-major, little-endian element bytes.
 struct Tensor {
   Shape shape;
   DType dtype = DType::F32;
-  std::vector<uint8_t> bytes;
+  Bytes bytes;
   size_t len() const { return bytes.size() / dtype_width(dtype); }
   template <typename T> const T* data() const { return reinterpret_cast<const T*>(bytes.data()); }
   template <typename T> T* data() { return reinterpret_cast<T*>(bytes.data()); }
   static Tensor make(DType dt, Shape shape) {
     Tensor t; t.dtype = dt; t.bytes.assign(std::max<size_t>(numel(shape), 0) * dtype_width(dt), 0); t.shape = std::move(shape); return t;
+  }
+  // storage left uninitialised: for results that are overwritten in full
+  static Tensor make_uninit(DType dt, Shape shape) {
+    Tensor t; t.dtype = dt; t.bytes.resize(numel(shape) * dtype_width(dt)); t.shape = std::move(shape); return t;
   }
   static Tensor from_f32(const float* p, size_t n, Shape shape) {
     Tensor t; t.dtype = DType::F32; t.shape = std::move(shape); t.bytes.resize(n * 4);

@@ -3,14 +3,16 @@
 #include <cstring>
 
 #include "../capi/handles.h"
+#include "hostmem.h"
 
 namespace ku::cu {
 
-CudaBackend::CudaBackend(int device) : rt_(device) {}
+CudaBackend::CudaBackend(int device) : rt_(device) { install_pinned_host_memory(); }
 
 CudaBackend::~CudaBackend() {
   rt_.make_current();
   cudaStreamSynchronize(rt_.stream());
+  for (auto& kv : pipelines_) destroy_pipeline(*kv.second);
   for (auto& e : ev_pool_) { cudaEventDestroy(e.first); cudaEventDestroy(e.second); }
 }
 
@@ -201,11 +203,20 @@ void CudaBackend::free_dev(DevTensor* t) {
 }
 
 std::vector<Tensor> CudaBackend::eval_many_with(const Graph& g, const std::vector<NodeId>& ids, const Feeds& feeds) {
+  if (ids.size() == 1 && !profiling_) {   // a large evaluation that separates by rows streams through the device in chunks
+    rt_.make_current();
+    (void)g.node(ids[0]);
+    if (Pipeline* p = pipeline_for(g, ids[0], feeds)) {
+      std::vector<Tensor> res;
+      res.push_back(run_pipeline(*p, g, ids[0], feeds));
+      return res;
+    }
+  }
   std::vector<DevTensor*> outs = eval_device(g, ids, feeds, DevFeeds{});
   std::vector<Tensor> res;
   try {
     for (DevTensor* d : outs) {
-      Tensor t = Tensor::make(d->dtype, d->shape);
+      Tensor t = Tensor::make_uninit(d->dtype, d->shape);
       download(*d, t.bytes.data());
       res.push_back(std::move(t));
     }

@@ -6,6 +6,8 @@
 #include <map>
 #include <memory>
 
+#include "../core/split.h"
+#include "comm.h"
 #include "sched.h"
 
 namespace ku::cu {
@@ -35,6 +37,14 @@ class CudaBackend : public Backend {
   void download(const DevTensor& t, void* host);
   void free_dev(DevTensor* t);
 
+  // Multi-GPU assembly (comm.h): join the box's communicator, then gather row shards into [world * rows, ...] on every rank.
+  void comm_init(const uint8_t id[128], int rank, int world);
+  void comm_free() { comm_.reset(); }
+  DevTensor* all_gather_rows(const DevTensor& shard);
+
+  // Forget everything cached for a graph (compiled programs with their scratch, uploaded constants, chunk pipelines).
+  void release_graph(uint64_t graph_id);
+
   Runtime& runtime() { return rt_; }
   // Per-launch timing with CUDA events on the launching stream (off by default).
   void set_profiling(bool on);
@@ -48,7 +58,30 @@ class CudaBackend : public Backend {
   Compiled& program_for(const Graph& g, const std::vector<NodeId>& ids);
   void* const_ptr(const Graph& g, NodeId node);
 
+  // A host-buffer evaluation cut into row chunks (core/split.h): the upload of chunk c + 1, the kernels of chunk c and
+  // the download of chunk c - 1 run at the same time on three streams (pipeline.cc).
+  struct ChunkInput {
+    SplitInput si;
+    DType dtype = DType::F32;
+    Shape full_shape, part_shape;
+    size_t outer = 1, width = 0, pitch = 0;   // the slice of part c: `outer` runs of `width` bytes, `pitch` bytes apart, from byte c * width
+    void* dev[2] = {nullptr, nullptr};        // device copies: two in rotation for a sliced input, one for a whole one
+  };
+  struct Pipeline {
+    bool usable = false;
+    SplitPlan plan;
+    std::vector<ChunkInput> inputs;
+    cudaStream_t h2d = nullptr, d2h = nullptr;
+    cudaEvent_t ev_whole = nullptr;
+    std::vector<cudaEvent_t> ev_in, ev_k;
+  };
+  Pipeline* pipeline_for(const Graph& g, NodeId root, const Feeds& feeds);
+  Tensor run_pipeline(Pipeline& p, const Graph& g, NodeId root, const Feeds& feeds);
+  void destroy_pipeline(Pipeline& p);
+
   Runtime rt_;
+  std::unique_ptr<Comm> comm_;
+  std::map<std::pair<uint64_t, NodeId>, std::unique_ptr<Pipeline>> pipelines_;
   std::map<std::pair<uint64_t, std::vector<NodeId>>, std::unique_ptr<Compiled>> programs_;
   std::map<std::pair<uint64_t, NodeId>, void*> consts_;
   bool profiling_ = false;

@@ -52,7 +52,7 @@ KuDevTensor* ku_cuda_upload_bytes(const KuBackend* b, uint32_t dtype, const void
 KuTensor* ku_cuda_download(const KuBackend* b, const KuDevTensor* t) {
   if (!t) { set_err("ku_cuda_download: null tensor"); return nullptr; }
   return guard<KuTensor*>(nullptr, [&]() {
-    Tensor h = Tensor::make(t->t->dtype, t->t->shape);
+    Tensor h = Tensor::make_uninit(t->t->dtype, t->t->shape);
     cuda_of(b)->download(*t->t, h.bytes.data());
     return new KuTensor{std::make_shared<const Tensor>(std::move(h))};
   });
@@ -122,6 +122,25 @@ size_t ku_cuda_profile_take(const KuBackend* b, uint8_t* out, size_t cap) {
     if (out && cap) std::memcpy(out, s.data(), std::min(cap, s.size()));
     return s.size();
   });
+}
+
+int32_t ku_cuda_comm_unique_id(uint8_t* out) {
+  if (!out) { set_err("ku_cuda_comm_unique_id: null out"); return -1; }
+  return guard<int32_t>(-1, [&]() { ku::cu::Comm::unique_id(out); return 0; });
+}
+int32_t ku_cuda_comm_init(const KuBackend* b, const uint8_t* id, int32_t rank, int32_t world) {
+  if (!id) { set_err("ku_cuda_comm_init: null id"); return -1; }
+  return guard<int32_t>(-1, [&]() { cuda_of(b)->comm_init(id, rank, world); return 0; });
+}
+void ku_cuda_comm_free(const KuBackend* b) { guard<int>(0, [&]() { cuda_of(b)->comm_free(); return 0; }); }
+KuDevTensor* ku_cuda_all_gather_rows(const KuBackend* b, const KuDevTensor* shard) {
+  if (!shard) { set_err("ku_cuda_all_gather_rows: null tensor"); return nullptr; }
+  return guard<KuDevTensor*>(nullptr, [&]() { return new KuDevTensor{cuda_of(b)->all_gather_rows(*shard->t)}; });
+}
+
+void ku_cuda_release_graph(const KuBackend* b, const KuGraph* g) {
+  if (!g) return;
+  guard<int>(0, [&]() { cuda_of(b)->release_graph(g->g.id()); return 0; });
 }
 
 KuNode ku_cuda_amp_to(KuGraph* g, KuNode root, uint32_t dtype) {

@@ -785,7 +785,7 @@ Val rand_val(const Op& op, const Val& seed_v, bool wide_mode) {
 
 Val from_tensor(const Tensor& t, bool wide_mode) {
   Val v;
-  v.shape = t.shape; v.dtype = t.dtype; v.wide = false; v.bytes = t.bytes;
+  v.shape = t.shape; v.dtype = t.dtype; v.wide = false; v.bytes.assign(t.bytes.begin(), t.bytes.end());
   return (wide_mode && is_float(t.dtype)) ? widen(v) : v;
 }
 
@@ -826,7 +826,7 @@ Tensor to_tensor(const Val& v) {
   Tensor t;
   t.shape = v.shape;
   t.dtype = v.wide ? DType::F64 : v.dtype;
-  t.bytes = v.bytes;
+  t.bytes.assign(v.bytes.begin(), v.bytes.end());
   return t;
 }
 

@@ -1,69 +1,70 @@
-"""Chunked host-buffer evaluation (kurumi_b200/pipeline.py): the result assembled from chunks of output rows,
-with uploads, kernels and downloads overlapped, equals the single evaluation."""
+"""ku_eval_with on host tensors streams a large row-separable evaluation through the device in chunks (upload, kernels
+and download overlapped, kurumi_b200/csrc/cuda/pipeline.cc): the result equals the evaluation done in one piece on
+device-resident inputs, bit for bit, for each of the five benchmark graphs; graphs that do not separate, and small
+ones, take the one-piece path."""
 import numpy as np
 import pytest
-import torch
 
-from kurumi_b200 import api, configs, pipeline
+from kurumi_b200 import api, configs
 
 pytestmark = pytest.mark.gpu
 
-
-def pinned(arr: np.ndarray) -> torch.Tensor:
-    t = torch.from_numpy(np.ascontiguousarray(arr).view(np.uint8).reshape(-1)).pin_memory()
-    return t
-
-
-@pytest.mark.parametrize("case", ["softmax_columns", "reduce_rows", "gemm_rows"])
-def test_chunked_equals_single(cuda_lib, gpu, case):
-    rng = np.random.default_rng(11)
-    chunks = 4
-    if case == "softmax_columns":
-        n = 1024
-        make = lambda g, c: configs.transposed_softmax(g, n=n, lines=n // c)
-        arrays = [(rng.standard_normal((n, n)).astype(np.float32), api.F32, 1), (rng.uniform(-1, 1, n).astype(np.float32), api.F32, None)]
-    elif case == "reduce_rows":
-        make = lambda g, c: configs.fused_reduce(g, rows=512 // c, cols=768)
-        arrays = [(rng.uniform(-1, 1, (512, 768)).astype(np.float32), api.F32, 0), (rng.uniform(-1, 1, (512, 768)).astype(np.float32), api.F32, 0)]
-    else:
-        make = lambda g, c: configs.gemm_bias_gelu(g, m=1024 // c, n=256, kdim=384)
-        arrays = [(api.f32_to_bf16(rng.standard_normal((1024, 384)).astype(np.float32) * 0.05), api.BF16, 0),
-                  (api.f32_to_bf16(rng.standard_normal((384, 256)).astype(np.float32) * 0.05), api.BF16, None),
-                  (api.f32_to_bf16(rng.uniform(-0.1, 0.1, 256).astype(np.float32)), api.BF16, None)]
-    # the single evaluation
-    g1 = api.Graph(cuda_lib)
-    root1, gens1 = make(g1, 1)
-    feeds = api.Feeds(cuda_lib)
-    for node, (a, dt, _) in zip(gens1, arrays):
-        feeds.set(node, a, dt)
-    whole = gpu.eval_with(g1, root1, feeds)
-    want = whole.numpy()
-    # the chunked evaluation from pinned host buffers
-    gc = api.Graph(cuda_lib)
-    rootc, gensc = make(gc, chunks)
-    hosts = [pinned(a) for (a, _, _) in arrays]
-    inputs = [pipeline.HostInput(node, h.data_ptr(), tuple(a.shape), dt, axis) for node, h, (a, dt, axis) in zip(gensc, hosts, arrays)]
-    out_host = torch.zeros(want.nbytes, dtype=torch.uint8).pin_memory()
-    rows = want.shape[0]
-    pipe = pipeline.RowPipeline(gpu, gc, rootc, inputs, out_host.data_ptr(), rows, want.nbytes // rows, chunks)
-    try:
-        for _ in range(3):   # buffers, events and the compiled program are reused from step to step
-            out_host.zero_()
-            pipe.step()
-            got = out_host.numpy().view(want.dtype).reshape(want.shape)
-            if case == "softmax_columns":   # the slab and the square problem may select different softmax kernels
-                np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-12)
-            else:
-                assert np.array_equal(got, want), case
-    finally:
-        pipe.close()
+CASES = [
+    (configs.fused_reduce, dict(rows=2048, cols=2048)),
+    (configs.transposed_softmax, dict(n=2048)),
+    (configs.gemm_bias_gelu, dict(m=2048, n=1024, kdim=1024)),
+    (configs.causal_attention, dict(batch=4, heads=4, seq=512, dh=128, fused=True)),
+    (configs.fp8_weight_gemm, dict(m=2048, kdim=1024, n=2048, amp=True)),
+]
 
 
-def test_uneven_split_is_refused(cuda_lib, gpu):
+@pytest.mark.parametrize("make,kwargs", CASES)
+def test_chunked_host_evaluation_equals_one_piece(cuda_lib, gpu, make, kwargs):
     g = api.Graph(cuda_lib)
-    root, gens = configs.fused_reduce(g, rows=100, cols=64)
-    x = torch.zeros(300 * 64 * 4, dtype=torch.uint8).pin_memory()
-    inputs = [pipeline.HostInput(n, x.data_ptr(), (300, 64), api.F32, 0) for n in gens]
-    out = torch.zeros(1200, dtype=torch.uint8).pin_memory()
-    with pytest.raises(api.Error):
-        pipeline.RowPipeline(gpu, g, root, inputs, out.data_ptr(), 300, 4, 7)
+    root, gens = make(g, **kwargs)
+    dev, host = {}, api.Feeds(cuda_lib)
+    for node, mk in gens.items():
+        h = api.Graph(cuda_lib)
+        dev[node] = gpu.eval_device(h, [mk(h)])[0]
+        host.set(node, dev[node].numpy(), dev[node].dtype)
+    one_piece = gpu.eval_device(g, [root], None, dev)[0].numpy()
+    before = gpu.stats()
+    chunked = gpu.eval_with(g, root, host)
+    after = gpu.stats()
+    got = chunked.numpy()
+    assert got.shape == one_piece.shape and got.tobytes() == one_piece.tobytes()
+    # it really ran in chunks: several launches of the same program, and exactly the input / output bytes crossed the bus
+    assert after["launches"] - before["launches"] >= 8
+    assert after["h2d_bytes"] - before["h2d_bytes"] == sum(d.nbytes for d in dev.values())
+    assert after["d2h_bytes"] - before["d2h_bytes"] == one_piece.nbytes
+    # a second call replays the cached pipeline
+    again = gpu.eval_with(g, root, host).numpy()
+    assert again.tobytes() == one_piece.tobytes()
+    gpu.release_graph(g)
+    assert gpu.eval_with(g, root, host).numpy().tobytes() == one_piece.tobytes()
+
+
+def test_graphs_that_do_not_separate_run_in_one_piece(cuda_lib, gpu):
+    rng = np.random.default_rng(3)
+    g = api.Graph(cuda_lib)
+    x = g.input([4096, 2048], api.F32)
+    root = g.softmax(x, 0)                       # normalises along the rows
+    xv = rng.standard_normal((4096, 2048)).astype(np.float32)
+    before = gpu.stats()["launches"]
+    got = gpu.eval_with(g, root, api.Feeds(cuda_lib).set(x, xv)).numpy()
+    assert gpu.stats()["launches"] - before <= 2
+    e = np.exp(xv.astype(np.float64) - xv.max(axis=0))
+    assert np.abs(got - e / e.sum(axis=0)).max() < 1e-6
+
+
+def test_missing_and_misshapen_feeds_fail_before_anything_is_queued(cuda_lib, gpu):
+    g = api.Graph(cuda_lib)
+    root, gens = configs.fused_reduce(g, rows=2048, cols=2048)
+    x, y = list(gens)
+    ok = np.zeros((2048, 2048), np.float32)
+    gpu.eval_with(g, root, api.Feeds(cuda_lib).set(x, ok).set(y, ok))
+    with pytest.raises(api.Error, match="missing feed"):
+        gpu.eval_with(g, root, api.Feeds(cuda_lib).set(x, ok))
+    with pytest.raises(api.Error, match="has shape"):
+        gpu.eval_with(g, root, api.Feeds(cuda_lib).set(x, ok).set(y, np.zeros((2048, 1024), np.float32)))
+    assert np.array_equal(gpu.eval_with(g, root, api.Feeds(cuda_lib).set(x, ok).set(y, ok)).numpy(), np.zeros(2048, np.float32))
