@@ -26,9 +26,9 @@ def test_fused_attention_matches_oracle(oracle_lib, cuda_lib, cpu, cpu64, gpu, s
     w, _, _ = p.run(cpu64, gpu, [out])
     got = util.to_f64(c[0], dts[0])
     util.assert_band(w[0], got, 2e-2, 2.0 ** -8, f"fused attention {shape} vs f64 run")
-    # the native-dtype oracle rounds scores and probabilities to bf16 on the way and is itself up to the stated band away
-    # from the f64 run: the two are compared with twice the band
-    util.assert_band(util.to_f64(o[0], dts[0]), got, 4e-2, 2.0 ** -7, f"fused attention {shape} vs bf16 oracle")
+    # the native-dtype oracle rounds raw scores, scaled scores and probabilities to bf16 on the way: it is itself further
+    # from the f64 run than the kernel is, so this is a cross-check with a wide band (the stated band is the one above)
+    util.assert_band(util.to_f64(o[0], dts[0]), got, 6e-2, 2.0 ** -6, f"fused attention {shape} vs bf16 oracle")
     if causal:   # query 0 attends to key 0 only (kurumi_core/tests/ops.rs:258-270)
         vv = util.to_f64(p.feeds[v][0], api.BF16)
         assert np.array_equal(got[..., 0, :], vv[..., 0, :])
@@ -60,9 +60,10 @@ def test_decomposed_attention_and_auto_selection(oracle_lib, cuda_lib, cpu, cpu6
             if tag == api.F32:
                 util.assert_close(z, util.to_f64(b, dt), 1e-4, 1e-4 * np.abs(z).max(), "decomposed attention f32")
             else:   # scores and probabilities are rounded to bf16 between the kernels, exactly the interpreter's steps: the
-                # native oracle is the reference here (one bf16 step), the f64 run is twice the band away
+                # native oracle is the reference here (one bf16 step); those roundings put the interpreter itself, and so this
+                # path, further from the f64 run than the fused kernel is
                 util.assert_band(util.to_f64(a, dt), util.to_f64(b, dt), 2.0 ** -6, 2.0 ** -7, "decomposed attention bf16 vs bf16 oracle")
-                util.assert_band(z, util.to_f64(b, dt), 4e-2, 2.0 ** -7, "decomposed attention bf16 vs f64 run")
+                util.assert_band(z, util.to_f64(b, dt), 6e-2, 2.0 ** -6, "decomposed attention bf16 vs f64 run")
 
 
 def test_attention_config_graph_uses_the_fused_primitive(cuda_lib):

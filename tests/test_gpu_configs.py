@@ -75,7 +75,7 @@ def test_c3_gemm_bias_gelu(oracle_lib, cuda_lib, cpu, cpu64, gpu):
 def test_c4_causal_attention(oracle_lib, cuda_lib, cpu, cpu64, gpu):
     got, native, wide, _ = run_config(configs.causal_attention, dict(batch=1, heads=2, seq=256, dh=128, fused=True), oracle_lib, cuda_lib, cpu, cpu64, gpu)
     util.assert_band(wide, got, 2e-2, STEP_BF16, "c4 reduced size vs f64 run")
-    util.assert_band(native, got, 4e-2, 2 * STEP_BF16, "c4 reduced size vs bf16 oracle")   # both are up to the band away from the f64 run
+    util.assert_band(native, got, 6e-2, 4 * STEP_BF16, "c4 reduced size vs bf16 oracle")   # a cross-check: the bf16 interpreter rounds its scores and is itself further from the f64 run
 
 
 @pytest.mark.parametrize("amp", [False, True])

@@ -12,9 +12,9 @@ pytestmark = pytest.mark.gpu
 CASES = [
     (configs.fused_reduce, dict(rows=2048, cols=2048)),
     (configs.transposed_softmax, dict(n=2048)),
-    (configs.gemm_bias_gelu, dict(m=2048, n=1024, kdim=1024)),
-    (configs.causal_attention, dict(batch=4, heads=4, seq=512, dh=128, fused=True)),
-    (configs.fp8_weight_gemm, dict(m=2048, kdim=1024, n=2048, amp=True)),
+    (configs.gemm_bias_gelu, dict(m=4096, n=1024, kdim=1024)),
+    (configs.causal_attention, dict(batch=8, heads=4, seq=1024, dh=128, fused=True)),
+    (configs.fp8_weight_gemm, dict(m=4096, kdim=1024, n=2048, amp=True)),
 ]
 
 
@@ -32,16 +32,21 @@ def test_chunked_host_evaluation_equals_one_piece(cuda_lib, gpu, make, kwargs):
     chunked = gpu.eval_with(g, root, host)
     after = gpu.stats()
     got = chunked.numpy()
-    assert got.shape == one_piece.shape and got.tobytes() == one_piece.tobytes()
+
+    def same(a, b):
+        if make is configs.transposed_softmax:   # a chunk of lines may run another softmax kernel (another summation order): the f32 band applies
+            return a.shape == b.shape and np.allclose(a, b, rtol=1e-5, atol=1e-12)
+        return a.shape == b.shape and a.tobytes() == b.tobytes()
+    assert same(got, one_piece)
     # it really ran in chunks: several launches of the same program, and exactly the input / output bytes crossed the bus
     assert after["launches"] - before["launches"] >= 8
     assert after["h2d_bytes"] - before["h2d_bytes"] == sum(d.nbytes for d in dev.values())
     assert after["d2h_bytes"] - before["d2h_bytes"] == one_piece.nbytes
     # a second call replays the cached pipeline
     again = gpu.eval_with(g, root, host).numpy()
-    assert again.tobytes() == one_piece.tobytes()
+    assert again.tobytes() == got.tobytes()
     gpu.release_graph(g)
-    assert gpu.eval_with(g, root, host).numpy().tobytes() == one_piece.tobytes()
+    assert gpu.eval_with(g, root, host).numpy().tobytes() == got.tobytes()
 
 
 def test_graphs_that_do_not_separate_run_in_one_piece(cuda_lib, gpu):
