@@ -4,22 +4,26 @@
     python bench.py --gpus N --steps K --warmup W            (this backend)
     python bench.py --impl reference --gpus N --steps K ...  (the reference's CPU path, restated)
 
-A "step" is one evaluation of the workload graph over one batch of seeded synthetic input. The
-default workload is configuration 2 of the baseline (view-fused row softmax through a transpose
-view, f32 [8192, 8192] + bias): the metric is achieved HBM GB/s = algorithmic bytes (one read of L,
-one read of the bias, one write of the output) / device time. With N > 1 every rank evaluates its
-own shard of an N-times larger batch (weak scaling, no data-path collective); the value is the
-sum over ranks divided by the slowest rank's time. One JSON line is printed by rank 0.
+A "step" is one evaluation of the workload graph over one batch of seeded synthetic input. The headline workload
+is configuration 2 of the baseline (view-fused row softmax through a transpose view, f32 [8192, 8192] + bias): the
+metric is achieved HBM GB/s = algorithmic bytes (one read of L, one read of the bias, one write of the output) /
+device time. The other four configurations are measured in the same run and reported under "workloads".
 
-`e2e` is the same metric with every input in pinned host memory and the result read back to pinned host
-memory inside the timed region, through the library's public calls: the evaluation is cut into chunks of
-independent output rows (kurumi_b200/pipeline.py) so that uploads, kernels and downloads overlap; the
-chunked result is compared with the single evaluation byte for byte. Inputs smaller than a few L2s are
-rotated through copies so that no step finds them cached.
+With N > 1 the ONE named problem is sharded by rows (ku_graph_row_split): rank r evaluates rows [r, r + 1) * M / N
+on its slices of the row-wise inputs and on all of the replicated ones; there is no collective on the data path,
+outputs stay device-resident shards ("scaling": "strong", value = whole-problem work / slowest rank's time). The
+NCCL all-gather that assembles the shards (ku_cuda_all_gather_rows) is timed apart, as "assembly".
+
+`e2e` is the same metric through the drop-in call with host buffers: ku_feeds_set + ku_eval_with + ku_tensor_bytes
+per step, host tensors in, a host tensor out; the library streams the evaluation through the device in row chunks.
+Inputs smaller than a few L2s are rotated through copies so that no device-timed step finds them cached.
+One JSON line is printed by rank 0.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes as C
+import hashlib
 import json
 import os
 import subprocess
@@ -34,26 +38,15 @@ sys.path.insert(0, ROOT)
 
 from kurumi_b200 import api, build, configs  # noqa: E402
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each workload's dominant kernel,
-# from one ncu capture per kernel at the full workload size; the captures are summarised under profiles/.
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each workload's dominant kernel, from one
+# ncu capture per kernel at the full workload size, summarised in the named file under profiles/. An entry is used only
+# while the kernel source it was captured from is unchanged (first 16 hex digits of its SHA-256).
 NCU_TRAFFIC = {
-    ("c1_fused_reduce", "reduce_rows"): 137.8e6,
-    ("c2_transposed_softmax", "softmax_groups_tma"): 481.4e6,
-    ("c2_transposed_softmax", "softmax_panels_tma"): 535.7e6,
-    ("c3_gemm_bias_gelu", "gemm_tc"): 1231e6,
-    ("c4_causal_attention", "attention_tc"): 1057e6,
-    ("c5_fp8_weight_gemm", "gemm_tc_f8"): 3556e6,
-}
-
-# how a workload's evaluation is cut into chunks of independent output rows for the end-to-end measurement:
-# chunk count, the builder arguments of one chunk, and per input (in the builder's order) the axis it is
-# sharded along (None = every chunk needs all of it)
-CHUNKING = {
-    "c1_fused_reduce": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, rows=kw["rows"] // c), "axes": [0, 0]},
-    "c2_transposed_softmax": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, lines=kw["n"] // c), "axes": [1, None]},
-    "c3_gemm_bias_gelu": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, m=kw["m"] // c), "axes": [0, None, None]},
-    "c4_causal_attention": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, batch=kw["batch"] // c), "axes": [0, 0, 0]},
-    "c5_fp8_weight_gemm": {"chunks": 8, "chunk_kw": lambda kw, c: dict(kw, m=kw["m"] // c), "axes": [0, None, None]},
+    ("c1_fused_reduce", "reduce_rows"): (137.8e6, "profiles/reduce_rows__c1_fused_reduce.txt", "kurumi_b200/csrc/cuda/emit.cc", "0000000000000000"),
+    ("c2_transposed_softmax", "softmax_groups_tma"): (481.4e6, "profiles/softmax_groups_tma__c2_transposed_softmax.txt", "kurumi_b200/csrc/cuda/kernels/softmax_groups_tma.cuh", "0000000000000000"),
+    ("c3_gemm_bias_gelu", "gemm_tc"): (1231e6, "profiles/gemm_tc2__c3_gemm_bias_gelu.txt", "kurumi_b200/csrc/cuda/kernels/gemm_tc2.cuh", "0000000000000000"),
+    ("c4_causal_attention", "attention_tc"): (1057e6, "profiles/attention_tc__c4_causal_attention.txt", "kurumi_b200/csrc/cuda/kernels/attention_tc.cuh", "0000000000000000"),
+    ("c5_fp8_weight_gemm", "gemm_tc_f8"): (3556e6, "profiles/gemm_tc2_f8__c5_fp8_weight_gemm.txt", "kurumi_b200/csrc/cuda/kernels/gemm_tc2.cuh", "0000000000000000"),
 }
 
 WORKLOADS = {
@@ -64,6 +57,7 @@ WORKLOADS = {
     "c4_causal_attention": (configs.causal_attention, dict(batch=8, heads=32, seq=4096, dh=128), "tensor"),
     "c5_fp8_weight_gemm": (configs.fp8_weight_gemm, dict(m=16384, kdim=8192, n=28672), "tensor"),
 }
+HEADLINE = "c2_transposed_softmax"
 
 
 def algorithmic_work(name: str, kw: dict):
@@ -71,8 +65,8 @@ def algorithmic_work(name: str, kw: dict):
     if name == "c1_fused_reduce":
         return 2 * kw["rows"] * kw["cols"] * 4 + kw["rows"] * 4, 0.0
     if name == "c2_transposed_softmax":
-        n = kw["n"]
-        return 2 * n * n * 4 + n * 4, 0.0
+        n, lines = kw["n"], kw.get("lines") or kw["n"]
+        return 2 * n * lines * 4 + n * 4, 0.0
     if name == "c3_gemm_bias_gelu":
         m, n, k = kw["m"], kw["n"], kw["kdim"]
         return (m * k + k * n + m * n + n) * 2, 2.0 * m * n * k
@@ -89,6 +83,21 @@ def measured_peaks():
         p = json.load(open(path))
         return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def ncu_traffic(name: str, family: str):
+    """(bytes per launch, source) from the table above, or (None, why) when the kernel changed since the capture."""
+    entry = NCU_TRAFFIC.get((name, family))
+    if entry is None:
+        return None, "no capture for this kernel"
+    nbytes, summary, source, sha = entry
+    try:
+        now = hashlib.sha256(open(os.path.join(ROOT, source), "rb").read()).hexdigest()[:16]
+    except OSError:
+        return None, f"{source} missing"
+    if now != sha:
+        return None, f"{source} changed since the capture summarised in {summary}"
+    return nbytes, summary
 
 
 class ClockSampler:
@@ -124,56 +133,20 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
 
 
-def reference_arm(args, name, builder, kw):
-    """The reference's own CPU path for the workload (kurumi's view-fused evaluator; it falls back to
-    the interpreter for graphs outside its f32 fused path, as the reference does), restated in
-    oracle/ because no Rust toolchain exists here. Single thread: the reference is single-threaded
-    by construction. Each step evaluates a bounded sample of the workload."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    olib = api.Library(build.ORACLE_LIB if os.path.exists(build.ORACLE_LIB) else build.build_oracle())
-    cpu = api.Backend(olib, 65)
-    skw, frac, what = cpu_sample(name, kw)
-    g = api.Graph(olib)
-    root, gens = builder(g, **skw)
-    gen = api.Backend(olib, 0)
-    feeds = api.Feeds(olib)
-    for node, mk in gens.items():
-        h = api.Graph(olib)
-        feeds.set(node, gen.eval(h, mk(h)))
-    for _ in range(args.warmup):
-        cpu.eval_with(g, root, feeds)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu.eval_with(g, root, feeds)
-    dt = (time.perf_counter() - t0) / args.steps
-    nbytes, flops = algorithmic_work(name, skw)
-    kind = WORKLOADS[name][2]
-    value = nbytes / dt / 1e9 if kind == "hbm" else flops / dt / 1e12
-    unit = "GB/s" if kind == "hbm" else "TFLOP/s"
-    line = {"impl": "reference", "metric": metric_name(name), "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_of(name), "data": "synthetic",
-            "config": {"workload": name, **kw, "sample": what},
-            "cpu_baseline": {"value": value, "unit": unit, "cores": 1, "kind": "port", "sample": what},
-            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    emit(line)
-
-
 def cpu_sample(name, kw):
-    """A bounded slice of the workload for the CPU baseline: (sizes, fraction of the full work, description)."""
+    """The workload, or a bounded slice of it, for the CPU evaluator: (sizes, description). Configurations 1 and 2 run at
+    full size; the contractions and attention take minutes on one core, so a stated slice of their rows / heads is timed."""
     if name == "c2_transposed_softmax":
-        n = min(kw["n"], 2048)
-        return dict(n=n), (n / kw["n"]) ** 2, f"[{n},{n}] instance of the same graph (work is linear in elements)"
+        return dict(kw), "full size"
     if name == "c1_fused_reduce":
-        return dict(kw), 1.0, "full size"
+        return dict(kw), "full size"
     if name == "c3_gemm_bias_gelu":
         m = min(kw["m"], 64)
-        return dict(m=m, n=kw["n"], kdim=kw["kdim"]), m / kw["m"], f"{m} of {kw['m']} rows of A"
+        return dict(m=m, n=kw["n"], kdim=kw["kdim"]), f"{m} of {kw['m']} rows of A"
     if name == "c4_causal_attention":
-        return dict(batch=1, heads=1, seq=min(kw["seq"], 512), dh=kw["dh"]), None, "1 head at seq 512"
-    m = min(kw["m"], 32)
-    return dict(m=m, kdim=kw["kdim"], n=kw["n"], amp=False), m / kw["m"], f"{m} of {kw['m']} rows of X"
+        return dict(batch=1, heads=1, seq=min(kw["seq"], 512), dh=kw["dh"]), "1 head at seq 512"
+    m, n = min(kw["m"], 256), min(kw["n"], 1792)   # few rows against all of W would time the widening of W, not the contraction
+    return dict(m=m, kdim=kw["kdim"], n=n, amp=False), f"{m} of {kw['m']} rows of X against {n} of {kw['n']} output channels"
 
 
 def metric_name(name):
@@ -182,6 +155,72 @@ def metric_name(name):
 
 def dtype_of(name):
     return {"c1_fused_reduce": "f32", "c2_transposed_softmax": "f32", "c3_gemm_bias_gelu": "bf16", "c4_causal_attention": "bf16", "c5_fp8_weight_gemm": "f8e4m3"}[name]
+
+
+def unit_of(name):
+    return "GB/s" if WORKLOADS[name][2] == "hbm" else "TFLOP/s"
+
+
+def rate(name, nbytes, flops, seconds):
+    return nbytes / seconds / 1e9 if WORKLOADS[name][2] == "hbm" else flops / seconds / 1e12
+
+
+def cpu_evaluator(name, kw):
+    """kurumi's own CPU path for the workload (the view-fused evaluator; it falls back to the interpreter for graphs
+    outside its f32 fused path, as the reference does), restated in oracle/ because no Rust toolchain exists here.
+    Single thread: the reference is single-threaded by construction. Returns (evaluate(), sample sizes, description)."""
+    olib = api.Library(build.ORACLE_LIB if os.path.exists(build.ORACLE_LIB) else build.build_oracle())
+    cpu = api.Backend(olib, 65)
+    skw, what = cpu_sample(name, kw)
+    g = api.Graph(olib)
+    root, gens = WORKLOADS[name][0](g, **skw)
+    # inputs of the configuration's shapes, dtypes and spreads, drawn with numpy: the evaluator's time does not depend on
+    # the values, and recording the seeded draw through the CPU interpreter would take longer than the measurement
+    rng = np.random.default_rng(0)
+    feeds = api.Feeds(olib)
+    for node in gens:
+        shape, dt = g.shape(node), g.dtype(node)
+        if dt == api.F8E4M3:
+            feeds.set(node, rng.integers(0, 0x78, shape, dtype=np.uint8) | (rng.integers(0, 2, shape, dtype=np.uint8) << 7), dt)
+        elif dt == api.BF16:
+            feeds.set(node, api.f32_to_bf16(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.05 if name != "c4_causal_attention" else 1.0)), dt)
+        else:
+            feeds.set(node, rng.standard_normal(shape, dtype=np.float32) * np.float32(2.0 if name == "c2_transposed_softmax" else 0.5), dt)
+    return (lambda: cpu.eval_with(g, root, feeds)), skw, what
+
+
+def reference_arm(args, name, kw):
+    """`--impl reference`: the CPU evaluator timed on this box's host, `steps` evaluations after `warmup`."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    evaluate, skw, what = cpu_evaluator(name, kw)
+    for _ in range(args.warmup):
+        evaluate()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        evaluate()
+    dt = (time.perf_counter() - t0) / args.steps
+    nbytes, flops = algorithmic_work(name, skw)
+    value, unit = rate(name, nbytes, flops, dt), unit_of(name)
+    emit({"impl": "reference", "metric": metric_name(name), "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+          "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype_of(name), "data": "synthetic",
+          "config": {"workload": name, **kw, "sample": what},
+          "cpu_baseline": {"value": value, "unit": unit, "cores": 1, "kind": "port", "sample": what},
+          "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+
+
+def cpu_baseline(name, kw, budget_s):
+    """The same evaluator timed beside the GPU number for about `budget_s` seconds (one evaluation at least)."""
+    evaluate, skw, what = cpu_evaluator(name, kw)
+    evaluate()
+    reps, t0 = 0, time.perf_counter()
+    while reps < 1 or (time.perf_counter() - t0 < budget_s and reps < 20):
+        evaluate()
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    nbytes, flops = algorithmic_work(name, skw)
+    return {"value": rate(name, nbytes, flops, dt), "unit": unit_of(name), "cores": 1, "kind": "port", "sample": what + f"; {reps} evaluations, {dt * 1e3:.1f} ms each",
+            "host_cpus": os.cpu_count()}
 
 
 _RESULT_FD = None
@@ -197,6 +236,292 @@ def emit(line: dict):
         os.write(_RESULT_FD, data)
 
 
+class Session:
+    """One rank: its GPU, the backend, the torch view of the backend's stream, and the process group when N > 1."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.rank, self.world, self.local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local)
+        if self.world > 1:
+            os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the JSON line only
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+        self.lib = api.Library(build.LIB)
+        self.gpu = api.CudaBackend(self.lib, self.local)
+        self.stream = torch.cuda.ExternalStream(self.gpu.stream, device=self.local)
+        if self.world > 1:   # the library's own communicator, for the assembly column
+            box = [self.gpu.comm_unique_id() if self.rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            self.gpu.comm_init(box[0], self.rank, self.world)
+
+    def barrier(self):
+        self.gpu.sync()
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+
+    def max_over_ranks(self, v: float) -> float:
+        t = self.torch.tensor([v], device=f"cuda:{self.local}", dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self):
+        if self.world > 1:
+            self.gpu.comm_free()
+            self.dist.destroy_process_group()
+
+
+def device_slice(s: Session, t, axis: int, index: int, parts: int):
+    """Slice `index` of `parts` along `axis` of a device tensor, as a new device tensor."""
+    step = t.shape[axis] // parts
+    g = api.Graph(s.lib)
+    x = g.input(list(t.shape), t.dtype)
+    ranges = [(0, d) for d in t.shape]
+    ranges[axis] = (index * step, (index + 1) * step)
+    out = s.gpu.eval_device(g, [g.slice(x, ranges)], None, {x: t})[0]
+    s.gpu.sync()
+    s.gpu.release_graph(g)
+    return out
+
+
+def setup(s: Session, name: str, kw: dict):
+    """The workload graph (its row shard when N > 1) and device-resident seeded inputs, in several copies when small."""
+    builder = WORKLOADS[name][0]
+    g_full = api.Graph(s.lib)
+    root_full, gens = builder(g_full, **kw)
+    if s.world > 1:
+        g, root, inputs = api.row_split(g_full, root_full, s.world)
+    else:
+        g, root, inputs = g_full, root_full, [(n, n, None) for n in gens]
+    in_bytes = 0
+    for orig, part, axis in inputs:
+        in_bytes += int(np.prod(g.shape(part))) * api.WIDTH[g.dtype(part)]
+    # Inputs smaller than about three L2s (126 MB) are kept in several copies that the steps rotate through, so that a
+    # step never finds its inputs in L2 from the step before.
+    n_sets = max(1, min(8, int(np.ceil(3 * 126e6 / max(in_bytes, 1)))))
+    first = {}
+    for orig, part, axis in inputs:   # the seeded draw, generated on the device; a rank keeps its slice of it
+        h = api.Graph(s.lib)
+        full = s.gpu.eval_device(h, [gens[orig](h)])[0]
+        s.gpu.sync()
+        s.gpu.release_graph(h)
+        if axis is None:
+            first[part] = full
+        else:
+            first[part] = device_slice(s, full, axis, s.rank, s.world)
+            full.free()
+    sets = [first]
+    for _ in range(n_sets - 1):       # further copies of the same values at other addresses
+        cp = {}
+        for part, t in first.items():
+            gi = api.Graph(s.lib)
+            x = gi.input(list(t.shape), t.dtype)
+            cp[part] = s.gpu.eval_device(gi, [gi.slice(x, [(0, d) for d in t.shape])], None, {x: t})[0]   # a root that is a bare input is copied out
+            s.gpu.sync()
+            s.gpu.release_graph(gi)
+        sets.append(cp)
+    return {"g": g, "root": root, "g_full": g_full, "inputs": inputs, "sets": sets, "in_bytes": in_bytes, "n_sets": n_sets}
+
+
+def teardown(s: Session, w: dict):
+    s.gpu.sync()
+    for st in w["sets"]:
+        for t in st.values():
+            t.free()
+    s.gpu.release_graph(w["g"])
+
+
+def measure(s: Session, name: str, kw: dict, steps: int, warmup: int, e2e_steps: int, cpu_budget: float, sample_clocks: bool):
+    """Device-timed value, roofline of the dominant kernel, end-to-end value through the drop-in call, assembly column
+    (N > 1) and the CPU evaluator's figure for one workload."""
+    torch = s.torch
+    kind = WORKLOADS[name][2]
+    nbytes, flops = algorithmic_work(name, kw)     # of the WHOLE problem, whatever N
+    w = setup(s, name, kw)
+    g, root, sets, n_sets = w["g"], w["root"], w["sets"], w["n_sets"]
+    counter = [0]
+
+    def step():
+        counter[0] += 1
+        return s.gpu.eval_device(g, [root], None, sets[counter[0] % n_sets])[0]
+
+    sampler = ClockSampler(s.local) if (sample_clocks and s.rank == 0) else None
+    if sampler:
+        sampler.start()
+    for _ in range(warmup):
+        step().free()
+    s.barrier()
+    launches0 = s.gpu.stats()["launches"]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(s.stream)
+    for _ in range(steps):
+        step().free()
+    e1.record(s.stream)
+    s.barrier()
+    ms_local = e0.elapsed_time(e1)
+    launches = s.gpu.stats()["launches"] - launches0
+    # nvidia-smi needs ~100 ms per sample: when the timed region is shorter than that, keep the same load running
+    # (untimed) so that the clock record still describes the kernel under load
+    clocks = None
+    if sampler:
+        t_sustain = time.perf_counter()
+        while ms_local < 1500 and time.perf_counter() - t_sustain < 1.2:
+            for _ in range(20):
+                step().free()
+            s.gpu.sync()
+        clocks = sampler.stop()
+        clocks["window"] = "warm-up + timed steps" + (" + 1.2 s of the same steps, untimed" if ms_local < 1500 else "")
+    s.barrier()
+    ms = s.max_over_ranks(ms_local)
+    per_step_s = ms / 1e3 / steps
+    res = {"value": rate(name, nbytes, flops, per_step_s), "unit": unit_of(name), "ms_per_step": ms / steps, "gpu_launches": int(launches), "clocks": clocks,
+           "l2": f"steps rotate through {n_sets} copies of the inputs ({w['in_bytes'] * n_sets / 1e6:.0f} MB per rank in all, L2 is 126 MB): no step finds its inputs cached"}
+
+    # dominant kernel: average launch duration from CUDA events around every launch on the backend's stream
+    s.gpu.profile(True)
+    n_prof = min(steps, 20)
+    for _ in range(n_prof):
+        step().free()
+    s.gpu.sync()
+    prof = s.gpu.take_profile()
+    s.gpu.profile(False)
+    peaks = measured_peaks()
+    if prof:
+        fam, p = max(prof.items(), key=lambda kv: kv[1]["ms"])
+        avg_s = p["ms"] / 1e3 / p["launches"]
+        duration_source = "CUDA events around each launch (a pass of its own after the timed region)"
+        if len(prof) == 1 and p["launches"] == n_prof:
+            # the step IS this one kernel: its average duration over the timed region (events bracket the K back-to-back
+            # launches on the launching stream) is the timed region / K; launch gaps count against it
+            avg_s = ms_local / 1e3 / steps
+            duration_source = "timed region / launches (one launch per step; CUDA events bracket the K launches)"
+        traffic, traffic_source = ncu_traffic(name, fam) if s.world == 1 else (None, "captured at one GPU only")
+        if kind == "hbm":
+            ach, peak, peak_source = (p["algo_bytes"] / p["launches"]) / avg_s / 1e9, peaks["hbm_gbs"], peaks["source"]
+        else:
+            ach, peak, peak_source = (p["flops"] / p["launches"]) / avg_s / 1e12, peaks["bf16_tflops"], peaks["source"] + " (bf16 burst)"
+        res["roofline"] = {"bound": kind, "kernel": fam, "achieved": ach, "peak": peak, "unit": unit_of(name), "frac": ach / peak, "traffic": traffic, "traffic_source": traffic_source,
+                           "avg_launch_us": avg_s * 1e6, "duration_source": duration_source, "peak_source": peak_source, "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values()),
+                           "per": "this rank's launch (its shard of the problem)" if s.world > 1 else "launch"}
+        res["kernel_times"] = {k: {"launches": v["launches"], "avg_us": v["ms"] * 1e3 / v["launches"]} for k, v in prof.items()}
+
+    w["launches_per_step"] = max(1, int(launches) // steps)
+    if e2e_steps > 0:
+        res["e2e"] = measure_e2e(s, name, nbytes, flops, w, e2e_steps)
+    if s.world > 1:
+        res["assembly"] = measure_assembly(s, step)
+    if cpu_budget > 0 and s.rank == 0 and s.world == 1:
+        res["cpu_baseline"] = cpu_baseline(name, kw, cpu_budget)
+    teardown(s, w)
+    return res
+
+
+def measure_e2e(s: Session, name: str, nbytes: int, flops: float, w: dict, n_steps: int):
+    """The drop-in call with host buffers: ku_feeds_set for every input, ku_eval_with, ku_tensor_bytes into the caller's
+    buffer, every step. Host wall clock around the steps (the calls return when the result is in host memory)."""
+    g, root = w["g"], w["root"]
+    L = s.lib.lib
+    tensors = {}
+    for part, t in w["sets"][0].items():   # this rank's inputs as host tensors (ku_tensor_new copies the caller's bytes)
+        tensors[part] = api.Tensor.from_numpy(s.lib, t.numpy(), t.dtype)
+    feeds = api.Feeds(s.lib)
+    out_bytes = int(np.prod(g.shape(root))) * api.WIDTH[g.dtype(root)]
+    host_out = np.zeros(max(out_bytes, 1), np.uint8)   # the caller's result buffer, touched once
+    out_ptr = host_out.ctypes.data
+
+    def e2e_step():
+        for part, t in tensors.items():
+            L.ku_feeds_set(feeds.h, C.c_uint32(part), t.h)
+        r = s.gpu.eval_with(g, root, feeds)
+        r.copy_into(out_ptr)
+        r.free()
+
+    before = s.gpu.stats()
+    for _ in range(2):
+        e2e_step()
+    chunked = s.gpu.stats()["launches"] - before["launches"] > 2 * w["launches_per_step"]   # more launches than two one-piece evaluations
+    s.barrier()
+    t0 = time.perf_counter()
+    for _ in range(n_steps):
+        e2e_step()
+    dt_local = (time.perf_counter() - t0) / n_steps
+    s.barrier()
+    dt = s.max_over_ranks(dt_local)
+    # the result in the caller's buffer is the device-resident evaluation's
+    ref = s.gpu.eval_device(g, [root], None, w["sets"][0])[0]
+    want = ref.numpy().view(np.uint8).reshape(-1)
+    ref.free()
+    if name == "c2_transposed_softmax":   # a chunk of lines may take another softmax kernel (another summation order): the f32 band
+        same = bool(np.allclose(host_out.view(np.float32), want.view(np.float32), rtol=1e-5, atol=1e-12))
+    else:
+        same = bool(np.array_equal(host_out[:out_bytes], want))
+    h2d = int(sum(t.nbytes for t in tensors.values()))
+    for t in tensors.values():
+        t.free()
+    return {"value": rate(name, nbytes, flops, dt), "unit": unit_of(name), "h2d_bytes_per_step": h2d * s.world if s.world > 1 else h2d, "d2h_bytes_per_step": out_bytes * s.world,
+            "ms_per_step": dt * 1e3, "steps": n_steps, "timing": "host wall clock around the calls, max over ranks",
+            "method": "ku_feeds_set + ku_eval_with (host tensors in, host tensor out) + ku_tensor_bytes per step" +
+                      ("; inside ku_eval_with the evaluation streams through the device in row chunks, upload, kernels and download overlapped" if chunked else "") +
+                      ("; every rank feeds its slice of the row-wise inputs and all of the replicated ones" if s.world > 1 else ""),
+            "matches_device_resident_evaluation": same}
+
+
+def measure_assembly(s: Session, step):
+    """N > 1: gathering the ranks' output shards into one tensor on every GPU is NOT on the data path that `value`
+    times (shards stay device-resident); its cost is reported beside it."""
+    torch = s.torch
+    shard = step()
+    for _ in range(2):
+        s.gpu.all_gather_rows(shard).free()
+    s.barrier()
+    reps = 5
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record(s.stream)
+    for _ in range(reps):
+        s.gpu.all_gather_rows(shard).free()
+    a1.record(s.stream)
+    s.barrier()
+    ms = s.max_over_ranks(a0.elapsed_time(a1) / reps)
+    nb = shard.nbytes
+    shard.free()
+    return {"ms": ms, "bytes_per_rank": int(nb), "collective": "ncclAllGather of the output shards on the backend's stream (ku_cuda_all_gather_rows), CUDA events, max over ranks",
+            "in_value": False}
+
+
+def fp8_ceiling(s: Session):
+    """This repository's own fp8 GEMM kernel on a plain square e4m3 x e4m3 contraction (8192^3, bf16 result, no
+    epilogue): best of 10 launches, the method of the measured bf16 burst figure. There is no library fp8 figure in
+    MEASURED_PEAKS.json; this is the ceiling the fp8 workload is set against, beside twice the measured bf16 peak."""
+    torch = s.torch
+    n = 8192
+    g = api.Graph(s.lib)
+    a, b = g.input([n, n], api.F8E4M3), g.input([n, n], api.F8E4M3)
+    root = g.matmul(g.cast(a, api.BF16), g.cast(b, api.BF16))
+    feeds = {}
+    for node, seed in ((a, 11), (b, 12)):
+        h = api.Graph(s.lib)
+        feeds[node] = s.gpu.eval_device(h, [h.cast(h.randn([n, n], seed), api.F8E4M3)])[0]
+        s.gpu.release_graph(h)
+    for _ in range(3):
+        s.gpu.eval_device(g, [root], None, feeds)[0].free()
+    s.gpu.sync()
+    best = 1e30
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s.stream)
+        s.gpu.eval_device(g, [root], None, feeds)[0].free()
+        e1.record(s.stream)
+        s.gpu.sync()
+        best = min(best, e0.elapsed_time(e1))
+    for t in feeds.values():
+        t.free()
+    s.gpu.release_graph(g)
+    return {"tflops": 2.0 * n ** 3 / (best / 1e3) / 1e12, "us": best * 1e3, "what": "own kernel, e4m3 x e4m3 8192^3 -> bf16, no epilogue, best of 10 launches (CUDA events)"}
+
+
 def main():
     # libraries (NCCL's version banner, for one) write to file descriptor 1: keep it for the result line alone
     global _RESULT_FD
@@ -208,262 +533,54 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="kurumi_b200", choices=["kurumi_b200", "reference"])
-    ap.add_argument("--workload", default="c2_transposed_softmax", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS), help="measure this workload alone (default: configuration 2 as the headline, the other four beside it)")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (profiling captures); 1.0 = the baseline's size")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--only-headline", action="store_true", help="skip the other four configurations")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
-    name = args.workload
-    builder, kw, kind = WORKLOADS[name]
-    kw = dict(kw)
-    if args.scale != 1.0:
-        for k in kw:
-            if k not in ("dh",):
-                kw[k] = max(128, int(kw[k] * args.scale) // 128 * 128)
+    name = args.workload or HEADLINE
+
+    def sizes(nm):
+        kw = dict(WORKLOADS[nm][1])
+        if args.scale != 1.0:
+            for k in kw:
+                if k != "dh":
+                    kw[k] = max(128, int(kw[k] * args.scale) // 128 * 128)
+        return kw
+    kw = sizes(name)
     if args.impl == "reference":
-        return reference_arm(args, name, builder, kw)
+        return reference_arm(args, name, kw)
 
-    import torch
-    import torch.distributed as dist
-    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the JSON line only
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    lib = api.Library(build.LIB)
-    gpu = api.CudaBackend(lib, local)
-    stream = torch.cuda.ExternalStream(gpu.stream, device=local)
-
-    # the workload graph and its seeded inputs, generated on the device (each rank: its own shard of
-    # an N-times larger batch: the same shapes and the same seeded draw, since kernel time does not depend on the values)
-    g = api.Graph(lib)
-    root, gens = builder(g, **kw)
-    nbytes, flops = algorithmic_work(name, kw)
-    # Inputs smaller than about three L2s (126 MB) are kept in several copies that the steps rotate
-    # through, so that a step never finds its inputs in L2 from the step before.
-    in_bytes = sum(int(np.prod(g.shape(n))) * api.WIDTH[g.dtype(n)] for n in gens)
-    n_sets = max(1, min(8, int(np.ceil(3 * 126e6 / max(in_bytes, 1)))))
-    dev_sets = []
-    for _ in range(n_sets):
-        dev_in = {}
-        for node, mk in gens.items():
-            h = api.Graph(lib)
-            dev_in[node] = gpu.eval_device(h, [mk(h)])[0]
-        dev_sets.append(dev_in)
-    dev_in = dev_sets[0]
-    gpu.sync()
-    counter = [0]
-
-    def step():
-        counter[0] += 1
-        return gpu.eval_device(g, [root], None, dev_sets[counter[0] % n_sets])[0]
-
-    def barrier():
-        gpu.sync()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    for _ in range(args.warmup):
-        step().free()
-    barrier()
-    launches0 = gpu.stats()["launches"]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step().free()
-    e1.record(stream)
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches = gpu.stats()["launches"] - launches0
-    # nvidia-smi needs ~100 ms per sample: when the timed region is shorter than that, keep the same
-    # load running (untimed) so the clock record still describes the kernel under load
-    t_sustain = time.perf_counter()
-    while rank == 0 and ms < 1500 and time.perf_counter() - t_sustain < 1.5:
-        for _ in range(20):
-            step().free()
-        gpu.sync()
-    clocks = sampler.stop() if rank == 0 else None
-    if clocks is not None:
-        clocks["window"] = "warm-up + timed steps" + (" + 1.5 s of the same steps, untimed" if ms < 1500 else "")
-    barrier()
-    t = torch.tensor([ms], device=f"cuda:{local}")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    per_step_s = ms / 1e3 / args.steps
-    unit = "GB/s" if kind == "hbm" else "TFLOP/s"
-    value = world * (nbytes / per_step_s / 1e9 if kind == "hbm" else flops / per_step_s / 1e12)
-
-    # dominant kernel: average launch duration from CUDA events around every launch on the backend's stream
-    gpu.profile(True)
-    for _ in range(min(args.steps, 20)):
-        step().free()
-    gpu.sync()
-    prof = gpu.take_profile()
-    gpu.profile(False)
-    peaks = measured_peaks()
-    roofline = None
-    if prof:
-        top = max(prof.items(), key=lambda kv: kv[1]["ms"])
-        fam, p = top
-        avg_s = p["ms"] / 1e3 / p["launches"]
-        duration_source = "CUDA events around each launch (a pass of its own after the timed region)"
-        if len(prof) == 1 and p["launches"] == min(args.steps, 20):
-            # the step IS this one kernel: its average duration over the timed region (events bracket the K
-            # back-to-back launches on the launching stream) is the timed region / K; launch gaps count against it
-            avg_s = per_step_s
-            duration_source = "timed region / launches (one launch per step; CUDA events bracket the K launches)"
-        traffic = NCU_TRAFFIC.get((args.workload, fam)) if args.scale == 1.0 else None
-        if kind == "hbm":
-            ach = (p["algo_bytes"] / p["launches"]) / avg_s / 1e9
-            peak = peaks["hbm_gbs"]
-            roofline = {"bound": "hbm", "kernel": fam, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
-                        "avg_launch_us": avg_s * 1e6, "duration_source": duration_source, "peak_source": peaks["source"], "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
-        else:
-            ach = (p["flops"] / p["launches"]) / avg_s / 1e12
-            peak = peaks["bf16_tflops"]
-            roofline = {"bound": "tensor", "kernel": fam, "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": traffic,
-                        "avg_launch_us": avg_s * 1e6, "duration_source": duration_source, "peak_source": peaks["source"] + " (bf16 burst)", "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
-
-    # end to end through the C ABI with host buffers: pinned host inputs -> device, evaluate, result -> pinned host
-    e2e = None
-    if not args.no_e2e:
-        host_in = {}
-        for node, d in dev_in.items():
-            hb = torch.empty(d.nbytes, dtype=torch.uint8).pin_memory()
-            d.download_into(hb.data_ptr(), d.nbytes)
-            host_in[node] = (hb, d.shape, d.dtype)
-        out0 = step()
-        host_out = torch.empty(out0.nbytes, dtype=torch.uint8).pin_memory()
-        out_bytes, out0_shape = out0.nbytes, tuple(out0.shape)
-        out0.free()
-
-        def serial_step():
-            ups = {node: gpu.upload_ptr(hb.data_ptr(), hb.numel(), shape, dt) for node, (hb, shape, dt) in host_in.items()}
-            o = gpu.eval_device(g, [root], None, ups)[0]
-            o.download_into(host_out.data_ptr(), out_bytes)   # waits for the result
-            o.free()
-            for u in ups.values():
-                u.free()
-
-        # the same step chunk by chunk over the independent output rows, uploads, kernels and downloads overlapped
-        pipe, e2e_method = None, "one upload of every input, one evaluation, one download"
-        plan = CHUNKING.get(name)
-        if plan is not None and args.scale == 1.0:
-            try:
-                from kurumi_b200 import pipeline
-                chunks, chunk_kw, axes = plan["chunks"], plan["chunk_kw"](kw, plan["chunks"]), plan["axes"]
-                gch = api.Graph(lib)
-                root_ch, gens_ch = builder(gch, **chunk_kw)
-                inputs = [pipeline.HostInput(node_ch, host_in[node][0].data_ptr(), tuple(host_in[node][1]), host_in[node][2], axes[i])
-                          for i, (node, node_ch) in enumerate(zip(dev_in, gens_ch))]
-                out_rows = out0_shape[0]
-                pipe = pipeline.RowPipeline(gpu, gch, root_ch, inputs, host_out.data_ptr(), out_rows, out_bytes // out_rows, chunks)
-                pipe.step()   # a failure of the chunked path shows here, before anything is timed
-                e2e_method = f"{chunks} chunks of output rows; host-to-device copies, evaluations (ku_cuda_eval_device) and device-to-host copies overlapped on three streams"
-            except Exception as exc:   # the unchunked step is still a valid end-to-end measurement
-                print(f"bench: chunked end-to-end path unavailable ({exc}); timing the unchunked step", file=sys.stderr)
-                pipe = None
-        e2e_step = pipe.step if pipe is not None else serial_step
-        n_e2e = max(3, min(args.steps, 10))
-        for _ in range(2):
-            e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(n_e2e):
-            e2e_step()
-        barrier()
-        dt = (time.perf_counter() - t0) / n_e2e
-        tt = torch.tensor([dt], device=f"cuda:{local}")
-        if world > 1:
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dt = float(tt.item())
-        ev = world * (nbytes / dt / 1e9 if kind == "hbm" else flops / dt / 1e12)
-        e2e = {"value": ev, "unit": unit, "h2d_bytes_per_step": int(sum(hb.numel() for hb, _, _ in host_in.values())), "d2h_bytes_per_step": int(out_bytes),
-               "ms_per_step": dt * 1e3, "timing": "host wall clock around upload + eval + download (download waits for the device)", "steps": n_e2e,
-               "method": e2e_method}
-        if pipe is not None:   # the result of the chunked step is the result of the single evaluation
-            ref_out = step()
-            check = torch.empty(out_bytes, dtype=torch.uint8).pin_memory()
-            ref_out.download_into(check.data_ptr(), out_bytes)
-            ref_out.free()
-            e2e["matches_single_evaluation"] = bool(torch.equal(check, host_out))
-            pipe.close()
-
-    # N > 1: gathering the ranks' output shards into one tensor on every GPU is NOT on the data path that
-    # `value` times (shards stay device-resident); its cost is reported beside it
-    assembly = None
-    if world > 1:
-        from cuda.bindings import runtime as cudart
-        o = step()
-        shard = torch.empty(o.nbytes, dtype=torch.uint8, device=f"cuda:{local}")
-        gpu.sync()
-        (err,) = cudart.cudaMemcpy(shard.data_ptr(), o.ptr, o.nbytes, cudart.cudaMemcpyKind.cudaMemcpyDeviceToDevice)
-        if int(err) != 0:
-            raise RuntimeError(f"cudaMemcpy of the output shard failed: {err}")
-        o.free()
-        whole = torch.empty(world * shard.numel(), dtype=torch.uint8, device=f"cuda:{local}")
-        for _ in range(2):
-            dist.all_gather_into_tensor(whole, shard)
-        torch.cuda.synchronize()
-        dist.barrier()
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 5
-        a0.record()
-        for _ in range(reps):
-            dist.all_gather_into_tensor(whole, shard)
-        a1.record()
-        torch.cuda.synchronize()
-        at = torch.tensor([a0.elapsed_time(a1) / reps], device=f"cuda:{local}")
-        dist.all_reduce(at, op=dist.ReduceOp.MAX)
-        assembly = {"ms": float(at.item()), "bytes_per_rank": int(shard.numel()), "collective": "nccl all_gather of the output shards (torch.distributed), CUDA events, max over ranks",
-                    "in_value": False}
-        del whole, shard
-
-    cpu_base = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_base = cpu_baseline(name, builder, kw)
-
-    if rank == 0:
-        line = {"metric": metric_name(name), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_of(name),
+    s = Session()
+    head = measure(s, name, kw, args.steps, args.warmup, 0 if args.no_e2e else max(3, min(args.steps, 10)), 0 if args.no_cpu_baseline else 8.0, True)
+    others = {}
+    if args.workload is None and not args.only_headline and args.scale == 1.0:
+        for nm in WORKLOADS:
+            if nm == name:
+                continue
+            k2 = sizes(nm)
+            r = measure(s, nm, k2, max(5, min(args.steps, 20)), 3, 0 if args.no_e2e else 3, 0 if args.no_cpu_baseline else 2.0, True)
+            r["config"] = {"workload": nm, **k2}
+            r["dtype"] = dtype_of(nm)
+            r["metric"] = metric_name(nm)
+            if nm == "c5_fp8_weight_gemm" and s.world == 1:
+                r["fp8_ceiling"] = fp8_ceiling(s)
+                r["roofline"]["frac_of_fp8_ceiling"] = r["roofline"]["achieved"] / r["fp8_ceiling"]["tflops"]
+                r["roofline"]["frac_of_twice_bf16_peak"] = r["roofline"]["achieved"] / (2 * r["roofline"]["peak"])
+            others[nm] = r
+    if s.rank == 0:
+        line = {"metric": metric_name(name), "value": head["value"], "unit": head["unit"], "n_gpus": s.world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype_of(name),
                 "data": "synthetic (seeded threefry2x32 / Box-Muller, generated on device)",
-                "config": {"workload": name, **kw, "l2": f"steps rotate through {n_sets} copies of the inputs ({in_bytes * n_sets / 1e6:.0f} MB in all, L2 is 126 MB): no step finds its inputs cached",
-                           "sharding": "each rank evaluates its own shard of an N-times larger batch (same shapes); no collective on the data path"},
-                "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu_base, "assembly": assembly,
-                "kernel_times": {k: {"launches": v["launches"], "avg_us": v["ms"] * 1e3 / v["launches"]} for k, v in prof.items()}}
+                "config": {"workload": name, **kw, "l2": head["l2"],
+                           "sharding": ("one GPU" if s.world == 1 else f"the one named problem is cut into {s.world} row shards (ku_graph_row_split), rank r evaluates shard r; no collective on the data path, "
+                                        "outputs stay device-resident shards; value = whole-problem work / slowest rank's device time")},
+                "clocks": head["clocks"], "e2e": head.get("e2e"), "gpu_launches": head["gpu_launches"], "roofline": head.get("roofline"), "cpu_baseline": head.get("cpu_baseline"),
+                "assembly": head.get("assembly"), "kernel_times": head.get("kernel_times"), "workloads": others or None}
         emit(line)
-    if world > 1:
-        dist.destroy_process_group()
-
-
-def cpu_baseline(name, builder, kw):
-    """kurumi's own CPU path (view-fused evaluator with interpreter fallback, one thread), restated
-    in oracle/, timed on this box's host on a bounded sample of the same workload."""
-    olib = api.Library(build.ORACLE_LIB)
-    cpu, gen = api.Backend(olib, 65), api.Backend(olib, 0)
-    skw, frac, what = cpu_sample(name, kw)
-    g = api.Graph(olib)
-    root, gens = builder(g, **skw)
-    feeds = api.Feeds(olib)
-    for node, mk in gens.items():
-        h = api.Graph(olib)
-        feeds.set(node, gen.eval(h, mk(h)))
-    cpu.eval_with(g, root, feeds)
-    reps, t0 = 0, time.perf_counter()
-    while reps < 3 or (time.perf_counter() - t0 < 10 and reps < 20):
-        cpu.eval_with(g, root, feeds)
-        reps += 1
-    dt = (time.perf_counter() - t0) / reps
-    nbytes, flops = algorithmic_work(name, skw)
-    kind = WORKLOADS[name][2]
-    return {"value": nbytes / dt / 1e9 if kind == "hbm" else flops / dt / 1e12, "unit": "GB/s" if kind == "hbm" else "TFLOP/s", "cores": 1, "kind": "port",
-            "sample": what + f"; {reps} evaluations, {dt * 1e3:.1f} ms each", "host_cpus": os.cpu_count()}
+    s.close()
 
 
 if __name__ == "__main__":
