@@ -1,6 +1,7 @@
 """One evaluation sharded over two GPUs: each rank (a process of its own, one GPU each) evaluates the part graph of
 ku_graph_row_split on its slices, the shards are assembled with the library's NCCL all-gather
-(ku_cuda_all_gather_rows), and the assembled tensor equals the one-GPU evaluation bit for bit. Skipped when the box
+(ku_cuda_all_gather_rows), and the assembled tensor equals the one-GPU evaluation bit for bit (within the f32 band
+for the softmax, whose shard may run another kernel). Skipped when the box
 shows fewer than two GPUs."""
 import os
 import subprocess
@@ -17,6 +18,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = r'''
 import os, sys, time
 import numpy as np
+import torch   # brings the NCCL that torch ships into the process; the library uses the copy already loaded
 sys.path.insert(0, sys.argv[1])
 from kurumi_b200 import api, build, configs
 rank, world, tmp = int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
@@ -35,7 +37,15 @@ else:
             raise SystemExit("no communicator id after 60 s")
         time.sleep(0.05)
     uid = open(id_file, "rb").read()
+print("rank", rank, "has the id", flush=True)
 gpu.comm_init(uid, rank, world)
+print("rank", rank, "joined", flush=True)
+import traceback
+def _die(kind, value, tb):
+    traceback.print_exception(kind, value, tb)
+    sys.stdout.flush(); sys.stderr.flush()
+    os._exit(1)      # no teardown: the communicator's peers are still inside a collective
+sys.excepthook = _die
 cases = [(configs.fused_reduce, dict(rows=512, cols=1024)), (configs.transposed_softmax, dict(n=1024)),
          (configs.gemm_bias_gelu, dict(m=512, n=512, kdim=256)), (configs.causal_attention, dict(batch=2, heads=2, seq=256, dh=128, fused=True)),
          (configs.fp8_weight_gemm, dict(m=512, kdim=256, n=512, amp=True))]
@@ -65,8 +75,12 @@ for i, (make, kw) in enumerate(cases):
     if rank == 0:
         want = gpu.eval_device(g, [root], None, full)[0].numpy()
         assert got.shape == want.shape, (i, got.shape, want.shape)
-        assert got.tobytes() == want.tobytes(), f"case {i}: the gathered result differs from the one-GPU evaluation"
+        if make is configs.transposed_softmax:   # half the lines may take another softmax kernel (another summation order): the f32 band
+            assert np.allclose(got, want, rtol=1e-5, atol=1e-12), f"case {i}: the gathered result is outside the f32 band of the one-GPU evaluation"
+        else:
+            assert got.tobytes() == want.tobytes(), f"case {i}: the gathered result differs from the one-GPU evaluation"
     np.save(os.path.join(tmp, f"case{i}_rank{rank}.npy"), got.view(np.uint8) if got.dtype.itemsize == 1 else got)
+    print("rank", rank, "case", i, "done", flush=True)
 gpu.sync()
 gpu.comm_free()
 print("rank", rank, "ok")
@@ -78,18 +92,25 @@ def test_two_gpus_produce_one_result(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_DEBUG="WARN")
-    procs = [subprocess.Popen([sys.executable, "-c", WORKER, ROOT, str(r), "2", str(tmp_path)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    logs = [open(tmp_path / f"rank{r}.log", "w+") for r in range(2)]
+    procs = [subprocess.Popen([sys.executable, "-c", WORKER, ROOT, str(r), "2", str(tmp_path)], env=env, stdout=logs[r], stderr=subprocess.STDOUT, text=True)
              for r in range(2)]
+    deadline = time.time() + 180
+    while any(p.poll() is None for p in procs) and time.time() < deadline:
+        if any(p.poll() not in (None, 0) for p in procs):   # a rank failed: its peers would wait for it in the next collective
+            break
+        time.sleep(0.2)
+    late = [r for r, p in enumerate(procs) if p.poll() is None]
+    for r in late:          # the exact processes started above
+        procs[r].kill()
+        procs[r].wait()
     outs = []
-    deadline = time.time() + 600
-    for p in procs:
-        try:
-            o, _ = p.communicate(timeout=max(1, deadline - time.time()))
-        except subprocess.TimeoutExpired:
-            for q in procs:
-                q.kill()
-            raise
-        outs.append(o)
+    for f in logs:
+        f.seek(0)
+        outs.append(f.read())
+        f.close()
+    failed = [r for r, p in enumerate(procs) if r not in late and p.returncode != 0]
+    assert not failed and not late, f"ranks {failed} failed, ranks {late} were stopped:\n" + "\n----\n".join(o[-2000:] for o in outs)
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {r} failed:\n{o[-3000:]}"
     for i in range(5):   # every rank holds the same assembled tensor
