@@ -191,6 +191,15 @@ uint32_t ku_runnable_entry_input_role(const KuRunnable *h, size_t i, size_t j);
 size_t ku_runnable_entry_input_name(const KuRunnable *h, size_t i, size_t j, uint8_t *out, size_t cap);
 void ku_runnable_free(KuRunnable *h);
 
+/* plan replay, kurumi.h:455-458 (kurumi/src/capi/eval.rs:152-182): compile once, run per feeds; constants are never
+ * re-copied. The reference compiles for its f32 fused CPU path and returns NULL off it; this library compiles the
+ * device program (kernels generated and built ahead of the first run) on a CUDA backend of its own on device 0,
+ * shared by all plans, and returns NULL only for a graph no kernel can evaluate. ku_plan_run takes the same graph. */
+typedef struct KuPlan KuPlan;
+KuPlan *ku_plan_compile(const KuGraph *g, KuNode node);
+KuTensor *ku_plan_run(const KuPlan *p, const KuGraph *g, const KuFeeds *feeds);
+void ku_plan_free(KuPlan *p);
+
 /* feeds, kurumi.h:461-463 */
 KuFeeds *ku_feeds_new(void);
 void ku_feeds_free(KuFeeds *f);

@@ -578,6 +578,29 @@ class CudaBackend(Backend):
         return res
 
 
+class Plan:
+    """ku_plan_compile / ku_plan_run / ku_plan_free: compile once, replay with new feeds."""
+
+    def __init__(self, g: Graph, node: int):
+        L = g.lib.lib
+        L.ku_plan_compile.restype = C.c_void_p
+        L.ku_plan_run.restype = C.c_void_p
+        h = L.ku_plan_compile(g.h, C.c_uint32(node))
+        if not h:
+            raise Error(g.lib.last_error() or "ku_plan_compile failed")
+        self.g, self.h = g, C.c_void_p(h)
+
+    def run(self, feeds: Feeds, graph: Graph | None = None) -> Tensor:
+        g = graph or self.g
+        return Tensor(g.lib, g.lib.lib.ku_plan_run(self.h, g.h, feeds.h))
+
+    def __del__(self):
+        try:
+            self.g.lib.lib.ku_plan_free(self.h)
+        except Exception:
+            pass
+
+
 def row_split(g: Graph, root: int, parts: int):
     """(part graph, part root, [(original input node, part input node, axis or None)]) of core/split.h; raises Error
     with the reason when the evaluation does not separate by rows."""

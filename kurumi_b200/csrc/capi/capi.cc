@@ -335,6 +335,26 @@ size_t ku_runnable_entry_input_name(const KuRunnable* h, size_t i, size_t j, uin
 }
 void ku_runnable_free(KuRunnable* h) { delete h; }
 
+// ---- plan replay (kurumi/src/capi/eval.rs:152-182, kurumi_core/src/realize/plan.rs:13-58) ----------------------
+KuPlan* ku_plan_compile(const KuGraph* g, KuNode node) {
+  if (!g) { set_err("ku_plan_compile: null graph handle"); return nullptr; }
+  return guard<KuPlan*>(nullptr, [&]() -> KuPlan* {
+    (void)g->g.node(node);
+    std::shared_ptr<ku::Backend> b = ku::plan_backend(g->g, node);
+    if (!b) return nullptr;
+    return new KuPlan{std::move(b), g->g.id(), node};
+  });
+}
+KuTensor* ku_plan_run(const KuPlan* p, const KuGraph* g, const KuFeeds* feeds) {
+  if (!p || !g || !feeds) { set_err("ku_plan_run: null plan/graph/feeds handle"); return nullptr; }
+  return guard<KuTensor*>(nullptr, [&]() -> KuTensor* {
+    if (g->g.id() != p->graph_id) throw Error("ku_plan_run: the plan was compiled from another graph");
+    Tensor t = p->backend->eval_with(g->g, p->node, feeds->f);
+    return new KuTensor{std::make_shared<const Tensor>(std::move(t))};
+  });
+}
+void ku_plan_free(KuPlan* p) { delete p; }
+
 // ---- row splitting (core/split.h) ---------------------------------------------------------------
 KuGraph* ku_graph_row_split(const KuGraph* g, KuNode root, size_t parts, KuNode* part_root, KuNode* orig_inputs, KuNode* part_inputs, int32_t* axes, size_t cap, size_t* n_inputs) {
   if (!g) { set_err("ku_graph_row_split: null graph handle"); return nullptr; }

@@ -13,6 +13,7 @@ struct KuTensor { ku::TensorPtr t; };
 struct KuFeeds { ku::Feeds f; };
 struct KuBackend { std::unique_ptr<ku::Backend> b; };
 struct KuRunnable { ku::Runnable r; };
+struct KuPlan { std::shared_ptr<ku::Backend> backend; uint64_t graph_id; ku::NodeId node; };
 
 namespace ku {
 void set_err(const std::string& msg);

@@ -262,5 +262,9 @@ class Backend {
 
 // Each library that embeds the C ABI defines this (the CUDA library accepts only KU_CUDA).
 std::unique_ptr<Backend> make_backend(uint32_t kind);
+// ... and this: the backend behind ku_plan_compile, which takes no backend argument (kurumi/src/capi/eval.rs:152-168):
+// compiles whatever can be compiled ahead of the first run and returns the backend that replays it, or null (with the
+// reason in the last-error string) when `root` is off this library's compile-once path.
+std::shared_ptr<Backend> plan_backend(const Graph& g, NodeId root);
 
 }  // namespace ku

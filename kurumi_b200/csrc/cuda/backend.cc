@@ -1,6 +1,7 @@
 #include "backend.h"
 
 #include <cstring>
+#include <mutex>
 
 #include "../capi/handles.h"
 #include "hostmem.h"
@@ -272,5 +273,16 @@ std::unique_ptr<Backend> make_backend(uint32_t kind) {
   }
   set_err("ku_backend_new: unknown kind " + std::to_string(kind));
   return nullptr;
+}
+// ku_plan_compile: one CUDA backend on device 0 serves every plan of the process; the program for `root` is compiled now
+// (kernel generation and NVRTC), so that ku_plan_run only binds buffers and replays launches.
+std::shared_ptr<Backend> plan_backend(const Graph& g, NodeId root) {
+  static std::mutex mu;
+  static std::weak_ptr<cu::CudaBackend> shared;
+  std::lock_guard<std::mutex> lk(mu);
+  std::shared_ptr<cu::CudaBackend> b = shared.lock();
+  if (!b) { b = std::make_shared<cu::CudaBackend>(0); shared = b; }
+  b->prepare(g, root);
+  return b;
 }
 }  // namespace ku

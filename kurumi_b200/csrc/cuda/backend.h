@@ -42,6 +42,9 @@ class CudaBackend : public Backend {
   void comm_free() { comm_.reset(); }
   DevTensor* all_gather_rows(const DevTensor& shard);
 
+  // Compile the program for one root ahead of its first evaluation (ku_plan_compile).
+  void prepare(const Graph& g, NodeId root) { rt_.make_current(); (void)program_for(g, {root}); }
+
   // Forget everything cached for a graph (compiled programs with their scratch, uploaded constants, chunk pipelines).
   void release_graph(uint64_t graph_id);
 

@@ -304,53 +304,26 @@ bool build_attention(const KernelLoader& load, DType dt, const Shape& shape, boo
   int64_t bh = 1;
   for (size_t i = 0; i + 2 < r; ++i) bh *= static_cast<int64_t>(shape[i]);
   const uint32_t fmt = dt == DType::BF16 ? 1u : 0u;
-  // Three arrangements of the same algorithm (KURUMI_ATTENTION_VARIANT = duo | twin | one; KURUMI_ATTENTION_ONE_CTA = one):
-  //   duo   one CTA per 256 queries: two query tiles share each K / V block of 128 keys, P in tensor memory (default)
-  //   twin  two CTAs of 128 queries per SM over key blocks of 64, P in tensor memory
-  //   one   one CTA of 128 queries per SM, key blocks of 128, P through shared memory
-  // duo and twin scale the block maximum instead of every score, which needs a positive scale.
-  const char* var = std::getenv("KURUMI_ATTENTION_VARIANT");
-  int variant = 2;
-  if (var && std::string(var) == "twin") variant = 1;
-  if ((var && std::string(var) == "one") || std::getenv("KURUMI_ATTENTION_ONE_CTA") || !(scale > 0.0f)) variant = 0;
-  const bool twin = variant == 1, duo = variant == 2;
-  // duo: KURUMI_ATTENTION_ISSUERS=2 gives each query tile its own MMA-issuing thread and makes the tiles' softmax warpgroups take turns
-  const int64_t issuers = (std::getenv("KURUMI_ATTENTION_ISSUERS") && std::atoi(std::getenv("KURUMI_ATTENTION_ISSUERS")) == 2) ? 2 : 1;
-  // duo: stages of the K and V rings (KURUMI_ATTENTION_STAGES=k,v, 2 or 3 each, at most 5 together at DH = 128 where a stage is 32 KB).
-  // Two each by default: 2 + 3 and 3 + 2 measured the same on the causal 4096-key configuration, the loads are not what the MMA thread waits for.
-  int64_t nks = 2, nvs = 2;
-  if (const char* e = std::getenv("KURUMI_ATTENTION_STAGES")) {
-    int a = 0, b = 0;
-    if (std::sscanf(e, "%d,%d", &a, &b) == 2 && a >= 2 && a <= 3 && b >= 2 && b <= 3 && (dh == 64 || a + b <= 5)) { nks = a; nvs = b; }
-  }
-  const int64_t tk = twin ? 64 : 128;
+  if (!(scale > 0.0f)) return false;   // the kernel scales the block maximum instead of every score
+  // K and V rings of two 32 KB stages each (DH = 128): three-stage rings measured the same on the causal 4096-key
+  // configuration, the loads are not what the MMA thread waits for
+  const int64_t nks = 2, nvs = 2, tk = 128;
   const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tk >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
   const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(dh >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
   char lit[64];
   std::snprintf(lit, sizeof(lit), "%.9gf", static_cast<double>(scale * 1.4426950408889634f));
   std::string src = device_prelude() +
                     defines({{"BH", bh}, {"S", s}, {"DH", dh}, {"CAUSAL", causal ? 1 : 0}, {"IDESC_S", static_cast<int64_t>(idesc_s)}, {"IDESC_O", static_cast<int64_t>(idesc_o)},
-                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"KU_TWIN", variant}, {"NKS", nks}, {"NVS", nvs}, {"KU_ISSUERS", issuers}, {"KU_TURNS", issuers != 2 || std::getenv("KURUMI_ATTENTION_NO_TURNS") ? 0 : (std::getenv("KURUMI_ATTENTION_STAGGER") ? 2 : 1)},
-                             {"KU_PTMEM", std::getenv("KURUMI_ATTENTION_P_SMEM") ? 0 : 1}, {"KU_PHASES", std::getenv("KURUMI_ATTENTION_PHASES") ? 1 : 0},
-                             {"KU_POLY", std::getenv("KURUMI_ATTENTION_POLY") ? std::atoi(std::getenv("KURUMI_ATTENTION_POLY")) : 0}}) +
+                             {"KU_IS_BF16", dt == DType::BF16 ? 1 : 0}, {"NKS", nks}, {"NVS", nvs}}) +
                     "#define SCALE_LOG2E " + lit + "\n" + kSrc_attention_tc;
   out->name = "attention_tc";
-  out->kernel = load(src, duo ? "ku_attention_tc_duo" : twin ? "ku_attention_tc_twin" : "ku_attention_tc", true);
-  out->grid[0] = static_cast<unsigned>(duo ? (s + 255) / 256 : (s + 127) / 128);
+  out->kernel = load(src, "ku_attention_tc_duo", true);
+  out->grid[0] = static_cast<unsigned>((s + 255) / 256);
   out->grid[1] = static_cast<unsigned>(bh);
   const int64_t tile = 128 * 128 * (dh / 64);
-  if (duo) {
-    out->block[0] = issuers == 2 ? 352 : 320;   // TMA warp, MMA warp (of tile 0), a softmax warpgroup per query tile[, MMA warp of tile 1]
-    // two Q tiles, two K and two V stages, barriers; at least 120 KB so that an SM (512 columns of tensor memory) holds one CTA
-    out->smem = static_cast<unsigned>(std::max<int64_t>((2 + nks + nvs) * tile + 256, 120 * 1024));
-  } else if (twin) {
-    out->block[0] = 192;   // TMA warp, MMA warp, 4 softmax warps
-    // Q, two K and two V stages of 64 keys, P, barriers; at least 80 KB so that no third CTA (which would wait for tensor memory) joins an SM
-    out->smem = static_cast<unsigned>(std::max<int64_t>(tile + 4 * (tile / 2) + 128 * 128 + 128, 80 * 1024));
-  } else {
-    out->block[0] = 320;   // TMA warp, MMA warp, 8 softmax warps
-    out->smem = static_cast<unsigned>(std::max<int64_t>(5 * tile + 128 * 128 * 2 + 1024, 120 * 1024));
-  }
+  out->block[0] = 320;   // TMA warp, MMA warp, a softmax warpgroup per query tile
+  // two Q tiles, two K and two V stages, barriers; at least 120 KB so that an SM (512 columns of tensor memory) holds one CTA
+  out->smem = static_cast<unsigned>(std::max<int64_t>((2 + nks + nvs) * tile + 256, 120 * 1024));
   for (int slot = -1; slot >= -3; --slot) {
     Arg a;
     a.kind = Arg::Tmap;

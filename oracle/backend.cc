@@ -36,6 +36,11 @@ std::unique_ptr<Backend> make_backend(uint32_t kind) {
     default: set_err("ku_backend_new: unknown kind " + std::to_string(kind)); return nullptr;
   }
 }
+// kurumi/src/capi/eval.rs:152-168: NULL off the f32 fused path
+std::shared_ptr<Backend> plan_backend(const Graph& g, NodeId root) {
+  if (!ko::plan_supported(g, root)) { set_err("ku_plan_compile: graph is not on the f32 fused plan path"); return nullptr; }
+  return std::make_shared<Realize>();
+}
 }  // namespace ku
 
 extern "C" {

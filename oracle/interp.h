@@ -29,5 +29,7 @@ std::vector<ku::Tensor> interpret_many(const ku::Graph& g, const std::vector<ku:
 // interpreter when the graph leaves the fused path. `kernels` (optional) receives the number of
 // passes over data, or -1 when the interpreter ran (realize/eval.rs:49-56).
 ku::Tensor force(const ku::Graph& g, ku::NodeId id, const ku::Feeds& feeds, long* kernels);
+// kurumi_core/src/realize/plan.rs:21-27: whether `root` can be compiled into a replayable plan (f32, fused ops, Inputs allowed).
+bool plan_supported(const ku::Graph& g, ku::NodeId root);
 
 }  // namespace ko

@@ -303,6 +303,8 @@ Buf buf_of(const Tensor& t) {
 
 }  // namespace
 
+bool plan_supported(const Graph& g, NodeId root) { return fused_supported(g, root, true); }
+
 Tensor force(const Graph& g, NodeId root, const Feeds& feeds, long* kernels) {
   if (!fused_supported(g, root, !feeds.empty())) {
     if (kernels) *kernels = -1;

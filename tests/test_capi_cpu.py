@@ -97,3 +97,27 @@ def test_input_generators_compile(cuda_lib):
     h = api.Graph(cuda_lib)
     roots = [gen(h) for gen in gens.values()]
     assert api.compile_check(cuda_lib, h, roots)
+
+
+def test_plan_compile_and_replay(oracle_lib, cpu):
+    """ku_plan_compile / ku_plan_run (kurumi/src/capi/eval.rs:152-182): a plan replays with fresh feeds and equals
+    ku_eval_with; off the f32 fused path the reference returns NULL with a message, and so does the CPU oracle."""
+    import numpy as np
+    from kurumi_b200 import api
+    g = api.Graph(oracle_lib)
+    x, y = g.input([4, 6], api.F32), g.input([4, 6], api.F32)
+    root = g.sum(g.relu(g.add(g.mul(x, y), g.mul(g.scalar(x, 0.5), x))), 1)
+    plan = api.Plan(g, root)
+    rng = np.random.default_rng(2)
+    for _ in range(2):
+        xv, yv = rng.standard_normal((4, 6)).astype(np.float32), rng.standard_normal((4, 6)).astype(np.float32)
+        f = api.Feeds(oracle_lib).set(x, xv).set(y, yv)
+        assert np.array_equal(plan.run(f).numpy(), cpu.eval_with(g, root, f).numpy())
+    with pytest.raises(api.Error, match="not on the f32 fused plan path"):
+        api.Plan(g, g.softmax(x, 1))
+    other = api.Graph(oracle_lib)
+    other.input([4, 6], api.F32)
+    with pytest.raises(api.Error, match="another graph"):
+        plan.run(api.Feeds(oracle_lib), other)
+    with pytest.raises(api.Error):
+        api.Plan(g, 10 ** 6)

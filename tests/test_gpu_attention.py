@@ -34,19 +34,6 @@ def test_fused_attention_matches_oracle(oracle_lib, cuda_lib, cpu, cpu64, gpu, s
         assert np.array_equal(got[..., 0, :], vv[..., 0, :])
 
 
-@pytest.mark.parametrize("variant", ["duo", "twin", "one"])
-def test_every_arrangement_of_the_kernel(oracle_lib, cuda_lib, cpu64, gpu, monkeypatch, variant):
-    """The three arrangements (two query tiles per CTA, two CTAs per SM, one CTA per SM) compute the same attention."""
-    monkeypatch.setenv("KURUMI_ATTENTION_VARIANT", variant)
-    rng = np.random.default_rng(43)
-    for shape, causal in (((2, 2, 900, 128), True), ((1, 3, 520, 64), False), ((1, 1, 257, 128), True)):
-        p = Pair(oracle_lib, cuda_lib)
-        q, k, v = (p.feed(shape, api.BF16, bf16(rng, shape, 2.0)) for _ in range(3))
-        out = p.sdpa_fused(q, k, v, causal)
-        w, c, dts = p.run(cpu64, gpu, [out])
-        util.assert_band(w[0], util.to_f64(c[0], dts[0]), 2e-2, 2.0 ** -8, f"{variant} {shape}")
-
-
 def test_decomposed_attention_and_auto_selection(oracle_lib, cuda_lib, cpu, cpu64, gpu):
     rng = np.random.default_rng(41)
     for tag, mk in ((api.F32, lambda s: rng.standard_normal(s).astype(np.float32)), (api.BF16, lambda s: bf16(rng, s))):

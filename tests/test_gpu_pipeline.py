@@ -73,3 +73,24 @@ def test_missing_and_misshapen_feeds_fail_before_anything_is_queued(cuda_lib, gp
     with pytest.raises(api.Error, match="has shape"):
         gpu.eval_with(g, root, api.Feeds(cuda_lib).set(x, ok).set(y, np.zeros((2048, 1024), np.float32)))
     assert np.array_equal(gpu.eval_with(g, root, api.Feeds(cuda_lib).set(x, ok).set(y, ok)).numpy(), np.zeros(2048, np.float32))
+
+
+def test_plan_compile_and_replay_on_the_device(cuda_lib, gpu):
+    """ku_plan_compile builds the device program ahead of the first run; ku_plan_run replays it with fresh feeds and
+    equals ku_eval_with. A graph off the reference's f32 fused path (a softmax) compiles here too."""
+    rng = np.random.default_rng(8)
+    g = api.Graph(cuda_lib)
+    root, gens = configs.fused_reduce(g, rows=96, cols=512)
+    x, y = list(gens)
+    plan = api.Plan(g, root)
+    for _ in range(2):
+        xv, yv = rng.uniform(-1, 1, (96, 512)).astype(np.float32), rng.uniform(-1, 1, (96, 512)).astype(np.float32)
+        f = api.Feeds(cuda_lib).set(x, xv).set(y, yv)
+        assert np.array_equal(plan.run(f).numpy(), gpu.eval_with(g, root, f).numpy())
+    sm = g.softmax(g.mul(x, y), 1)
+    p2 = api.Plan(g, sm)
+    xv = rng.standard_normal((96, 512)).astype(np.float32)
+    out = p2.run(api.Feeds(cuda_lib).set(x, xv).set(y, xv)).numpy()
+    assert np.abs(out.sum(axis=1) - 1).max() < 1e-5
+    with pytest.raises(api.Error, match="missing feed"):
+        plan.run(api.Feeds(cuda_lib).set(x, xv))
