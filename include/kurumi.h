@@ -98,6 +98,15 @@ KuNode ku_mean(KuGraph *g, KuNode x, size_t axis);
 KuNode ku_reduce_max(KuGraph *g, KuNode x, size_t axis);
 KuNode ku_reduce_min(KuGraph *g, KuNode x, size_t axis);
 KuNode ku_softmax(KuGraph *g, KuNode x, size_t axis);
+/* indexing along one axis, kurumi.h:245-253. Gathers clamp out-of-range indices, scatters drop them; updates fold into a
+ * copy of the operand in index order; scatter combine: 0 = set, 1 = add, 2 = max, 3 = min. sort = gather_along(x, argsort(x)). */
+KuNode ku_gather(KuGraph *g, KuNode x, KuNode idx, size_t axis);
+KuNode ku_gather_along(KuGraph *g, KuNode x, KuNode idx, size_t axis);
+KuNode ku_take_along_dim(KuGraph *g, KuNode x, KuNode idx, size_t axis);
+KuNode ku_sort(KuGraph *g, KuNode x, size_t axis, uint32_t descending);
+KuNode ku_argsort(KuGraph *g, KuNode x, size_t axis, uint32_t descending);
+KuNode ku_scatter(KuGraph *g, KuNode operand, KuNode indices, KuNode updates, size_t axis, uint32_t combine);
+KuNode ku_scatter_along(KuGraph *g, KuNode operand, KuNode indices, KuNode updates, size_t axis, uint32_t combine);
 KuNode ku_argmax(KuGraph *g, KuNode x, size_t axis); /* kurumi.h:193-194: I64 index of the first maximum / minimum */
 KuNode ku_argmin(KuGraph *g, KuNode x, size_t axis);
 KuNode ku_rmsnorm(KuGraph *g, KuNode x, size_t axis, float eps); /* kurumi.h:302 */

@@ -228,6 +228,24 @@ class Graph:
         s, r = _sz(a.shape)
         return self._n("ku_constant", C.c_uint32(dtype), a.ctypes.data_as(C.c_void_p), C.c_size_t(a.nbytes), s, C.c_size_t(r))
 
+    def gather(self, x: int, idx: int, axis: int) -> int:
+        return self._n("ku_gather", C.c_uint32(x), C.c_uint32(idx), C.c_size_t(axis))
+
+    def gather_along(self, x: int, idx: int, axis: int) -> int:
+        return self._n("ku_gather_along", C.c_uint32(x), C.c_uint32(idx), C.c_size_t(axis))
+
+    def scatter(self, operand: int, idx: int, updates: int, axis: int, combine: int = 0) -> int:
+        return self._n("ku_scatter", C.c_uint32(operand), C.c_uint32(idx), C.c_uint32(updates), C.c_size_t(axis), C.c_uint32(combine))
+
+    def scatter_along(self, operand: int, idx: int, updates: int, axis: int, combine: int = 0) -> int:
+        return self._n("ku_scatter_along", C.c_uint32(operand), C.c_uint32(idx), C.c_uint32(updates), C.c_size_t(axis), C.c_uint32(combine))
+
+    def argsort(self, x: int, axis: int, descending: bool = False) -> int:
+        return self._n("ku_argsort", C.c_uint32(x), C.c_size_t(axis), C.c_uint32(1 if descending else 0))
+
+    def sort(self, x: int, axis: int, descending: bool = False) -> int:
+        return self._n("ku_sort", C.c_uint32(x), C.c_size_t(axis), C.c_uint32(1 if descending else 0))
+
     def argmax(self, x: int, axis: int) -> int:
         return self._n("ku_argmax", C.c_uint32(x), C.c_size_t(axis))
 

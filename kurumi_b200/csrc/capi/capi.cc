@@ -201,6 +201,19 @@ int32_t ku_eval_many(KuGraph* g, const KuNode* ids, size_t n, const KuBackend* b
   });
 }
 
+// indexing, kurumi.h:245-253
+KuNode ku_gather(KuGraph* g, KuNode x, KuNode idx, size_t axis) { return build(g, [&](Graph& gr) { return gr.gather(x, idx, axis); }); }
+KuNode ku_gather_along(KuGraph* g, KuNode x, KuNode idx, size_t axis) { return build(g, [&](Graph& gr) { return gr.gather_along(x, idx, axis); }); }
+KuNode ku_take_along_dim(KuGraph* g, KuNode x, KuNode idx, size_t axis) { return build(g, [&](Graph& gr) { return gr.gather_along(x, idx, axis); }); }
+KuNode ku_sort(KuGraph* g, KuNode x, size_t axis, uint32_t descending) { return build(g, [&](Graph& gr) { return gr.sort(x, axis, descending != 0); }); }
+KuNode ku_argsort(KuGraph* g, KuNode x, size_t axis, uint32_t descending) { return build(g, [&](Graph& gr) { return gr.argsort(x, axis, descending != 0); }); }
+KuNode ku_scatter(KuGraph* g, KuNode operand, KuNode indices, KuNode updates, size_t axis, uint32_t combine) {
+  return build(g, [&](Graph& gr) { if (combine > 3) throw Error("ku_scatter: bad combine " + std::to_string(combine)); return gr.scatter(operand, indices, updates, axis, static_cast<uint8_t>(combine)); });
+}
+KuNode ku_scatter_along(KuGraph* g, KuNode operand, KuNode indices, KuNode updates, size_t axis, uint32_t combine) {
+  return build(g, [&](Graph& gr) { if (combine > 3) throw Error("ku_scatter_along: bad combine " + std::to_string(combine)); return gr.scatter_along(operand, indices, updates, axis, static_cast<uint8_t>(combine)); });
+}
+
 KuNode ku_quant_matmul(KuGraph* g, KuNode act, KuNode qweight, KuNode scales, KuNode mins, uint8_t bits, size_t group_size) {
   return build(g, [&](Graph& gr) { return gr.quant_matmul(act, qweight, scales, mins == KU_ERR ? nullptr : &mins, bits, group_size); });
 }

@@ -26,7 +26,8 @@ const char* op_name(OpKind k) {
   static const char* n[] = {"Const", "Input", "Iota", "RandUniform", "Cast", "Bitcast", "Detach", "Add", "Mul", "Max",
                             "Neg", "IDiv", "And", "Or", "Xor", "Shl", "Shr", "CmpLt", "CmpEq", "Where", "Recip", "Sqrt",
                             "Exp2", "Log2", "Sin", "Floor", "Sum", "Prod", "ReduceMax", "Softmax", "RmsNorm", "Sdpa",
-                            "Reshape", "Permute", "Expand", "Slice", "Flip", "Pad", "DotGeneral", "QuantMatmul", "ArgReduce"};
+                            "Reshape", "Permute", "Expand", "Slice", "Flip", "Pad", "DotGeneral", "QuantMatmul", "ArgReduce",
+                            "Gather", "GatherAlong", "Scatter", "ScatterAlong", "Argsort"};
   return n[static_cast<size_t>(k)];
 }
 
@@ -56,7 +57,7 @@ DType Graph::infer_dtype(const Op& op, const std::vector<NodeId>& src) const {
     case OpKind::Const: return op.data->dtype;
     case OpKind::Input: case OpKind::Iota: case OpKind::Cast: case OpKind::Bitcast: return op.to;
     case OpKind::CmpLt: case OpKind::CmpEq: return DType::BOOL;
-    case OpKind::ArgReduce: return DType::I64;   // indices
+    case OpKind::ArgReduce: case OpKind::Argsort: return DType::I64;   // indices
     case OpKind::RandUniform: return DType::F32;
     case OpKind::Where: return node(src[1]).dtype;
     default: return node(src[0]).dtype;
@@ -98,6 +99,14 @@ Shape Graph::derive_shape(const Op& op, const std::vector<NodeId>& src) const {
       return o;
     }
     case OpKind::QuantMatmul: return Shape{ishape(0)[0], ishape(1)[0]};   // act [M, K] x dequant(qweight) [N, K]^T
+    case OpKind::Gather: {   // kurumi_core/src/graph/infer.rs:96-99
+      const Shape &a = ishape(0), &ix = ishape(1);
+      Shape o(a.begin(), a.begin() + static_cast<long>(op.axis));
+      o.insert(o.end(), ix.begin(), ix.end());
+      o.insert(o.end(), a.begin() + static_cast<long>(op.axis) + 1, a.end());
+      return o;
+    }
+    case OpKind::GatherAlong: return ishape(1);   // the index shape
     default: return ishape(0);  // elementwise, Softmax, RmsNorm, Sdpa, Flip
   }
 }
@@ -206,6 +215,59 @@ NodeId Graph::sum(NodeId a, size_t axis) { reduce_axis_ok("sum", a, axis); requi
 NodeId Graph::prod(NodeId a, size_t axis) { reduce_axis_ok("prod", a, axis); require("prod", a, is_arith(dtype(a)), "numeric or complex"); Op op; op.kind = OpKind::Prod; op.axis = axis; return push(std::move(op), {a}); }
 NodeId Graph::reduce_max(NodeId a, size_t axis) { reduce_axis_ok("reduce_max", a, axis); require("reduce_max", a, is_numeric(dtype(a)), "numeric"); Op op; op.kind = OpKind::ReduceMax; op.axis = axis; return push(std::move(op), {a}); }
 // kurumi_core/src/graph/ops/core/reduce.rs:24-33
+// ---- indexing (kurumi_core/src/graph/ops/core/indexing.rs:21-136) --------------------------------
+NodeId Graph::gather(NodeId operand, NodeId indices, size_t axis) {
+  reduce_axis_ok("gather", operand, axis);
+  if (!is_int(dtype(indices))) throw Error::shape("gather", std::string("indices must be integer, got ") + dtype_name(dtype(indices)));
+  Op op; op.kind = OpKind::Gather; op.axis = axis;
+  return push(std::move(op), {operand, indices});
+}
+NodeId Graph::gather_along(NodeId operand, NodeId indices, size_t axis) {
+  reduce_axis_ok("gather_along", operand, axis);
+  if (!is_int(dtype(indices))) throw Error::shape("gather_along", std::string("indices must be integer, got ") + dtype_name(dtype(indices)));
+  const Shape &os = shape(operand), &is = shape(indices);
+  bool ok = is.size() == os.size();
+  for (size_t d = 0; ok && d < os.size(); ++d) if (d != axis && is[d] != os[d]) ok = false;
+  if (!ok) throw Error::shape("gather_along", "indices " + shape_str(is) + " must match operand " + shape_str(os) + " except axis " + std::to_string(axis));
+  Op op; op.kind = OpKind::GatherAlong; op.axis = axis;
+  return push(std::move(op), {operand, indices});
+}
+NodeId Graph::scatter(NodeId operand, NodeId indices, NodeId updates, size_t axis, uint8_t combine) {
+  reduce_axis_ok("scatter", operand, axis);
+  if (combine > 3) throw Error::shape("scatter", "unknown combiner " + std::to_string(combine));
+  if (!is_int(dtype(indices))) throw Error::shape("scatter", std::string("indices must be integer, got ") + dtype_name(dtype(indices)));
+  same_dtype("scatter", operand, updates);
+  const Shape &os = shape(operand), &is = shape(indices);
+  Shape want(os.begin(), os.begin() + static_cast<long>(axis));
+  want.insert(want.end(), is.begin(), is.end());
+  want.insert(want.end(), os.begin() + static_cast<long>(axis) + 1, os.end());
+  if (shape(updates) != want) throw Error::shape("scatter", "updates shape " + shape_str(shape(updates)) + " != " + shape_str(want));
+  if (combine != 0 && !is_numeric(dtype(operand))) throw Error::shape("scatter", "Add/Max combiner needs a numeric operand");
+  Op op; op.kind = OpKind::Scatter; op.axis = axis; op.combine = combine;
+  return push(std::move(op), {operand, indices, updates});
+}
+NodeId Graph::scatter_along(NodeId operand, NodeId indices, NodeId updates, size_t axis, uint8_t combine) {
+  reduce_axis_ok("scatter_along", operand, axis);
+  if (combine > 3) throw Error::shape("scatter_along", "unknown combiner " + std::to_string(combine));
+  if (!is_int(dtype(indices))) throw Error::shape("scatter_along", std::string("indices must be integer, got ") + dtype_name(dtype(indices)));
+  if (combine != 0 && !is_numeric(dtype(operand))) throw Error::shape("scatter_along", "Add/Max combiner needs a numeric operand");
+  same_dtype("scatter_along", operand, updates);
+  if (shape(indices) != shape(updates)) throw Error::shape("scatter_along", "indices and updates must share a shape");
+  const Shape &os = shape(operand), &is = shape(indices);
+  bool ok = is.size() == os.size();
+  for (size_t d = 0; ok && d < os.size(); ++d) if (d != axis && is[d] != os[d]) ok = false;
+  if (!ok) throw Error::shape("scatter_along", "indices " + shape_str(is) + " must match operand " + shape_str(os) + " except axis " + std::to_string(axis));
+  Op op; op.kind = OpKind::ScatterAlong; op.axis = axis; op.combine = combine;
+  return push(std::move(op), {operand, indices, updates});
+}
+NodeId Graph::argsort(NodeId a, size_t axis, bool descending) {
+  reduce_axis_ok("argsort", a, axis);
+  require("argsort", a, is_numeric(dtype(a)), "numeric");
+  Op op; op.kind = OpKind::Argsort; op.axis = axis; op.descending = descending;
+  return push(std::move(op), {a});
+}
+NodeId Graph::sort(NodeId a, size_t axis, bool descending) { return gather_along(a, argsort(a, axis, descending), axis); }
+
 NodeId Graph::argmax(NodeId a, size_t axis) { reduce_axis_ok("argmax", a, axis); require("argmax", a, is_numeric(dtype(a)), "numeric"); Op op; op.kind = OpKind::ArgReduce; op.axis = axis; op.arg_min = false; return push(std::move(op), {a}); }
 NodeId Graph::argmin(NodeId a, size_t axis) { reduce_axis_ok("argmin", a, axis); require("argmin", a, is_numeric(dtype(a)), "numeric"); Op op; op.kind = OpKind::ArgReduce; op.axis = axis; op.arg_min = true; return push(std::move(op), {a}); }
 NodeId Graph::softmax(NodeId a, size_t axis) { reduce_axis_ok("softmax", a, axis); require("softmax", a, is_float(dtype(a)), "float"); Op op; op.kind = OpKind::Softmax; op.axis = axis; return push(std::move(op), {a}); }

@@ -85,6 +85,7 @@ enum class OpKind : uint8_t {
   Sum, Prod, ReduceMax, Softmax, RmsNorm, Sdpa,
   Reshape, Permute, Expand, Slice, Flip, Pad, DotGeneral,
   QuantMatmul, ArgReduce,
+  Gather, GatherAlong, Scatter, ScatterAlong, Argsort,
 };
 const char* op_name(OpKind k);
 inline bool is_movement(OpKind k) { return k >= OpKind::Reshape && k <= OpKind::Pad; }
@@ -105,6 +106,8 @@ struct Op {
   size_t group_size = 0;                       // QuantMatmul: weights per (scale, min) group along K
   bool symmetric = true;                       // QuantMatmul: no mins operand
   bool arg_min = false;                        // ArgReduce: index of the minimum instead of the maximum
+  uint8_t combine = 0;                         // Scatter / ScatterAlong: 0 set, 1 add, 2 max, 3 min (kurumi_core/src/graph/op.rs:104-109)
+  bool descending = false;                     // Argsort
 };
 
 struct Node {
@@ -160,6 +163,14 @@ class Graph {
   NodeId argmax(NodeId a, size_t axis);   // I64 index of the first maximum along the axis
   NodeId argmin(NodeId a, size_t axis);
   NodeId rmsnorm(NodeId a, size_t axis, float eps);
+  // indexing along one axis (kurumi_core/src/graph/ops/core/indexing.rs:21-123): out-of-range indices are clamped by the
+  // gathers and dropped by the scatters; updates fold into the operand in index order
+  NodeId gather(NodeId operand, NodeId indices, size_t axis);          // out = operand[..axis] ++ indices.shape ++ operand[axis+1..]
+  NodeId gather_along(NodeId operand, NodeId indices, size_t axis);    // out = indices.shape, one index per position
+  NodeId scatter(NodeId operand, NodeId indices, NodeId updates, size_t axis, uint8_t combine);
+  NodeId scatter_along(NodeId operand, NodeId indices, NodeId updates, size_t axis, uint8_t combine);
+  NodeId argsort(NodeId a, size_t axis, bool descending);              // I64 permutation per line, stable
+  NodeId sort(NodeId a, size_t axis, bool descending);                 // gather_along(a, argsort(a))
   NodeId reshape(NodeId a, Shape shape);
   NodeId permute(NodeId a, std::vector<size_t> perm);
   NodeId expand(NodeId a, Shape shape);

@@ -20,6 +20,7 @@ constexpr TagRow kTags[] = {
     {OpKind::Sin, 24},    {OpKind::Floor, 25},  {OpKind::Sum, 26},      {OpKind::Prod, 27},       {OpKind::ReduceMax, 28}, {OpKind::Softmax, 30},
     {OpKind::RmsNorm, 31}, {OpKind::Sdpa, 32},  {OpKind::Reshape, 33},  {OpKind::Permute, 34},    {OpKind::Expand, 35},  {OpKind::Slice, 36},
     {OpKind::Flip, 37},   {OpKind::Pad, 38},    {OpKind::DotGeneral, 39}, {OpKind::QuantMatmul, 40}, {OpKind::ArgReduce, 29},
+    {OpKind::Gather, 50}, {OpKind::Scatter, 51}, {OpKind::GatherAlong, 52}, {OpKind::ScatterAlong, 53}, {OpKind::Argsort, 54},
 };
 uint8_t tag_of(OpKind k) {
   for (const TagRow& r : kTags) if (r.kind == k) return r.tag;
@@ -57,6 +58,9 @@ void write_op(Writer& w, const Op& op) {
     case OpKind::Cast: case OpKind::Bitcast: w.dtype(op.to); break;
     case OpKind::Sum: case OpKind::Prod: case OpKind::ReduceMax: case OpKind::Softmax: w.u64(op.axis); break;
     case OpKind::ArgReduce: w.u64(op.axis); w.u8(op.arg_min ? 1 : 0); break;
+    case OpKind::Gather: case OpKind::GatherAlong: w.u64(op.axis); break;
+    case OpKind::Scatter: case OpKind::ScatterAlong: w.u64(op.axis); w.u8(op.combine); break;
+    case OpKind::Argsort: w.u64(op.axis); w.u8(op.descending ? 1 : 0); break;
     case OpKind::RmsNorm: w.u64(op.axis); w.f32(op.eps); break;
     case OpKind::Sdpa: w.u8(op.causal ? 1 : 0); break;
     case OpKind::Reshape: case OpKind::Expand: w.vec(op.shape); break;
@@ -208,6 +212,13 @@ NodeId read_node(Reader& r, Graph& g, size_t index) {
       op.arg_min = kind == 1;
       break;
     }
+    case OpKind::Gather: case OpKind::GatherAlong: op.axis = r.usize(); break;
+    case OpKind::Scatter: case OpKind::ScatterAlong:
+      op.axis = r.usize();
+      op.combine = r.u8();
+      if (op.combine > 3) throw bad("unknown scatter combiner " + std::to_string(op.combine));
+      break;
+    case OpKind::Argsort: op.axis = r.usize(); op.descending = r.u8() != 0; break;
     case OpKind::RmsNorm: op.axis = r.usize(); op.eps = r.f32(); break;
     case OpKind::Sdpa: op.causal = r.u8() != 0; break;
     case OpKind::Reshape: case OpKind::Expand: op.shape = r.vec(); checked_numel(op.shape); break;
@@ -269,6 +280,11 @@ NodeId read_node(Reader& r, Graph& g, size_t index) {
     case OpKind::ReduceMax: need(1); id = g.reduce_max(src[0], op.axis); break;
     case OpKind::Softmax: need(1); id = g.softmax(src[0], op.axis); break;
     case OpKind::ArgReduce: need(1); id = op.arg_min ? g.argmin(src[0], op.axis) : g.argmax(src[0], op.axis); break;
+    case OpKind::Gather: need(2); id = g.gather(src[0], src[1], op.axis); break;
+    case OpKind::GatherAlong: need(2); id = g.gather_along(src[0], src[1], op.axis); break;
+    case OpKind::Scatter: need(3); id = g.scatter(src[0], src[1], src[2], op.axis, op.combine); break;
+    case OpKind::ScatterAlong: need(3); id = g.scatter_along(src[0], src[1], src[2], op.axis, op.combine); break;
+    case OpKind::Argsort: need(1); id = g.argsort(src[0], op.axis, op.descending); break;
     case OpKind::RmsNorm: need(1); id = g.rmsnorm(src[0], op.axis, op.eps); break;
     case OpKind::Sdpa: need(3); id = g.sdpa_fused(src[0], src[1], src[2], op.causal); break;
     case OpKind::Reshape: need(1); id = g.reshape(src[0], op.shape); break;

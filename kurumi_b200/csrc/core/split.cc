@@ -96,6 +96,26 @@ struct Walk {
         if (ax < nb + lf.size()) return want(id, n.src[0], static_cast<int>(lf[ax - nb])) && want(id, n.src[1], kWhole);
         return want(id, n.src[0], kWhole) && want(id, n.src[1], static_cast<int>(rf[ax - nb - lf.size()]));
       }
+      case OpKind::Gather: {   // out = operand[..axis] ++ indices.shape ++ operand[axis+1..]
+        const size_t ir = g.shape(n.src[1]).size();
+        if (ax < op.axis) return want(id, n.src[0], a) && want(id, n.src[1], kWhole);
+        if (ax < op.axis + ir) return want(id, n.src[0], kWhole) && want(id, n.src[1], static_cast<int>(ax - op.axis));
+        return want(id, n.src[0], static_cast<int>(ax - ir + 1)) && want(id, n.src[1], kWhole);
+      }
+      case OpKind::GatherAlong:
+        if (ax == op.axis) return want(id, n.src[0], kWhole) && want(id, n.src[1], a);
+        return all(id, a);
+      case OpKind::Scatter: {
+        if (ax == op.axis) return fail(id, "scatters along the split axis");
+        const size_t ir = g.shape(n.src[1]).size();
+        return want(id, n.src[0], a) && want(id, n.src[1], kWhole) && want(id, n.src[2], static_cast<int>(ax < op.axis ? ax : ax + ir - 1));
+      }
+      case OpKind::ScatterAlong:
+        if (ax == op.axis) return fail(id, "scatters along the split axis");
+        return all(id, a);
+      case OpKind::Argsort:
+        if (ax == op.axis) return fail(id, "sorts along the split axis");
+        return want(id, n.src[0], a);
       case OpKind::QuantMatmul:
         if (ax != 0) return fail(id, "separates over activation rows only");
         if (!want(id, n.src[0], 0)) return false;

@@ -567,6 +567,42 @@ Emitted emit_reduce(const Fused& f, OpKind kind, size_t axis, int sm_count) {
     e.block = 256;
     e.grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(outer, static_cast<int64_t>(sm_count) * 8)));
     e.family = "reduce_rows";
+  } else if (len >= 64 && outer * inner <= static_cast<int64_t>(sm_count) * 512) {
+    // few outputs, a long axis (a reduction over rows, a short tensor's last axis): a CTA owns 32 neighbouring outputs and
+    // cuts the axis into SEG contiguous segments, one per warp-row of threads; a thread folds its segment in index order,
+    // then the segments combine in ascending order (a fixed order: results do not depend on the launch)
+    const int64_t outs = outer * inner;
+    const int threads = len >= 2048 ? 1024 : 256, seg = threads / 32;
+    const int64_t chunk = (len + seg - 1) / seg;
+    o << "extern \"C\" __global__ void __launch_bounds__(" << threads << ") ku_reduce_split(" << g.params() << "void* __restrict__ out) {\n  const KuComb comb;\n";
+    o << "  __shared__ " << ro.acc_t << " part[" << seg << "][33];\n";
+    o << "  const int col = threadIdx.x & 31, sg = threadIdx.x >> 5;\n";
+    o << "  for (" << g.idx_t << " o0 = (" << g.idx_t << ")blockIdx.x * 32; o0 < " << outs << "; o0 += (" << g.idx_t << ")gridDim.x * 32) {\n";
+    o << "    const " << g.idx_t << " o = o0 + col;\n";
+    o << "    " << ro.acc_t << " acc = " << ro.identity << ";\n";
+    o << "    if (o < " << outs << ") {\n";
+    o << "      const " << g.idx_t << " oi = o % " << inner << ", oo = o / " << inner << ";\n";
+    if (ax > 0) o << decompose("oo", sp.dims, 0, ax, g.idx_t, "c", "      ");
+    if (ax + 1 < nd) {
+      std::vector<int64_t> tail(sp.dims);
+      o << decompose("oi", tail, ax + 1, nd, g.idx_t, "c", "      ");
+    }
+    o << "      const " << g.idx_t << " k1 = (" << g.idx_t << ")(sg + 1) * " << chunk << " < " << len << " ? (" << g.idx_t << ")(sg + 1) * " << chunk << " : " << len << ";\n";
+    o << "      for (" << g.idx_t << " k = (" << g.idx_t << ")sg * " << chunk << "; k < k1; ++k) {\n";
+    {
+      std::vector<std::string> lv(f.leaves.size());
+      for (size_t li = 0; li < f.leaves.size(); ++li) lv[li] = g.leaf_value(li, coords);
+      o << g.body(lv, "        ");
+    }
+    o << "        acc = comb(acc, v" << f.root << ");\n      }\n    }\n";
+    o << "    part[sg][col] = acc;\n    __syncthreads();\n";
+    o << "    if (sg == 0 && o < " << outs << ") {\n      " << ro.acc_t << " a = part[0][col];\n";
+    o << "      for (int q = 1; q < " << seg << "; ++q) a = comb(a, part[q][col]);\n";
+    o << "      ((" << stype(d) << "*)out)[o] = " << enc(d, "a") << ";\n    }\n    __syncthreads();\n  }\n}\n";
+    e.entry = "ku_reduce_split";
+    e.block = static_cast<unsigned>(threads);
+    e.grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((outs + 31) / 32, static_cast<int64_t>(sm_count) * 4)));
+    e.family = "reduce_split";
   } else {
     // one thread per output element, folding the axis in index order (the interpreter's own order);
     // adjacent threads walk adjacent inner positions, so loads coalesce when the axis is not innermost
@@ -927,6 +963,124 @@ Emitted emit_gemm_simt(const GemmDesc& gd, const Fused* epi, int sm_count) {
   e.entry = "ku_gemm_simt";
   e.block = 256;
   e.family = "gemm_simt";
+  (void)sm_count;
+  return e;
+}
+
+// ---- indexing and sorting -------------------------------------------------------------------------
+// Kernels over contiguous row-major buffers (the scheduler writes operands out first). The semantics are the
+// interpreter's, kurumi_core/src/interp/indexing/{gather,scatter}.rs and interp/sort.rs: gathers clamp an out-of-range
+// index, scatters drop it, updates fold into the copy of the operand in index order (so results are bit-exact and
+// deterministic: every destination element is owned by one thread, which walks the indices in order), sorting is stable.
+namespace {
+std::string combine_expr(uint8_t combine, DType d) {   // old value `a`, update `b`, both in the dtype's register type
+  const std::string C = ctype(d), U = wrap_utype(d);
+  const bool flt = is_float(d);
+  switch (combine) {
+    case 0: return "b";
+    case 1: return flt ? "(a + b)" : "(" + C + ")((" + U + ")a + (" + U + ")b)";
+    case 2: return flt ? (d == DType::F64 ? "fmax(a, b)" : "fmaxf(a, b)") : "(a > b ? a : b)";
+    default: return flt ? (d == DType::F64 ? "fmin(a, b)" : "fminf(a, b)") : "(a < b ? a : b)";
+  }
+}
+}  // namespace
+
+Emitted emit_gather(DType d, DType idx_dt, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count) {
+  std::ostringstream o;
+  o << device_prelude();
+  const int64_t total = pre * k * post;
+  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_gather(const void* __restrict__ src, const void* __restrict__ idx, void* __restrict__ out) {\n";
+  o << "  for (i64 e = (i64)blockIdx.x * 256 + threadIdx.x; e < " << total << "ll; e += (i64)gridDim.x * 256) {\n";
+  o << "    const i64 j = e % " << post << "ll, ki = (e / " << post << "ll) % " << k << "ll, p = e / " << (post * k) << "ll;\n";
+  o << "    i64 a = (i64)((const " << stype(idx_dt) << "*)idx)[ki];\n";
+  o << "    a = a < 0 ? 0 : (a > " << (da - 1) << "ll ? " << (da - 1) << "ll : a);\n";
+  o << "    ((" << stype(d) << "*)out)[e] = ((const " << stype(d) << "*)src)[(p * " << da << "ll + a) * " << post << "ll + j];\n  }\n}\n";
+  Emitted e;
+  e.source = o.str(); e.entry = "ku_gather"; e.block = 256; e.grid = pick_grid(total, 256, sm_count, 8); e.family = "gather";
+  return e;
+}
+
+Emitted emit_gather_along(DType d, DType idx_dt, int64_t outer, int64_t da, int64_t la, int64_t inner, int sm_count) {
+  std::ostringstream o;
+  o << device_prelude();
+  const int64_t total = outer * la * inner;
+  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_gather_along(const void* __restrict__ src, const void* __restrict__ idx, void* __restrict__ out) {\n";
+  o << "  for (i64 e = (i64)blockIdx.x * 256 + threadIdx.x; e < " << total << "ll; e += (i64)gridDim.x * 256) {\n";
+  o << "    const i64 pi = e % " << inner << "ll, po = e / " << (la * inner) << "ll;\n";
+  o << "    i64 a = (i64)((const " << stype(idx_dt) << "*)idx)[e];\n";
+  o << "    a = a < 0 ? 0 : (a > " << (da - 1) << "ll ? " << (da - 1) << "ll : a);\n";
+  o << "    ((" << stype(d) << "*)out)[e] = ((const " << stype(d) << "*)src)[(po * " << da << "ll + a) * " << inner << "ll + pi];\n  }\n}\n";
+  Emitted e;
+  e.source = o.str(); e.entry = "ku_gather_along"; e.block = 256; e.grid = pick_grid(total, 256, sm_count, 8); e.family = "gather_along";
+  return e;
+}
+
+// `out` already holds the copy of the operand. Scatter: thread per (p, j) walks the k indices; ScatterAlong (along = true):
+// thread per line (po, pi) walks the la positions of the index tensor. [pre | outer, da, post | inner] is the operand.
+Emitted emit_scatter(DType d, DType idx_dt, bool along, uint8_t combine, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count) {
+  std::ostringstream o;
+  o << device_prelude();
+  const int64_t total = pre * post;
+  const std::string S = stype(d), C = ctype(d);
+  o << "extern \"C\" __global__ void __launch_bounds__(128) ku_scatter(const void* __restrict__ idx, const void* __restrict__ upd, void* __restrict__ out) {\n";
+  o << "  for (i64 t = (i64)blockIdx.x * 128 + threadIdx.x; t < " << total << "ll; t += (i64)gridDim.x * 128) {\n";
+  o << "    const i64 j = t % " << post << "ll, p = t / " << post << "ll;\n";
+  o << "    for (i64 ki = 0; ki < " << k << "ll; ++ki) {\n";
+  o << "      const i64 u = (p * " << k << "ll + ki) * " << post << "ll + j;\n";
+  o << "      const i64 raw = (i64)((const " << stype(idx_dt) << "*)idx)[" << (along ? "u" : "ki") << "];\n";
+  o << "      if (raw < 0 || raw >= " << da << "ll) continue;\n";
+  o << "      " << S << "* dst = (" << S << "*)out + (p * " << da << "ll + raw) * " << post << "ll + j;\n";
+  if (combine == 0) {
+    o << "      *dst = ((const " << S << "*)upd)[u];\n";
+  } else {
+    o << "      const " << C << " a = " << dec(d, "*dst") << ", b = " << dec(d, "((const " + S + "*)upd)[u]") << ";\n";
+    o << "      *dst = (" << S << ")" << enc(d, combine_expr(combine, d)) << ";\n";
+  }
+  o << "    }\n  }\n}\n";
+  Emitted e;
+  e.source = o.str(); e.entry = "ku_scatter"; e.block = 128; e.grid = pick_grid(total, 128, sm_count, 8); e.family = along ? "scatter_along" : "scatter";
+  return e;
+}
+
+// One CTA per line: a bitonic network over (key, original index) pairs in shared memory. The pairs are totally ordered
+// (equal keys order by index), so the network's result is the stable permutation; padding sorts last.
+Emitted emit_argsort(DType d, bool descending, int64_t outer, int64_t len, int64_t inner, int sm_count) {
+  int64_t lpad = 1;
+  while (lpad < len) lpad <<= 1;
+  // keys are held in at least 32 bits (the index array behind them stays aligned)
+  const size_t key_bytes = d == DType::F64 || dtype_width(d) == 8 ? 8 : 4;
+  const std::string S = stype(d), C = is_float(d) ? (d == DType::F64 ? "double" : "float") : key_bytes == 8 ? ctype(d) : is_signed(d) ? "i32" : "u32";
+  std::ostringstream o;
+  o << device_prelude();
+  o << "#define LEN " << len << "\n#define LPAD " << lpad << "\n#define INNER " << inner << "ll\n";
+  o << "typedef " << C << " key_t;\n";
+  o << "__device__ __forceinline__ bool ku_before(key_t ka, int ia, key_t kb, int ib) {\n";
+  o << "  if (ia >= LEN || ib >= LEN) return ia < ib;\n";
+  o << "  const bool lt = " << (descending ? "ka > kb" : "ka < kb") << ", gt = " << (descending ? "ka < kb" : "ka > kb") << ";\n";
+  o << "  return lt || (!gt && ia < ib);\n}\n";
+  o << "extern \"C\" __global__ void ku_argsort(const void* __restrict__ src, void* __restrict__ out) {\n";
+  o << "  extern __shared__ __align__(16) unsigned char raw[];\n";
+  o << "  key_t* keys = (key_t*)raw;\n  int* ids = (int*)(raw + (size_t)LPAD * sizeof(key_t));\n";
+  o << "  const i64 line = blockIdx.x, po = line / INNER, pi = line % INNER;\n";
+  o << "  const " << S << "* base = (const " << S << "*)src + po * LEN * INNER + pi;\n";
+  o << "  for (int i = threadIdx.x; i < LPAD; i += blockDim.x) {\n";
+  o << "    ids[i] = i;\n    keys[i] = i < LEN ? (key_t)" << dec(d, "base[(i64)i * INNER]") << " : (key_t)0;\n  }\n";
+  o << "  __syncthreads();\n";
+  o << "  for (int k = 2; k <= LPAD; k <<= 1)\n    for (int j = k >> 1; j > 0; j >>= 1) {\n";
+  o << "      for (int i = threadIdx.x; i < LPAD; i += blockDim.x) {\n";
+  o << "        const int l = i ^ j;\n        if (l > i) {\n";
+  o << "          const key_t ka = keys[i], kb = keys[l];\n          const int ia = ids[i], ib = ids[l];\n";
+  o << "          const bool up = (i & k) == 0;\n";
+  o << "          if (ku_before(kb, ib, ka, ia) == up) { keys[i] = kb; keys[l] = ka; ids[i] = ib; ids[l] = ia; }\n";
+  o << "        }\n      }\n      __syncthreads();\n    }\n";
+  o << "  i64* dst = (i64*)out + po * LEN * INNER + pi;\n";
+  o << "  for (int r = threadIdx.x; r < LEN; r += blockDim.x) dst[(i64)r * INNER] = (i64)ids[r];\n}\n";
+  Emitted e;
+  e.source = o.str(); e.entry = "ku_argsort";
+  e.block = static_cast<unsigned>(std::max<int64_t>(32, std::min<int64_t>(1024, lpad / 2)));
+  e.grid = static_cast<unsigned>(outer * inner);
+  e.smem = static_cast<unsigned>(lpad * (key_bytes + 4));
+  e.family = "argsort";
   (void)sm_count;
   return e;
 }

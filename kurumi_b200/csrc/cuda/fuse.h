@@ -140,6 +140,12 @@ Emitted emit_arg_reduce(const Fused& f, size_t axis, bool arg_min, int sm_count)
 // Softmax / RmsNorm over `axis` of `f`; output has f's shape, row-major.
 Emitted emit_softmax(const Fused& f, OpKind kind, size_t axis, float eps, int sm_count);
 
+// Indexing along one axis and per-line sorting over contiguous buffers (kernel parameters: see emit.cc).
+Emitted emit_gather(DType d, DType idx_dt, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count);
+Emitted emit_gather_along(DType d, DType idx_dt, int64_t outer, int64_t da, int64_t la, int64_t inner, int sm_count);
+Emitted emit_scatter(DType d, DType idx_dt, bool along, uint8_t combine, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count);
+Emitted emit_argsort(DType d, bool descending, int64_t outer, int64_t len, int64_t inner, int sm_count);
+
 struct GemmDesc {
   DType dtype = DType::F32;       // operand / result dtype of the DotGeneral
   int64_t batch = 1, m = 0, n = 0, k = 0;

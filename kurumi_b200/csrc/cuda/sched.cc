@@ -533,6 +533,69 @@ Fused Scheduler::quant_matmul(const Node& n, const std::vector<Fused>& in) {
   return combine(OpKind::Cast, dt, {&r});
 }
 
+// ---- indexing and sorting -----------------------------------------------------------------------------
+// Gather / GatherAlong / Scatter / ScatterAlong / Argsort (kurumi_core/src/interp/indexing/**, interp/sort.rs) run over
+// contiguous operands; a scatter first writes the operand into the result buffer (fused with whatever produced it), then
+// folds the updates in.
+Fused Scheduler::dense(const Fused& f0) {
+  Fused f = resolve_acc(f0);
+  if (f.is_plain_buffer() && f.root_leaf().view.is_contiguous()) return f;
+  return materialize(f);
+}
+
+Fused Scheduler::indexing(const Node& n, const std::vector<Fused>& in) {
+  const Op& op = n.op;
+  const Shape& os = g_.shape(n.src[0]);
+  const DType dt = g_.dtype(n.src[0]);
+  const size_t axis = op.axis;
+  int64_t pre = 1, post = 1;
+  for (size_t d = 0; d < axis; ++d) pre *= static_cast<int64_t>(os[d]);
+  for (size_t d = axis + 1; d < os.size(); ++d) post *= static_cast<int64_t>(os[d]);
+  const int64_t da = static_cast<int64_t>(os[axis]);
+  auto launch = [&](const Emitted& e, std::initializer_list<int> slots) {
+    Launch L;
+    L.name = e.family;
+    L.kernel = (*load_)(e.source, e.entry, false);
+    L.grid[0] = e.grid; L.block[0] = e.block; L.smem = e.smem;
+    for (int sl : slots) { Arg a; a.kind = Arg::SlotPtr; a.slot = sl; L.args.push_back(a); }
+    for (int sl : slots) L.algo_bytes += static_cast<double>(prog_.slots[static_cast<size_t>(sl)].bytes);
+    prog_.launches.push_back(std::move(L));
+  };
+  if (op.kind == OpKind::Argsort) {
+    Fused x = dense(in[0]);
+    const int slot = new_slot(Slot::Temp, DType::I64, n.shape);
+    if (!dry() && numel(n.shape) > 0) {
+      int64_t lpad = 1;
+      while (lpad < da) lpad <<= 1;
+      const int64_t key = (dt == DType::F64 || dtype_width(dt) == 8) ? 8 : 4;
+      if (lpad * (key + 4) > 200 * 1024) throw Error::backend("argsort along an axis of " + std::to_string(da) + " elements is longer than the sorting kernel holds in shared memory");
+      launch(emit_argsort(dt, op.descending, pre, da, post, sm_), {x.root_leaf().slot, slot});
+    }
+    return buffer_value(slot, DType::I64, n.shape);
+  }
+  const DType idt = g_.dtype(n.src[1]);
+  const Shape& is = g_.shape(n.src[1]);
+  if (op.kind == OpKind::Gather || op.kind == OpKind::GatherAlong) {
+    Fused x = dense(in[0]), ix = dense(in[1]);
+    const int slot = new_slot(Slot::Temp, dt, n.shape);
+    if (!dry() && numel(n.shape) > 0) {
+      if (da == 0) throw Error::backend("gather from an empty axis");
+      if (op.kind == OpKind::Gather) launch(emit_gather(dt, idt, pre, da, post, static_cast<int64_t>(numel(is)), sm_), {x.root_leaf().slot, ix.root_leaf().slot, slot});
+      else launch(emit_gather_along(dt, idt, pre, da, static_cast<int64_t>(is[axis]), post, sm_), {x.root_leaf().slot, ix.root_leaf().slot, slot});
+    }
+    return buffer_value(slot, dt, n.shape);
+  }
+  // scatters: the operand goes into the result buffer first
+  Fused ix = dense(in[1]), up = dense(in[2]);
+  const int slot = new_slot(Slot::Temp, dt, n.shape);
+  materialize(resolve_acc(in[0]), slot);
+  const bool along = op.kind == OpKind::ScatterAlong;
+  const int64_t k = along ? static_cast<int64_t>(is[axis]) : static_cast<int64_t>(numel(is));
+  if (!dry() && numel(n.shape) > 0 && numel(is) > 0)
+    launch(emit_scatter(dt, idt, along, op.combine, pre, da, post, k, sm_), {ix.root_leaf().slot, up.root_leaf().slot, slot});
+  return buffer_value(slot, dt, n.shape);
+}
+
 // ---- the walk ---------------------------------------------------------------------------------------
 Fused Scheduler::value_of(NodeId id) { return memo_.at(id); }
 
@@ -604,6 +667,7 @@ Fused Scheduler::eval_node(NodeId id) {
       return movement(n, in[0]);
     case OpKind::DotGeneral: return dot(n, in[0], in[1]);
     case OpKind::QuantMatmul: return quant_matmul(n, in);
+    case OpKind::Gather: case OpKind::GatherAlong: case OpKind::Scatter: case OpKind::ScatterAlong: case OpKind::Argsort: return indexing(n, in);
     case OpKind::ArgReduce: {
       Fused f = resolve_acc(in[0]);
       const int slot = new_slot(Slot::Temp, DType::I64, n.shape);

@@ -49,6 +49,8 @@ class Scheduler {
                     const std::vector<size_t>& rc, const std::vector<size_t>& lb, const std::vector<size_t>& rb);
   Fused sdpa(const Node& n, const Fused& q, const Fused& k, const Fused& v);
   Fused quant_matmul(const Node& n, const std::vector<Fused>& in);
+  Fused indexing(const Node& n, const std::vector<Fused>& in);
+  Fused dense(const Fused& f);   // the value in a contiguous buffer of its own layout (written out if it is not one already)
   Fused view_step(OpKind k, Fused f, const Shape& shape);
   Fused imm_value(const Shape& shape, DType dt, uint64_t bits) const;
   void emit_gemm(int id, const Fused* epi, int out_slot);

@@ -312,6 +312,151 @@ void reduce_fold(const T* data, const Shape& shape, size_t axis, T init, F f, T*
   }
 }
 
+// ---- indexing and sorting (kurumi_core/src/interp/indexing.rs:23-36, indexing/gather.rs, indexing/scatter.rs, sort.rs) ----
+std::vector<int64_t> indices_i64(const Val& ix) {
+  const size_t n = numel(ix.shape);
+  std::vector<int64_t> out(n);
+  KO_INTS(ix.dtype, {
+    using T = E<DT>;
+    auto* p = reinterpret_cast<const typename T::S*>(ix.bytes.data());
+    for (size_t i = 0; i < n; ++i) out[i] = static_cast<int64_t>(p[i]);
+  })
+  return out;
+}
+
+// indexing/gather.rs:55-77: operand laid out [pre, axis, post]; the post-slice at each clamped index; out = [pre, idx.shape, post]
+Val gather_val(const Val& a, const Val& ix, size_t axis) {
+  const std::vector<int64_t> idx = indices_i64(ix);
+  Shape out(a.shape.begin(), a.shape.begin() + static_cast<long>(axis));
+  out.insert(out.end(), ix.shape.begin(), ix.shape.end());
+  out.insert(out.end(), a.shape.begin() + static_cast<long>(axis) + 1, a.shape.end());
+  Val o = make_val(a.dtype, out, a.wide);
+  const size_t w = esize(a), da = a.shape[axis];
+  size_t pre = 1, post = 1;
+  for (size_t d = 0; d < axis; ++d) pre *= a.shape[d];
+  for (size_t d = axis + 1; d < a.shape.size(); ++d) post *= a.shape[d];
+  const size_t k = numel(ix.shape);
+  if (numel(out) == 0) return o;
+  size_t dst = 0;
+  for (size_t p = 0; p < pre; ++p)
+    for (size_t ki = 0; ki < k; ++ki) {
+      const int64_t j = std::min<int64_t>(std::max<int64_t>(idx[ki], 0), static_cast<int64_t>(da) - 1);   // out of range: clamped
+      std::memcpy(o.bytes.data() + dst * w, a.bytes.data() + ((p * da + static_cast<size_t>(j)) * post) * w, post * w);
+      dst += post;
+    }
+  return o;
+}
+
+// indexing/gather.rs:31-51: out[c] = operand[c with axis <- clamp(idx[c])]; out and idx share a shape
+Val gather_along_val(const Val& a, const Val& ix, size_t axis) {
+  const std::vector<int64_t> idx = indices_i64(ix);
+  Val o = make_val(a.dtype, ix.shape, a.wide);
+  const size_t w = esize(a), n = numel(ix.shape);
+  const auto st = row_major_strides(a.shape);
+  const int64_t da = static_cast<int64_t>(a.shape[axis]);
+  std::vector<size_t> coord(ix.shape.size(), 0);
+  for (size_t f = 0; f < n; ++f) {
+    const size_t j = static_cast<size_t>(std::min<int64_t>(std::max<int64_t>(idx[f], 0), da - 1));
+    size_t src = 0;
+    for (size_t d = 0; d < a.shape.size(); ++d) src += (d == axis ? j : coord[d]) * st[d];
+    std::memcpy(o.bytes.data() + f * w, a.bytes.data() + src * w, w);
+    inc(coord, ix.shape);
+  }
+  return o;
+}
+
+// fold element `src` of `up` into element `dst` of `out`: 0 set, 1 add, 2 max, 3 min, with the dtype's own arithmetic
+// (low-precision floats: upcast to f32, combine, round back; integers wrap)
+void combine_elem(Val& out, size_t dst, const Val& up, size_t src, uint8_t combine) {
+  if (combine == 0) { const size_t w = esize(out); std::memcpy(out.bytes.data() + dst * w, up.bytes.data() + src * w, w); return; }
+  if (out.wide) {
+    double& x = wd(out)[dst];
+    const double y = wd(up)[src];
+    x = combine == 1 ? x + y : combine == 2 ? std::fmax(x, y) : std::fmin(x, y);
+    return;
+  }
+  KO_NUMERIC(out.dtype, {
+    using T = E<DT>;
+    auto* z = reinterpret_cast<typename T::S*>(out.bytes.data());
+    auto* u = reinterpret_cast<const typename T::S*>(up.bytes.data());
+    const typename T::C x = T::ld(z[dst]), y = T::ld(u[src]);
+    typename T::C r;
+    if (combine == 1) r = op_add(x, y);
+    else if (combine == 2) r = op_max(x, y);
+    else { if constexpr (std::is_floating_point_v<typename T::C>) r = std::fmin(x, y); else r = x < y ? x : y; }
+    z[dst] = T::st(r);
+  })
+}
+
+// indexing/scatter.rs:180-207: a copy of the operand; each update post-slice folds into [.., idx, ..] in index order, out-of-range dropped
+Val scatter_val(const Val& a, const Val& ix, const Val& up, size_t axis, uint8_t combine) {
+  const std::vector<int64_t> idx = indices_i64(ix);
+  Val o = a;
+  size_t pre = 1, post = 1;
+  for (size_t d = 0; d < axis; ++d) pre *= a.shape[d];
+  for (size_t d = axis + 1; d < a.shape.size(); ++d) post *= a.shape[d];
+  const size_t k = numel(ix.shape), da = a.shape[axis];
+  if (numel(a.shape) == 0) return o;
+  for (size_t p = 0; p < pre; ++p)
+    for (size_t ki = 0; ki < k; ++ki) {
+      const int64_t raw = idx[ki];
+      if (raw < 0 || raw >= static_cast<int64_t>(da)) continue;
+      const size_t dst = (p * da + static_cast<size_t>(raw)) * post, src = (p * k + ki) * post;
+      for (size_t j = 0; j < post; ++j) combine_elem(o, dst + j, up, src + j, combine);
+    }
+  return o;
+}
+
+// indexing/scatter.rs:142-166: per-position index along the axis; idx and updates share a shape
+Val scatter_along_val(const Val& a, const Val& ix, const Val& up, size_t axis, uint8_t combine) {
+  const std::vector<int64_t> idx = indices_i64(ix);
+  Val o = a;
+  const auto st = row_major_strides(a.shape);
+  const int64_t da = static_cast<int64_t>(a.shape[axis]);
+  const size_t n = numel(ix.shape);
+  std::vector<size_t> coord(ix.shape.size(), 0);
+  for (size_t f = 0; f < n; ++f) {
+    const int64_t j = idx[f];
+    if (j >= 0 && j < da) {
+      size_t dst = 0;
+      for (size_t d = 0; d < a.shape.size(); ++d) dst += (d == axis ? static_cast<size_t>(j) : coord[d]) * st[d];
+      combine_elem(o, dst, up, f, combine);
+    }
+    inc(coord, ix.shape);
+  }
+  return o;
+}
+
+// sort.rs:41-68: per line, the stable permutation that sorts it (ties keep the lower original index); elements compare
+// by value, `descending` reverses the comparison of the keys only. A line holding a NaN has no defined order in the
+// reference (partial_cmp falls back to Equal, which is not a consistent ordering): not pinned here either.
+Val argsort_val(const Val& a, size_t axis, bool descending) {
+  Val o = make_val(DType::I64, a.shape, false);
+  auto* out = reinterpret_cast<int64_t*>(o.bytes.data());
+  const auto st = row_major_strides(a.shape);
+  const size_t len = a.shape[axis], stride = st[axis], total = numel(a.shape);
+  if (total == 0) return o;
+  auto run = [&](auto key) {   // key(flat) -> comparable value
+    std::vector<size_t> perm(len);
+    for (size_t f = 0; f < total; ++f) {
+      if ((f / stride) % len != 0) continue;   // f is the first element of a line
+      for (size_t i = 0; i < len; ++i) perm[i] = i;
+      std::stable_sort(perm.begin(), perm.end(), [&](size_t i, size_t j) {
+        const auto vi = key(f + i * stride), vj = key(f + j * stride);
+        return descending ? vi > vj : vi < vj;
+      });
+      for (size_t r = 0; r < len; ++r) out[f + r * stride] = static_cast<int64_t>(perm[r]);
+    }
+  };
+  if (a.wide) { const double* p = wd(a); run([&](size_t i) { return p[i]; }); return o; }
+  KO_NUMERIC(a.dtype, {
+    using T = E<DT>;
+    auto* p = reinterpret_cast<const typename T::S*>(a.bytes.data());
+    run([&](size_t i) { return T::ld(p[i]); });
+  })
+  return o;
+}
+
 // kurumi_core/src/interp/reduce.rs:16-66: I64 index of the maximum / minimum along `axis`; the first element is the
 // starting best and a later one replaces it only when strictly greater / smaller, so ties keep the lowest index
 // and a NaN never replaces anything (nor is a leading NaN ever replaced). Elements compare by value.
@@ -811,6 +956,11 @@ Val eval_op(const Node& n, const std::vector<const Val*>& in, bool wide_mode) {
       return ew_unary(op.kind, *in[0]);
     case OpKind::Sum: case OpKind::Prod: case OpKind::ReduceMax: return reduce_val(op.kind, *in[0], op.axis, wide_mode);
     case OpKind::ArgReduce: return arg_reduce_val(*in[0], op.axis, op.arg_min);
+    case OpKind::Gather: return gather_val(*in[0], *in[1], op.axis);
+    case OpKind::GatherAlong: return gather_along_val(*in[0], *in[1], op.axis);
+    case OpKind::Scatter: return scatter_val(*in[0], *in[1], *in[2], op.axis, op.combine);
+    case OpKind::ScatterAlong: return scatter_along_val(*in[0], *in[1], *in[2], op.axis, op.combine);
+    case OpKind::Argsort: return argsort_val(*in[0], op.axis, op.descending);
     case OpKind::Softmax: return softmax_val(*in[0], op.axis);
     case OpKind::RmsNorm: return rmsnorm_val(*in[0], op.axis, op.eps);
     case OpKind::Sdpa: return sdpa_val(*in[0], *in[1], *in[2], op.causal);

@@ -33,3 +33,47 @@ def test_transposed_softmax_from_a_blob(oracle_lib, cuda_lib, cpu64, gpu):
     got = gpu.eval_with(gc, outs[0], fc).numpy()
     want = cpu64.eval_with(go, root, fo).numpy()
     util.assert_close(want, got, 1e-5, 1e-12, "softmax from a blob")
+
+
+def gemm_bias_gelu_backward(g, m, n, k):
+    """The reverse-mode graph of configuration 3, out = gelu(A @ B + bias), for a cotangent dOut, written out with the
+    builders as the reference's autograd (kurumi_core/src/grad/**) emits it: primitives only, the two backward
+    contractions are transposed dot_generals (kurumi_metal/src/backend/eval/matmul.rs:81-147 lists the layouts).
+    gelu(z) = 0.5 z (1 + tanh(u)), u = c (z + a z^3); d/dz = 0.5 (1 + t) + 0.5 z (1 - t^2) c (1 + 3 a z^2)."""
+    A, B, bias, dout = g.input([m, k], api.BF16), g.input([k, n], api.BF16), g.input([n], api.BF16), g.input([m, n], api.BF16)
+    z = g.add(g.matmul(A, B), g.broadcast_to(bias, [m, n]))
+    c, a = 0.7978845608028654, 0.044715
+    z2 = g.mul(z, z)
+    t = g.tanh(g.mul(g.scalar(z, c), g.add(z, g.mul(g.scalar(z, a), g.mul(z2, z)))))
+    one = g.scalar(z, 1.0)
+    left = g.mul(g.scalar(z, 0.5), g.add(one, t))
+    sech2 = g.add(one, g.neg(g.mul(t, t)))
+    right = g.mul(g.mul(g.scalar(z, 0.5), z), g.mul(sech2, g.mul(g.scalar(z, c), g.add(one, g.mul(g.scalar(z, 3 * a), z2)))))
+    dz = g.mul(dout, g.add(left, right))
+    dA = g.dot_general(dz, B, [1], [1])          # [m, n] x [k, n]^T -> [m, k]
+    dB = g.dot_general(A, dz, [0], [0])          # [m, k]^T x [m, n] -> [k, n]
+    dbias = g.sum(dz, 0)                         # a reduction over the rows
+    return (A, B, bias, dout), (dA, dB, dbias)
+
+
+def test_backward_graph_of_the_gemm_configuration_from_a_blob(oracle_lib, cuda_lib, cpu64, gpu):
+    m, n, k = 384, 512, 256
+    go = api.Graph(oracle_lib)
+    ins_o, outs_o = gemm_bias_gelu_backward(go, m, n, k)
+    blob = go.serialize(list(outs_o), [(node, 1, name) for node, name in zip(ins_o, ("A", "B", "bias", "dOut"))], reachable=True)
+    gc, entries = api.deserialize(cuda_lib, blob)
+    (_, outs, ins) = entries[0]
+    by_name = {name: node for node, _, name in ins}
+    rng = np.random.default_rng(33)
+    vals = {"A": rng.standard_normal((m, k)) / np.sqrt(k), "B": rng.standard_normal((k, n)), "bias": rng.uniform(-0.1, 0.1, n), "dOut": rng.standard_normal((m, n))}
+    fo, fc = api.Feeds(oracle_lib), api.Feeds(cuda_lib)
+    for (node_o, name) in zip(ins_o, ("A", "B", "bias", "dOut")):
+        bits = api.f32_to_bf16(vals[name].astype(np.float32))
+        fo.set(node_o, bits, api.BF16)
+        fc.set(by_name[name], bits, api.BF16)
+    fams = api.compile_check(cuda_lib, gc, outs)
+    assert fams.count("gemm_tc") == 3, fams          # forward and the two transposed backward contractions on the tensor cores
+    got = gpu.eval_many_with(gc, outs, fc)
+    want = cpu64.eval_many_with(go, list(outs_o), fo)
+    for name, a, b in zip(("dA", "dB", "dbias"), want, got):
+        util.assert_band(a.numpy(), util.to_f64(b.numpy(), api.BF16), 2e-2, 2.0 ** -7, f"backward of gemm + bias + gelu, {name}")
