@@ -382,29 +382,106 @@ Fused Scheduler::dot(const Node& n, const Fused& a, const Fused& b) {
 // Op::Sdpa (kurumi_core/src/graph/op.rs:55-58); the math is the interpreter's decomposition,
 // kurumi_core/src/interp/nn.rs:125-172. The tiled tensor-core kernel takes the shapes it
 // supports; everything else runs the same decomposition on device through the generic kernels.
+Fused Scheduler::attention(DType dt, const Shape& shape, bool causal, float scale, const Fused& q, const Fused& k, const Fused& v) {
+  const size_t r = shape.size();
+  const size_t S = shape[r - 2], dh = shape[r - 1];
+  if (dry()) return buffer_value(new_slot(Slot::Temp, dt, shape), dt, shape);
+  Launch L;
+  if (!build_attention(*load_, dt, shape, causal, scale, sm_, &L)) throw Error::backend("internal: attention kernel rejected a supported shape");
+  const int slot = new_slot(Slot::Temp, dt, shape);
+  const int slots[4] = {q.root_leaf().slot, k.root_leaf().slot, v.root_leaf().slot, slot};
+  for (auto& a : L.args) { int* s = a.kind == Arg::Tmap ? &a.tm.slot : &a.slot; if ((a.kind == Arg::Tmap || a.kind == Arg::SlotPtr) && *s < 0) *s = slots[-*s - 1]; }
+  size_t bh = 1;
+  for (size_t i = 0; i + 2 < r; ++i) bh *= shape[i];
+  L.algo_bytes = 4.0 * static_cast<double>(numel(shape) * dtype_width(dt));
+  L.flops = 4.0 * static_cast<double>(dh) * static_cast<double>(bh) * (causal ? static_cast<double>(S) * (S + 1) / 2.0 : static_cast<double>(S) * S);
+  prog_.launches.push_back(std::move(L));
+  return buffer_value(slot, dt, shape);
+}
+
+bool Scheduler::match_sdpa(NodeId id, SdpaMatch* m) const {
+  auto uses = [&](NodeId x) { auto it = consumers_.find(x); return it == consumers_.end() ? size_t(0) : it->second; };
+  const Node& n = g_.node(id);
+  const size_t r = n.shape.size();
+  if (n.op.kind != OpKind::DotGeneral || r < 2) return false;
+  std::vector<size_t> batch;
+  for (size_t i = 0; i + 2 < r; ++i) batch.push_back(i);
+  if (n.op.lc != std::vector<size_t>{r - 1} || n.op.rc != std::vector<size_t>{r - 2} || n.op.lb != batch || n.op.rb != batch) return false;
+  std::vector<NodeId> inner;
+  const NodeId attn_id = n.src[0], v = n.src[1];
+  const Node& attn = g_.node(attn_id);
+  if (attn.op.kind != OpKind::Softmax || attn.op.axis != r - 1 || uses(attn_id) != 1) return false;
+  inner.push_back(attn_id);
+  NodeId sc_id = attn.src[0];
+  bool causal = false;
+  // a scalar constant expanded to a shape: Expand(Const of one element)
+  auto scalar_of = [&](NodeId x, double* val) {
+    const Node& e = g_.node(x);
+    if (e.op.kind != OpKind::Expand || uses(x) != 1) return false;
+    const Node& c = g_.node(e.src[0]);
+    if (c.op.kind != OpKind::Const || numel(c.shape) != 1 || uses(e.src[0]) != 1) return false;
+    *val = elem_to_f64(c.dtype, c.op.data->bytes.data());
+    inner.push_back(x); inner.push_back(e.src[0]);
+    return true;
+  };
+  // the causal bias: [Cast] <- Expand <- Reshape <- Const f32 [S, S] holding 0 on and below the diagonal, -inf above
+  auto causal_bias_of = [&](NodeId x, size_t S) {
+    std::vector<NodeId> chain;
+    NodeId cur = x;
+    if (g_.node(cur).op.kind == OpKind::Cast) { chain.push_back(cur); cur = g_.node(cur).src[0]; }
+    if (g_.node(cur).op.kind != OpKind::Expand) return false;
+    chain.push_back(cur); cur = g_.node(cur).src[0];
+    if (g_.node(cur).op.kind != OpKind::Reshape) return false;
+    chain.push_back(cur); cur = g_.node(cur).src[0];
+    const Node& c = g_.node(cur);
+    chain.push_back(cur);
+    if (c.op.kind != OpKind::Const || c.dtype != DType::F32 || c.shape != Shape{S, S}) return false;
+    for (NodeId y : chain) if (uses(y) != 1) return false;
+    const float* d = c.op.data->data<float>();
+    for (size_t i = 0; i < S; ++i)
+      for (size_t j = 0; j < S; ++j) {
+        const float want = j > i ? -std::numeric_limits<float>::infinity() : 0.0f;
+        if (!(d[i * S + j] == want)) return false;
+      }
+    inner.insert(inner.end(), chain.begin(), chain.end());
+    return true;
+  };
+  const size_t S = n.shape[r - 2];
+  if (g_.node(sc_id).op.kind == OpKind::Add) {
+    if (uses(sc_id) != 1) return false;
+    const Node& add = g_.node(sc_id);
+    NodeId scores = add.src[0], bias = add.src[1];
+    if (g_.node(scores).op.kind != OpKind::Mul) std::swap(scores, bias);
+    if (!causal_bias_of(bias, S)) return false;
+    inner.push_back(sc_id);
+    sc_id = scores;
+    causal = true;
+  }
+  const Node& mul = g_.node(sc_id);
+  if (mul.op.kind != OpKind::Mul || uses(sc_id) != 1) return false;
+  inner.push_back(sc_id);
+  NodeId raw_id = mul.src[0], inv = mul.src[1];
+  if (g_.node(raw_id).op.kind != OpKind::DotGeneral) std::swap(raw_id, inv);
+  double scale = 0;
+  if (!scalar_of(inv, &scale) || !(scale > 0)) return false;
+  const Node& raw = g_.node(raw_id);
+  if (raw.op.kind != OpKind::DotGeneral || uses(raw_id) != 1) return false;
+  if (raw.op.lc != std::vector<size_t>{r - 1} || raw.op.rc != std::vector<size_t>{r - 1} || raw.op.lb != batch || raw.op.rb != batch) return false;
+  inner.push_back(raw_id);
+  const NodeId q = raw.src[0], k = raw.src[1];
+  if (g_.shape(q) != n.shape || g_.shape(k) != n.shape || g_.shape(v) != n.shape) return false;   // self-attention shapes only
+  if (g_.dtype(q) != n.dtype || !attention_supported(n.dtype, n.shape)) return false;
+  m->q = q; m->k = k; m->v = v; m->causal = causal; m->scale = static_cast<float>(scale); m->interior = std::move(inner);
+  return true;
+}
+
 Fused Scheduler::sdpa(const Node& n, const Fused& q0, const Fused& k0, const Fused& v0) {
   const DType dt = n.dtype;
   const size_t r = n.shape.size();
   const size_t S = n.shape[r - 2], dh = n.shape[r - 1];
   const float scale = 1.0f / std::sqrt(static_cast<float>(dh));
   Fused q = materialize(resolve_acc(q0)), k = materialize(resolve_acc(k0)), v = materialize(resolve_acc(v0));
-  if (!dry() && attention_supported(dt, n.shape)) {
-    Launch L;
-    if (!build_attention(*load_, dt, n.shape, n.op.causal, scale, sm_, &L)) throw Error::backend("internal: attention kernel rejected a supported shape");
-    {
-      const int slot = new_slot(Slot::Temp, dt, n.shape);
-      const int slots[4] = {q.root_leaf().slot, k.root_leaf().slot, v.root_leaf().slot, slot};
-      for (auto& a : L.args) { int* s = a.kind == Arg::Tmap ? &a.tm.slot : &a.slot; if ((a.kind == Arg::Tmap || a.kind == Arg::SlotPtr) && *s < 0) *s = slots[-*s - 1]; }
-      size_t bh = 1;
-      for (size_t i = 0; i + 2 < r; ++i) bh *= n.shape[i];
-      L.algo_bytes = 4.0 * static_cast<double>(numel(n.shape) * dtype_width(dt));
-      L.flops = 4.0 * static_cast<double>(dh) * static_cast<double>(bh) * (n.op.causal ? static_cast<double>(S) * (S + 1) / 2.0 : static_cast<double>(S) * S);
-      prog_.launches.push_back(std::move(L));
-      return buffer_value(slot, dt, n.shape);
-    }
-  } else if (dry() && attention_supported(dt, n.shape)) {
-    return buffer_value(new_slot(Slot::Temp, dt, n.shape), dt, n.shape);
-  }
+  if (attention_supported(dt, n.shape)) return attention(dt, n.shape, n.op.causal, scale, q, k, v);
   std::vector<size_t> batch;
   for (size_t i = 0; i + 2 < r; ++i) batch.push_back(i);
   Shape ss(n.shape.begin(), n.shape.end() - 2);
@@ -685,6 +762,21 @@ Program Scheduler::compile(const std::vector<NodeId>& roots) {
   const std::vector<NodeId> order = reachable(g_, roots);
   for (NodeId id : order) for (NodeId s : g_.node(id).src) ++consumers_[s];
   for (NodeId id : order) {
+    SdpaMatch m;
+    if (match_sdpa(id, &m)) {
+      for (NodeId x : m.interior) skipped_[x] = true;
+      sdpa_matches_.emplace(id, std::move(m));
+    }
+  }
+  for (NodeId id : order) {
+    if (skipped_.count(id)) continue;
+    auto sm = sdpa_matches_.find(id);
+    if (sm != sdpa_matches_.end()) {
+      const SdpaMatch& m = sm->second;
+      Fused q = materialize(resolve_acc(memo_.at(m.q))), k = materialize(resolve_acc(memo_.at(m.k))), v = materialize(resolve_acc(memo_.at(m.v)));
+      memo_.emplace(id, attention(g_.dtype(id), g_.shape(id), m.causal, m.scale, q, k, v));
+      continue;
+    }
     Fused f = eval_node(id);
     // a shared, expensive expression is written once instead of being recomputed per consumer
     if (consumers_[id] > 1 && op_nodes(f) > 24 && find_acc(f) < 0) f = materialize(f);

@@ -48,6 +48,11 @@ class Scheduler {
   Fused dot_general(DType dt, const Shape& out_shape, const Fused& a, const Fused& b, const std::vector<size_t>& lc,
                     const std::vector<size_t>& rc, const std::vector<size_t>& lb, const std::vector<size_t>& rb);
   Fused sdpa(const Node& n, const Fused& q, const Fused& k, const Fused& v);
+  Fused attention(DType dt, const Shape& shape, bool causal, float scale, const Fused& q, const Fused& k, const Fused& v);
+  // The decomposition Graph::sdpa records below its 1 GiB score-buffer threshold (kurumi_core/src/graph/ops/nn/attention.rs:97-113),
+  // found again so that the same user call runs the same fused kernel at every size.
+  struct SdpaMatch { NodeId q, k, v; bool causal; float scale; std::vector<NodeId> interior; };
+  bool match_sdpa(NodeId id, SdpaMatch* m) const;
   Fused quant_matmul(const Node& n, const std::vector<Fused>& in);
   Fused indexing(const Node& n, const std::vector<Fused>& in);
   Fused dense(const Fused& f);   // the value in a contiguous buffer of its own layout (written out if it is not one already)
@@ -67,6 +72,8 @@ class Scheduler {
   std::unordered_map<NodeId, Fused> memo_;
   std::unordered_map<NodeId, size_t> consumers_;
   std::vector<PendingGemm> gemms_;
+  std::unordered_map<NodeId, SdpaMatch> sdpa_matches_;   // final dot_general of a recognised decomposition
+  std::unordered_map<NodeId, bool> skipped_;             // interior nodes of those: never evaluated
 };
 
 // Compile `roots` of `g`: a dry run decides epilogue fusion, the second run emits kernels.

@@ -58,3 +58,31 @@ def test_attention_config_graph_uses_the_fused_primitive(cuda_lib):
     root, _ = configs.causal_attention(g)     # [8, 32, 4096, 128]: score buffer over 1 GiB -> Op::Sdpa
     assert "Sdpa" in g.dump(root)
     assert api.compile_check(cuda_lib, g, [root]) == ["attention_tc"]
+
+
+def test_the_decomposition_runs_the_same_fused_kernel(oracle_lib, cuda_lib, cpu64, gpu):
+    """Graph::sdpa records dot -> scale -> causal bias -> softmax -> dot below its 1 GiB score-buffer threshold and the
+    fused primitive above it (kurumi_core/src/graph/ops/nn/attention.rs:78-113): the backend finds the decomposition again,
+    so the same call runs the same kernel at every size. A decomposition whose scores are also wanted stays decomposed."""
+    rng = np.random.default_rng(44)
+    small, big = api.Graph(cuda_lib), api.Graph(cuda_lib)
+    for g, shape in ((small, [2, 2, 512, 128]), (big, [8, 32, 4096, 128])):
+        q, k, v = (g.input(shape, api.BF16) for _ in range(3))
+        root = g.sdpa(q, k, v, True)
+        assert ("Sdpa" in g.dump(root)) == (g is big)
+        assert api.compile_check(cuda_lib, g, [root]) == ["attention_tc"]
+    for shape, causal in (((2, 2, 512, 128), True), ((1, 3, 300, 64), False)):
+        p = Pair(oracle_lib, cuda_lib)
+        q, k, v = (p.feed(shape, api.BF16, bf16(rng, shape)) for _ in range(3))
+        out = p.sdpa_decomposed(q, k, v, causal)
+        assert api.compile_check(cuda_lib, p.gc, [out]) == ["attention_tc"]
+        w, c, dts = p.run(cpu64, gpu, [out])
+        util.assert_band(w[0], util.to_f64(c[0], dts[0]), 2e-2, 2.0 ** -8, f"decomposition on the fused kernel {shape}")
+    # the probabilities are an output too: nothing may be skipped
+    p = Pair(oracle_lib, cuda_lib)
+    shape = (1, 2, 256, 128)
+    q, k, v = (p.feed(shape, api.BF16, bf16(rng, shape)) for _ in range(3))
+    out = p.sdpa_decomposed(q, k, v, True)
+    probs = p.go.node_src(out)[0] if hasattr(p.go, "node_src") else None
+    fams = api.compile_check(cuda_lib, p.gc, [out, p.mul(out, out)])
+    assert fams[0] == "attention_tc"
