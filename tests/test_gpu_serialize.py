@@ -56,7 +56,7 @@ def gemm_bias_gelu_backward(g, m, n, k):
     return (A, B, bias, dout), (dA, dB, dbias)
 
 
-def test_backward_graph_of_the_gemm_configuration_from_a_blob(oracle_lib, cuda_lib, cpu64, gpu):
+def test_backward_graph_of_the_gemm_configuration_from_a_blob(oracle_lib, cuda_lib, cpu, cpu64, gpu):
     m, n, k = 384, 512, 256
     go = api.Graph(oracle_lib)
     ins_o, outs_o = gemm_bias_gelu_backward(go, m, n, k)
@@ -75,5 +75,9 @@ def test_backward_graph_of_the_gemm_configuration_from_a_blob(oracle_lib, cuda_l
     assert fams.count("gemm_tc") == 3, fams          # forward and the two transposed backward contractions on the tensor cores
     got = gpu.eval_many_with(gc, outs, fc)
     want = cpu64.eval_many_with(go, list(outs_o), fo)
-    for name, a, b in zip(("dA", "dB", "dbias"), want, got):
-        util.assert_band(a.numpy(), util.to_f64(b.numpy(), api.BF16), 2e-2, 2.0 ** -7, f"backward of gemm + bias + gelu, {name}")
+    native = cpu.eval_many_with(go, list(outs_o), fo)
+    for name, a, nat, b in zip(("dA", "dB", "dbias"), want, native, got):
+        # the derivative of gelu is some 25 bf16 primitives, each rounded (the interpreter's semantics, which the device keeps):
+        # against the bf16 interpreter the contraction band applies; the f64 run, which rounds nothing on the way, is further off
+        util.assert_band(util.to_f64(nat.numpy(), api.BF16), util.to_f64(b.numpy(), api.BF16), 2e-2, 2.0 ** -7, f"backward of gemm + bias + gelu vs bf16 interpreter, {name}")
+        util.assert_band(a.numpy(), util.to_f64(b.numpy(), api.BF16), 4e-2, 2.0 ** -6, f"backward of gemm + bias + gelu vs f64 run, {name}")
