@@ -83,15 +83,19 @@ int32_t ku_cuda_softmax_lines_f32(const KuBackend *b, const float *in, const flo
 /* The same softmax for callers that must not allocate device memory when they call it: a
  * latency-critical loop that cannot take the device-wide synchronisation cudaMalloc / cudaFree may
  * imply, a host application that owns all of HBM through its own arena, or code running where the
- * CUDA allocator must not be entered (host callbacks, allocation hooks). No counterpart in the reference: kurumi
- * has no device entry point of this kind. The scratch is a fixed 8 MiB array in the library's device
+ * CUDA allocator must not be entered (another library's allocation hook). No counterpart in the reference:
+ * kurumi has no device entry point of this kind. The scratch is a fixed 8 MiB array in the library's device
  * image (every GPU that loads the library holds it until exit), so the call is rejected with -1 when
  * lines * ceil(len / 128) * 8 + lines * 4 bytes exceed 8 MiB (for example 8192 lines of 8192 fit,
- * 16384 lines of 16384 do not). Runs on `stream` (a cudaStream_t) of the current device. The first call
- * on each device looks up the array's device address (cudaGetSymbolAddress); that first call should
- * come before any stream capture begins. All
- * calls share the one array: nothing in it needs clearing between calls, but two calls whose kernels
- * can overlap on the GPU (different streams, no dependency) race on it. No cudaMalloc / cudaFree. */
+ * 16384 lines of 16384 do not), and, like the entry above, for lines longer than 65535 * 64 positions.
+ * Runs on `stream`, a cudaStream_t that must belong to the device that is current when the call is made (the
+ * scratch address is looked up for the current device; the call does not check whose stream it was given).
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and, with the
+ * runtime's lazy loading, is also when the kernels and the array are placed on that GPU: make one small real
+ * call per device (a few lines, so that all three kernels load) at start-up, before HBM is handed away and
+ * before any stream capture begins; later calls neither allocate nor load. All calls share the one array:
+ * nothing in it needs clearing between calls, but two calls whose kernels can overlap on the GPU
+ * (different streams, no dependency) race on it. No cudaMalloc / cudaFree. */
 int32_t ku_cuda_softmax_lines_f32_noalloc(const float *in, const float *bias, float *out, size_t lines, size_t len, size_t ld, void *stream);
 
 /* Everything the backend caches for a graph - compiled programs with their scratch buffers, uploaded constants,

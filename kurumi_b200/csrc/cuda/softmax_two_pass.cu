@@ -150,6 +150,8 @@ bool args_ok(const float* in, const float* out, size_t lines, size_t len, size_t
   if ((!in || !out) && lines && len) { ku::set_err("softmax_lines: null input / output pointer"); return false; }
   if (ld < lines) { ku::set_err("softmax_lines: ld is smaller than the number of lines"); return false; }
   if (lines >= (size_t(1) << 31) || len >= (size_t(1) << 31)) { ku::set_err("softmax_lines: extent does not fit 31 bits"); return false; }
+  // the position blocks of a line (64 positions each in the write-out pass) are the launch grid's second dimension
+  if (len > size_t(65535) * 64) { ku::set_err("softmax_lines: lines longer than 65535 * 64 = 4194240 positions are not supported by this entry point"); return false; }
   return true;
 }
 
@@ -184,9 +186,13 @@ extern "C" int32_t ku_cuda_softmax_lines_f32(const KuBackend* b, const float* in
 // Some callers may not allocate device memory at the moment they need this softmax: a serving loop
 // whose latency budget has no room for the device-wide synchronisation cudaMalloc / cudaFree can
 // imply, a host application that has handed all of HBM to its own arena so the CUDA allocator has
-// nothing left to give, or code that runs where entering the CUDA allocator is not allowed (a
-// host callback, another library's allocation hook). For them the scratch of the two-pass algorithm
-// lives in a fixed array inside the library's device image.
+// nothing left to give, or code that runs where entering the CUDA allocator is not allowed (another
+// library's allocation hook). For them the scratch of the two-pass algorithm lives in a fixed array
+// inside the library's device image. The FIRST call on a device is different: it looks up the array's
+// device address, and with the CUDA runtime's lazy loading it is also the moment the device image - the
+// kernels and the 8 MiB array itself - is placed on that GPU. So a process makes one small real call per
+// device at start-up (a few lines, so that all three kernels load), before it hands HBM away and before
+// any stream capture; the calls after it touch neither the allocator nor the loader.
 namespace {
 constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;  // 8 MiB per GPU that loads the library, held until the process exits
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];

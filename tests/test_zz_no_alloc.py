@@ -37,3 +37,26 @@ def test_no_alloc_entry_rejects_sizes_beyond_its_fixed_scratch(gpu):
         gpu.softmax_lines(d, None, d, 16384, 16384, 16384, entry="ku_cuda_softmax_lines_f32_noalloc")
     with pytest.raises(api.Error, match="ld"):
         gpu.softmax_lines(d, None, d, 64, 64, 32, entry="ku_cuda_softmax_lines_f32_noalloc")
+    # one line of 100 M positions would fit the scratch (6.25 MB) but not the launch grid: refused before anything is queued
+    with pytest.raises(api.Error, match="65535"):
+        gpu.softmax_lines(d, None, d, 1, 100_000_000, 1, entry="ku_cuda_softmax_lines_f32_noalloc")
+    with pytest.raises(api.Error, match="65535"):
+        gpu.softmax_lines(d, None, d, 1, 100_000_000, 1)
+
+
+def test_calls_after_the_warm_up_leave_device_memory_alone(gpu):
+    """The first call on a device places the kernels and the scratch array (lazy loading); from then on a call changes
+    nothing about the device's free memory."""
+    from cuda.bindings import runtime as cudart
+    rng = np.random.default_rng(51)
+    L = rng.standard_normal((512, 256)).astype(np.float32)
+    d_in, d_out = gpu.upload(L), gpu.upload(np.zeros((256, 512), np.float32))
+    gpu.softmax_lines(d_in, None, d_out, 256, 512, 256, entry="ku_cuda_softmax_lines_f32_noalloc")   # the warm-up call
+    gpu.sync()
+    err, free0, _ = cudart.cudaMemGetInfo()
+    assert int(err) == 0
+    for _ in range(3):
+        gpu.softmax_lines(d_in, None, d_out, 256, 512, 256, entry="ku_cuda_softmax_lines_f32_noalloc")
+    gpu.sync()
+    err, free1, _ = cudart.cudaMemGetInfo()
+    assert int(err) == 0 and free1 == free0
