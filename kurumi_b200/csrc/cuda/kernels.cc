@@ -136,6 +136,7 @@ bool build_softmax_two_pass(const Fused& f, size_t axis, Launch* out, size_t* sc
 }
 
 extern const std::string kSrc_quant_gemv;
+extern const std::string kSrc_quant_gemv_mma;
 
 bool quant_gemv_supported(DType act, int64_t m, int64_t n, int64_t k, int bits, int64_t group) {
   if (std::getenv("KURUMI_NO_QUANT_GEMV")) return false;
@@ -148,6 +149,35 @@ bool quant_gemv_supported(DType act, int64_t m, int64_t n, int64_t k, int bits, 
 bool build_quant_gemv(const KernelLoader& load, DType act, int64_t m, int64_t n, int64_t k, int bits, int64_t group, bool symmetric, int sm_count, Launch* out) {
   if (!quant_gemv_supported(act, m, n, k, bits, group)) return false;
   const int64_t piece = 128 / bits;
+  // 16-bit activations against 2- or 4-bit weights whose groups hold whole runs of four 16-byte pieces: the products run on
+  // mma.sync with the raw field values as one operand (kernels/quant_gemv_mma.cuh)
+  if (act != DType::F32 && (bits == 2 || bits == 4) && group % (4 * piece) == 0 && k % (4 * piece) == 0 && n * (k / group) < (int64_t(1) << 31)) {
+    const int64_t run = 4 * piece, depth = 3, res = 4;
+    // a CTA is 8 warps: 8 / ks tiles of 16 rows, ks warps per tile. The largest split whose CTAs still fit one wave keeps
+    // the most loads in flight; past that the CTAs loop over blocks of rows.
+    const int64_t tiles = (n + 15) / 16, wave = static_cast<int64_t>(sm_count) * res;
+    int64_t ks = 8;
+    while (ks > 1 && ((tiles + 8 / ks - 1) / (8 / ks) > wave || k / run < ks * depth)) ks /= 2;
+    // all K columns of the activations staged once when that leaves room for res CTAs per SM, else in chunks that the
+    // ring's slots line up with
+    const int64_t budget = (200 * 1024) / res - 4096, unit = run * ks * depth;
+    int64_t kc = k;
+    if (m * (k + 16) * 2 + m * (k / run) * 4 > budget) kc = std::max<int64_t>(unit, (budget / (2 * m) - 16) / unit * unit);
+    std::string src = device_prelude() +
+                      defines({{"M", m}, {"N", n}, {"K", k}, {"BITS", bits}, {"GROUP", group}, {"SYM", symmetric ? 1 : 0}, {"ACT", act == DType::BF16 ? 1 : 2},
+                               {"KC", kc}, {"KS", ks}, {"D", depth}, {"RES", res}}) +
+                      kSrc_quant_gemv_mma;
+    out->name = "quant_gemv";
+    out->kernel = load(src, "ku_quant_gemv_mma", true);
+    const int64_t rows_per_cta = (8 / ks) * 16;
+    out->grid[0] = static_cast<unsigned>(std::min<int64_t>((n + rows_per_cta - 1) / rows_per_cta, wave));
+    out->block[0] = 256;
+    out->smem = static_cast<unsigned>(m * (kc + 16) * 2 + m * ((kc + run - 1) / run) * 4);
+    for (int sidx = 1; sidx <= 5; ++sidx) { Arg a; a.kind = Arg::SlotPtr; a.slot = -sidx; out->args.push_back(a); }
+    out->algo_bytes = static_cast<double>(n * k * bits / 8 + n * (k / group) * 2 * (symmetric ? 1 : 2) + m * k * dtype_width(act) + m * n * dtype_width(act));
+    out->flops = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k);
+    return true;
+  }
   // a chunk of activation columns in shared memory: whole warp-wide strides of 32 pieces (the kernel's layout
   // permutes columns inside such a stride), about 96 KB at most, never more than K rounded up to a stride
   const int64_t stride = 32 * piece;

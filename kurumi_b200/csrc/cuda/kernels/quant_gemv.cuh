@@ -58,7 +58,8 @@ ku_quant_gemv(const u8* __restrict__ qw, const u16* __restrict__ scales, const u
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
           const int n = (n0 + r) < N ? (n0 + r) : (N - 1);   // rows past the end re-read the last row; their results are dropped
-          pks[r] = *(const uint4*)(qw + (size_t)n * RB + (size_t)kc0 * BITS / 8 + b);
+          // past L1: every byte of the weight is used once, the scales and minima are used again
+          asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(pks[r].x), "=r"(pks[r].y), "=r"(pks[r].z), "=r"(pks[r].w) : "l"(qw + (size_t)n * RB + (size_t)kc0 * BITS / 8 + b));
         }
         const int c0 = b * 8 / BITS;   // first column of the piece inside the chunk
         const float* ap = a_s + blkc * (32 * PIECE) + lane;   // this lane's column f of the block is ap[f * 32]

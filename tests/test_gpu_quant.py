@@ -66,3 +66,34 @@ def test_many_rows_lowering(oracle_lib, cuda_lib, cpu64, gpu, act_dtype, m, tol)
     got = util.to_f64(gpu.eval_with(gc, rc, fc).numpy(), act_dtype)
     want = cpu64.eval_with(go, ro, fo).numpy()
     util.assert_close(want, got, tol, tol * np.abs(want).max(), f"quant matmul m={m}")
+
+
+@pytest.mark.parametrize("bits,group", [(4, 128), (4, 256), (2, 256)])
+@pytest.mark.parametrize("sym", [True, False])
+@pytest.mark.parametrize("act_dtype,m", [(api.BF16, 1), (api.F16, 3), (api.BF16, 8)])
+def test_few_rows_16_bit_activations_on_the_tensor_cores(oracle_lib, cuda_lib, cpu, cpu64, gpu, bits, group, sym, act_dtype, m):
+    """2- and 4-bit weights against 16-bit activations run their products on mma.sync with the raw field values as one
+    operand (kernels/quant_gemv_mma.cuh): the sums are exact up to f32 accumulation, scale and minimum applied in f32, one
+    rounding at the end - as close to the interpreter as the scalar kernel is. Ragged N, several K chunks."""
+    n, k = 200, 4096 + 1024
+    go, ro, fo = build(oracle_lib, m, n, k, bits, group, sym, act_dtype, 17)
+    gc, rc, fc = build(cuda_lib, m, n, k, bits, group, sym, act_dtype, 17)
+    assert api.compile_check(cuda_lib, gc, [rc]) == ["quant_gemv"]
+    got = util.to_f64(gpu.eval_with(gc, rc, fc).numpy(), act_dtype)
+    native = util.to_f64(cpu.eval_with(go, ro, fo).numpy(), act_dtype)
+    wide = cpu64.eval_with(go, ro, fo).numpy()
+    step = 2.0 ** -7 if act_dtype == api.BF16 else 2.0 ** -10
+    util.assert_close(wide, got, step, step * np.abs(wide).max(), f"mma gemv bits={bits} group={group} sym={sym} m={m} vs f64 run")
+    assert (got != native).mean() < 0.05, (got != native).mean()   # one rounding at the end on both sides
+
+
+def test_more_rows_than_one_wave_of_ctas_covers(oracle_lib, cuda_lib, cpu64, gpu):
+    """With more 16-row tiles than one wave of CTAs holds, the CTAs of the mma kernel loop over blocks of rows and stage the
+    activations once; the ragged last block is cut at N."""
+    m, n, k, bits, group = 2, 148 * 4 * 128 + 1000 + 7, 512, 4, 128
+    go, ro, fo = build(oracle_lib, m, n, k, bits, group, False, api.F16, 23)
+    gc, rc, fc = build(cuda_lib, m, n, k, bits, group, False, api.F16, 23)
+    assert api.compile_check(cuda_lib, gc, [rc]) == ["quant_gemv"]
+    got = util.to_f64(gpu.eval_with(gc, rc, fc).numpy(), api.F16)
+    wide = cpu64.eval_with(go, ro, fo).numpy()
+    util.assert_close(wide, got, 2.0 ** -10, 2.0 ** -10 * np.abs(wide).max(), "mma gemv over several blocks per CTA")
