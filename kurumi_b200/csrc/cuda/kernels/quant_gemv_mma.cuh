@@ -116,19 +116,23 @@ ku_quant_gemv_mma(const u8* __restrict__ qw, const u16* __restrict__ scales, con
         __syncthreads();
         // activations of the chunk in instruction order: the four 16-bit values of (run, s, piece) are columns
         // c0, c0 + HALF, c0 + 1, c0 + 1 + HALF with c0 = run * RUN + piece * PIECE + word * FPW + i, pair p = 2 s = word * HALF + i
-        // (read 16 bytes at a time; column c = ((run * 4 + piece) * (PIECE / FPW) + word) * FPW + h * HALF + 2 * s_in + e goes to
-        // 16-bit slot ((run * (PIECE / 4) + word * (HALF / 2) + s_in) * 4 + piece) * 4 + 2 * e + h)
-        for (int idx = threadIdx.x; idx < M * (kc / 8); idx += NT) {
-          const int m = idx / (kc / 8), c8 = (idx - m * (kc / 8)) * 8;
-          const uint4 v = *(const uint4*)((const u16*)act + (size_t)m * K + kc0 + c8);
-          const unsigned w4[4] = {v.x, v.y, v.z, v.w};
+        // (a thread takes the FPW columns under one 32-bit word of weights, 16 or 32 bytes, and writes them as HALF / 2 groups of four)
+        for (int idx = threadIdx.x; idx < M * (kc / FPW); idx += NT) {
+          const int m = idx / (kc / FPW), wi = idx - m * (kc / FPW);      // wi = (run * 4 + piece) * (PIECE / FPW) + word
+          const int wd = wi % (PIECE / FPW), pc = (wi / (PIECE / FPW)) & 3, run = wi / (4 * (PIECE / FPW));
+          const uint4* src = (const uint4*)((const u16*)act + (size_t)m * K + kc0 + wi * FPW);
+          unsigned w[FPW / 2];
 #pragma unroll
-          for (int e8 = 0; e8 < 8; ++e8) {
-            const int c = c8 + e8, run = c / RUN, pc = (c / PIECE) & 3, wd = (c % PIECE) / FPW, f = c % FPW;
-            const int h = f / HALF, i = f % HALF;
-            const int slot = ((run * (PIECE / 4) + wd * (HALF / 2) + (i >> 1)) * 4 + pc) * 4 + 2 * (i & 1) + h;
-            a_s[m * ROWP + slot] = (u16)(w4[e8 >> 1] >> (16 * (e8 & 1)));
+          for (int q = 0; q < FPW / 8; ++q) { const uint4 v = src[q]; w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w; }
+#define KU_COL(f) ((w[(f) >> 1] >> (16 * ((f) & 1))) & 0xFFFFu)
+#pragma unroll
+          for (int sn = 0; sn < HALF / 2; ++sn) {
+            uint2 v;
+            v.x = KU_COL(2 * sn) | (KU_COL(2 * sn + HALF) << 16);
+            v.y = KU_COL(2 * sn + 1) | (KU_COL(2 * sn + 1 + HALF) << 16);
+            *(uint2*)(a_s + m * ROWP + (((run * (PIECE / 4) + wd * (HALF / 2) + sn) * 4 + pc) * 4)) = v;
           }
+#undef KU_COL
         }
         __syncthreads();
         // the sum of each activation row over each run, a warp per (row, run), from the staged copy (the order inside a run is free)
