@@ -56,7 +56,11 @@ WORKLOADS = {
     "c3_gemm_bias_gelu": (configs.gemm_bias_gelu, dict(m=8192, n=8192, kdim=8192), "tensor"),
     "c4_causal_attention": (configs.causal_attention, dict(batch=8, heads=32, seq=4096, dh=128), "tensor"),
     "c5_fp8_weight_gemm": (configs.fp8_weight_gemm, dict(m=16384, kdim=8192, n=28672), "tensor"),
+    # beyond the five configurations: the decode step of a weight-only quantised projection (one GPU; its one activation
+    # row leaves nothing to cut into row shards)
+    "n3_quant_gemv": (configs.quant_gemv, dict(m=1, n=28672, kdim=8192, bits=4, group=128), "hbm"),
 }
+ONE_GPU_ONLY = {"n3_quant_gemv"}
 HEADLINE = "c2_transposed_softmax"
 
 
@@ -73,6 +77,9 @@ def algorithmic_work(name: str, kw: dict):
     if name == "c4_causal_attention":
         b, h, s, d = kw["batch"], kw["heads"], kw["seq"], kw["dh"]
         return 4 * b * h * s * d * 2, 4.0 * d * b * h * s * (s + 1) / 2
+    if name == "n3_quant_gemv":
+        m, n, k, bits, group = kw["m"], kw["n"], kw["kdim"], kw["bits"], kw["group"]
+        return n * k * bits // 8 + 2 * n * (k // group) * 2 + m * k * 2 + m * n * 2, 2.0 * m * n * k
     m, k, n = kw["m"], kw["kdim"], kw["n"]
     return m * k * 2 + k * n + n * 4 + m * n * 2, 2.0 * m * n * k
 
@@ -145,6 +152,9 @@ def cpu_sample(name, kw):
         return dict(m=m, n=kw["n"], kdim=kw["kdim"]), f"{m} of {kw['m']} rows of A"
     if name == "c4_causal_attention":
         return dict(batch=1, heads=1, seq=min(kw["seq"], 512), dh=kw["dh"]), "1 head at seq 512"
+    if name == "n3_quant_gemv":
+        n = min(kw["n"], 4096)   # the interpreter widens the whole weight to f32 first: 4 bytes per weight of host memory
+        return dict(kw, n=n), f"{n} of {kw['n']} output channels"
     m, n = min(kw["m"], 256), min(kw["n"], 1792)   # few rows against all of W would time the widening of W, not the contraction
     return dict(m=m, kdim=kw["kdim"], n=n, amp=False), f"{m} of {kw['m']} rows of X against {n} of {kw['n']} output channels"
 
@@ -154,7 +164,7 @@ def metric_name(name):
 
 
 def dtype_of(name):
-    return {"c1_fused_reduce": "f32", "c2_transposed_softmax": "f32", "c3_gemm_bias_gelu": "bf16", "c4_causal_attention": "bf16", "c5_fp8_weight_gemm": "f8e4m3"}[name]
+    return {"c1_fused_reduce": "f32", "c2_transposed_softmax": "f32", "c3_gemm_bias_gelu": "bf16", "c4_causal_attention": "bf16", "c5_fp8_weight_gemm": "f8e4m3", "n3_quant_gemv": "int4 x bf16"}[name]
 
 
 def unit_of(name):
@@ -182,6 +192,10 @@ def cpu_evaluator(name, kw):
         shape, dt = g.shape(node), g.dtype(node)
         if dt == api.F8E4M3:
             feeds.set(node, rng.integers(0, 0x78, shape, dtype=np.uint8) | (rng.integers(0, 2, shape, dtype=np.uint8) << 7), dt)
+        elif dt == api.U8:
+            feeds.set(node, rng.integers(0, 256, shape, dtype=np.uint8), dt)
+        elif dt == api.F16:
+            feeds.set(node, rng.uniform(0.004, 0.012, shape).astype(np.float16).view(np.uint16), dt)
         elif dt == api.BF16:
             feeds.set(node, api.f32_to_bf16(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.05 if name != "c4_causal_attention" else 1.0)), dt)
         else:
@@ -546,7 +560,7 @@ def main():
         kw = dict(WORKLOADS[nm][1])
         if args.scale != 1.0:
             for k in kw:
-                if k != "dh":
+                if k != "dh" and not (nm in ONE_GPU_ONLY and k in ("m", "bits", "group")):
                     kw[k] = max(128, int(kw[k] * args.scale) // 128 * 128)
         return kw
     kw = sizes(name)
@@ -554,11 +568,13 @@ def main():
         return reference_arm(args, name, kw)
 
     s = Session()
+    if name in ONE_GPU_ONLY and s.world > 1:
+        raise SystemExit(f"{name} is measured on one GPU only")
     head = measure(s, name, kw, args.steps, args.warmup, 0 if args.no_e2e else max(3, min(args.steps, 10)), 0 if args.no_cpu_baseline else 8.0, True)
     others = {}
     if args.workload is None and not args.only_headline and args.scale == 1.0:
         for nm in WORKLOADS:
-            if nm == name:
+            if nm == name or (nm in ONE_GPU_ONLY and s.world > 1):
                 continue
             k2 = sizes(nm)
             r = measure(s, nm, k2, max(5, min(args.steps, 20)), 3, 0 if args.no_e2e else 3, 0 if args.no_cpu_baseline else 2.0, True)

@@ -123,3 +123,18 @@ def fp8_weight_gemm(g: api.Graph, m=16384, kdim=8192, n=28672, amp=True):
         return h.cast(h.div(wf, h.broadcast_to(sc, [kdim, n])), api.F8E4M3)
     gens = {X: lambda h: h.cast(h.randn([m, kdim], k[0]), api.BF16), Wq: gen_wq, scales: gen_scales}
     return out, gens
+
+
+def quant_gemv(g: api.Graph, m=1, n=28672, kdim=8192, bits=4, group=128):
+    """Decode step of a weight-only quantised projection (Op::QuantMatmul): m activation rows in bf16 against
+    [n, kdim] weights packed `bits` wide with f16 scale and minimum per `group` columns."""
+    kb, ng = kdim * bits // 8, kdim // group
+    act, qw = g.input([m, kdim], api.BF16), g.input([n, kb], api.U8)
+    sc, mn = g.input([n, ng], api.F16), g.input([n, ng], api.F16)
+    out = g.quant_matmul(act, qw, sc, mn, bits, group)
+    k = split_n(5, 4)
+    gens = {act: lambda h: h.cast(h.randn([m, kdim], k[0]), api.BF16),
+            qw: lambda h: h.cast(h.rand_range([n, kb], k[1], 0.0, 256.0), api.U8),        # every byte value, i.e. every pair of fields
+            sc: lambda h: h.cast(h.rand_range([n, ng], k[2], 0.004, 0.012), api.F16),
+            mn: lambda h: h.cast(h.rand_range([n, ng], k[3], -0.09, -0.03), api.F16)}
+    return out, gens

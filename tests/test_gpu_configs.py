@@ -255,3 +255,27 @@ def test_c5_full_size_random_rows_against_the_f64_run(oracle_lib, cuda_lib, gpu)
     util.assert_band(want, util.to_f64(got, api.BF16), 2e-2, STEP_BF16, "c5 full size, 64 random rows vs f64 run")
     assert ((w & 0x7F) != 0x7F).all()                            # no NaN codes in the quantised weights
     assert (util.to_f64(w, api.F8E4M3).__abs__().max(axis=0) == 448).all()   # every channel uses the full e4m3 range
+
+
+def test_quantised_decode_step_full_size_channels_against_the_f64_run(oracle_lib, cuda_lib, cpu64, gpu):
+    """The decode-step workload of the bench (one bf16 activation row against [28672, 8192] 4-bit weights): 2048 output
+    channels, eight in every 112-row stretch so that every CTA of the kernel's one wave is sampled, against the f64
+    interpreter run on those rows of the packed weight, scales and minima."""
+    g = api.Graph(cuda_lib)
+    root, gens = configs.quant_gemv(g)
+    assert api.compile_check(cuda_lib, g, [root]) == ["quant_gemv"]
+    dev = device_inputs(cuda_lib, gpu, gens)
+    out = gpu.eval_device(g, [root], None, dev)[0].numpy()
+    (an, qn, sn, mn) = list(gens)
+    rng = np.random.default_rng(8)
+    rows = np.sort(np.concatenate([b0 + rng.choice(112, 8, replace=False) for b0 in range(0, 28672, 112)]))
+    assert len(rows) == 2048
+    act, qw, sc, mins = (dev[n].numpy() for n in (an, qn, sn, mn))
+    assert len(np.unique(qw[rows])) == 256                                  # every byte value: every field value in both positions
+    go = api.Graph(oracle_lib)
+    ro, gens_o = configs.quant_gemv(go, n=len(rows))
+    (ao, qo, so, mo) = list(gens_o)
+    f = api.Feeds(oracle_lib).set(ao, act, api.BF16).set(qo, np.ascontiguousarray(qw[rows]), api.U8)
+    f.set(so, np.ascontiguousarray(sc[rows]), api.F16).set(mo, np.ascontiguousarray(mins[rows]), api.F16)
+    want = cpu64.eval_with(go, ro, f).numpy()
+    util.assert_band(want, util.to_f64(out[:, rows], api.BF16), 2.0 ** -7, STEP_BF16, "quantised decode step, 2048 channels vs f64 run")
