@@ -472,6 +472,9 @@ def measure_e2e(s: Session, name: str, nbytes: int, flops: float, w: dict, n_ste
         same = bool(np.allclose(host_out.view(np.float32), want.view(np.float32), rtol=1e-5, atol=1e-12))
     else:
         same = bool(np.array_equal(host_out[:out_bytes], want))
+        if not same and g.dtype(root) == api.BF16:   # a chunk of few rows may take the one-SM form of the contraction kernel: one bf16 step
+            fa, fb = (api.bf16_to_f32(v[:out_bytes].view(np.uint16)).astype(np.float64) for v in (host_out, want))
+            same = bool((np.abs(fa - fb) <= 2.0 ** -7 * np.maximum(np.abs(fa), np.abs(fb)) + 1e-30).all())
     h2d = int(sum(t.nbytes for t in tensors.values()))
     for t in tensors.values():
         t.free()

@@ -30,7 +30,7 @@
 #define KU_LOG2E 1.4426950408889634f
 // the fused producer reads its other operands at coordinates clamped into the tensor: tiles overhang the last
 // lines / positions, and what is computed there is masked or never stored
-#define KU_CI(i) ((R % 32 != 0 && (i) >= R) ? R - 1 : (i))
+#define KU_CI(i) ((R % PWL != 0 && (i) >= R) ? R - 1 : (i))
 #define KU_CJ(j) ((C % JT != 0 && (j) >= C) ? C - 1 : (j))
 #define TILE_BYTES (JT * 128)
 #define SPIN_LIMIT (1u << 22)
@@ -316,6 +316,9 @@ ku_softmax_panels_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
       }
       const int q = warp;   // this warp writes lines i0 + 4q .. i0 + 4q + 3
       const float4 c4 = *(const float4*)&line_c[n & 1][q * 4];
+      // the last panel may hold fewer than its 8 strips of 32 lines: a strip past the last line has nothing to write
+      // (its tile is zero fill, its item still counts)
+      if ((R % PWL == 0) || i0 < R) {
       // lane = position within a 32-position strip; one 16-byte load gives 4 lines at that position,
       // then 4 warp-wide stores of 128 contiguous bytes each
 #pragma unroll 4
@@ -335,6 +338,7 @@ ku_softmax_panels_tma(const __grid_constant__ KuTmap tmap, KU_SRC_PARAMS_LEAD vo
           if ((R % 32 == 0) || i0 + q * 4 + 2 < R) KU_STORE(&o[2 * (i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.z, KU_LOG2E, -c4.z))));
           if ((R % 32 == 0) || i0 + q * 4 + 3 < R) KU_STORE(&o[3 * (i64)C], KU_ENC(ku_ex2(__fmaf_rn(v.w, KU_LOG2E, -c4.w))));
         }
+      }
       }
     }
     if (warp == 0) {   // hand the look-ahead to the next iteration

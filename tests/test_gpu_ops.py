@@ -290,6 +290,32 @@ def test_large_transposed_softmax_ragged_and_special_lines(oracle_lib, cuda_lib,
     assert abs(got[6, 1234] - 1.0) < 1e-6 and np.count_nonzero(got[6]) == 1
 
 
+@pytest.mark.parametrize("n,m", [(8192, 128), (4096, 288)])
+def test_transposed_softmax_with_a_short_last_panel(oracle_lib, cuda_lib, cpu64, gpu, n, m):
+    """The panel kernel cuts the lines into panels of 256: a line count that is a multiple of 32 but not of 256 leaves the
+    last panel with fewer than its eight strips (a row shard of the softmax configuration on eight GPUs, streamed in
+    eight chunks, is 128 lines). Strips past the last line write nothing: the result is right and the inputs, which lie
+    next to the result in device memory, are untouched."""
+    rng = np.random.default_rng(22)
+    Lv, bv = rng_f32(rng, (n, m), 2.0), rng.uniform(-1, 1, n).astype(np.float32)
+    g = api.Graph(cuda_lib)
+    L, bias = g.input([n, m], api.F32), g.input([n], api.F32)
+    out = g.softmax(g.add(g.permute(L, [1, 0]), g.broadcast_to(bias, [m, n])), 1)
+    assert api.compile_check(cuda_lib, g, [out]) == ["softmax_panels_tma"]
+    dL, db = gpu.upload(Lv), gpu.upload(bv)
+    tail = gpu.upload(np.full((m, n), 7.0, np.float32))            # allocations around the result's
+    got = gpu.eval_device(g, [out], None, {L: dL, bias: db})[0]
+    tail2 = gpu.upload(np.full((m, n), 9.0, np.float32))
+    for _ in range(2):
+        got.free()
+        got = gpu.eval_device(g, [out], None, {L: dL, bias: db})[0]
+    x = Lv.T.astype(np.float64) + bv.astype(np.float64)[None, :]
+    e = np.exp(x - x.max(axis=1, keepdims=True))
+    util.assert_close(e / e.sum(axis=1, keepdims=True), got.numpy(), 1e-5, 1e-12, f"panels, {m} lines of {n}")
+    assert np.array_equal(dL.numpy(), Lv) and np.array_equal(db.numpy(), bv)
+    assert (tail.numpy() == 7.0).all() and (tail2.numpy() == 9.0).all()
+
+
 def test_softmax_special_values(oracle_lib, cuda_lib, cpu, gpu):
     p = Pair(oracle_lib, cuda_lib)
     v = np.zeros((4, 256), np.float32)

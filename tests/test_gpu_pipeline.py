@@ -15,6 +15,13 @@ CASES = [
     (configs.gemm_bias_gelu, dict(m=4096, n=1024, kdim=1024)),
     (configs.causal_attention, dict(batch=8, heads=4, seq=1024, dh=128, fused=True)),
     (configs.fp8_weight_gemm, dict(m=4096, kdim=1024, n=2048, amp=True)),
+    # what one of eight ranks evaluates of each full-size configuration: the chunks of a shard are the smallest pieces
+    # the kernels meet (128 softmax lines, 64 rows of a reduction, 128 rows of a contraction, 4 heads)
+    (configs.fused_reduce, dict(rows=512, cols=4096)),
+    (configs.transposed_softmax, dict(n=8192, lines=1024)),
+    (configs.gemm_bias_gelu, dict(m=1024, n=8192, kdim=8192)),
+    (configs.causal_attention, dict(batch=1, heads=32, seq=4096, dh=128)),
+    (configs.fp8_weight_gemm, dict(m=2048, kdim=8192, n=28672, amp=True)),
 ]
 
 
@@ -36,10 +43,20 @@ def test_chunked_host_evaluation_equals_one_piece(cuda_lib, gpu, make, kwargs):
     def same(a, b):
         if make is configs.transposed_softmax:   # a chunk of lines may run another softmax kernel (another summation order): the f32 band applies
             return a.shape == b.shape and np.allclose(a, b, rtol=1e-5, atol=1e-12)
-        return a.shape == b.shape and a.tobytes() == b.tobytes()
+        if a.shape == b.shape and a.tobytes() == b.tobytes():
+            return True
+        # a chunk of few rows may take the one-SM form of the contraction kernel instead of the SM-pair form: the same
+        # products, accumulated in f32 in another grouping, so results may differ by one rounding step of bf16
+        if chunked.dtype != api.BF16 or a.shape != b.shape:
+            return False
+        fa, fb = api.bf16_to_f32(a).astype(np.float64), api.bf16_to_f32(b).astype(np.float64)
+        return bool((np.abs(fa - fb) <= 2.0 ** -7 * np.maximum(np.abs(fa), np.abs(fb)) + 1e-30).all())
     assert same(got, one_piece)
     # it really ran in chunks: several launches of the same program, and exactly the input / output bytes crossed the bus
-    assert after["launches"] - before["launches"] >= 8
+    if make is configs.causal_attention and kwargs["batch"] == 1:
+        assert after["launches"] - before["launches"] == 1      # attention separates over the batch axis only: one piece
+    else:
+        assert after["launches"] - before["launches"] >= 8
     assert after["h2d_bytes"] - before["h2d_bytes"] == sum(d.nbytes for d in dev.values())
     assert after["d2h_bytes"] - before["d2h_bytes"] == one_piece.nbytes
     # a second call replays the cached pipeline
