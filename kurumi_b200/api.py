@@ -525,6 +525,28 @@ class CudaBackend(Backend):
         s, r = _sz(shape)
         return DevTensor(self, self.lib.lib.ku_cuda_upload_bytes(self.h, C.c_uint32(dtype), C.c_void_p(ptr), C.c_size_t(nbytes), s, C.c_size_t(r)))
 
+    def prepare_device_step(self, g: Graph, nodes, dev_feeds: dict):
+        """A repeated device-resident evaluation with the argument marshalling done once: returns step() -> DevTensor of
+        the first root (ku_cuda_eval_device with a kept ku_cuda_dev_feeds handle) and close(). For loops whose evaluations
+        take tens of microseconds, where rebuilding the feeds handle per call would be the larger part of a step."""
+        L = self.lib.lib
+        ids = (C.c_uint32 * max(len(nodes), 1))(*nodes)
+        out = (C.c_void_p * max(len(nodes), 1))()
+        n = C.c_size_t(len(nodes))
+        df = C.c_void_p(L.ku_cuda_dev_feeds_new())
+        for node, t in dev_feeds.items():
+            L.ku_cuda_dev_feeds_set(df, C.c_uint32(node), t.h)
+        fn, gh, bh = L.ku_cuda_eval_device, g.h, self.h
+
+        def step():
+            if fn(gh, ids, n, bh, None, df, out) != 0:
+                raise Error(self.lib.last_error())
+            return DevTensor(self, out[0])
+
+        def close():
+            L.ku_cuda_dev_feeds_free(df)
+        return step, close
+
     def eval_device(self, g: Graph, nodes, feeds: Feeds | None = None, dev_feeds: dict | None = None) -> list:
         ids = (C.c_uint32 * max(len(nodes), 1))(*nodes)
         out = (C.c_void_p * max(len(nodes), 1))()
