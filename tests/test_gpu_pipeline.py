@@ -22,6 +22,12 @@ CASES = [
     (configs.gemm_bias_gelu, dict(m=1024, n=8192, kdim=8192)),
     (configs.causal_attention, dict(batch=1, heads=32, seq=4096, dh=128)),
     (configs.fp8_weight_gemm, dict(m=2048, kdim=8192, n=28672, amp=True)),
+    # and one of four ranks
+    (configs.fused_reduce, dict(rows=1024, cols=4096)),
+    (configs.transposed_softmax, dict(n=8192, lines=2048)),
+    (configs.gemm_bias_gelu, dict(m=2048, n=8192, kdim=8192)),
+    (configs.causal_attention, dict(batch=2, heads=32, seq=4096, dh=128)),
+    (configs.fp8_weight_gemm, dict(m=4096, kdim=8192, n=28672, amp=True)),
 ]
 
 
@@ -56,7 +62,7 @@ def test_chunked_host_evaluation_equals_one_piece(cuda_lib, gpu, make, kwargs):
     if make is configs.causal_attention and kwargs["batch"] == 1:
         assert after["launches"] - before["launches"] == 1      # attention separates over the batch axis only: one piece
     else:
-        assert after["launches"] - before["launches"] >= 8
+        assert after["launches"] - before["launches"] >= 2
     assert after["h2d_bytes"] - before["h2d_bytes"] == sum(d.nbytes for d in dev.values())
     assert after["d2h_bytes"] - before["d2h_bytes"] == one_piece.nbytes
     # a second call replays the cached pipeline
