@@ -192,12 +192,18 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer ----
+      // A thread that issues alone runs a handful of clocks per instruction: the descriptors are built once per tile and
+      // stepped by constants (the start-address field counts 16-byte units and never carries out of its 14 bits here),
+      // so that an MMA costs its issuer two additions, not two descriptor constructions.
+      const unsigned long long qd0 = ku_smem_desc(q_s, 16, 1024), qd1 = ku_smem_desc(q_s + Q_BYTES, 16, 1024);
       auto issue_s = [&](int t, int j) {   // S_t = Q_t K_j^T (K_j has been waited for by the caller)
         const int st = j % NKS;
+        const unsigned long long qd = t ? qd1 : qd0, kd = ku_smem_desc(k_s + st * TILE_BYTES, 16, 1024);
+        const unsigned d = tmem_base + t * 128;
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
-          const unsigned off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          ku_mma(tmem_base + t * 128, ku_smem_desc(q_s + t * Q_BYTES + off, 16, 1024), ku_smem_desc(k_s + st * TILE_BYTES + off, 16, 1024), IDESC_S, kk != 0);
+          const unsigned long long off = (unsigned long long)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          ku_mma(d, qd + off, kd + off, IDESC_S, kk != 0);
         }
         ku_mma_commit(ku_smem(&s_full[t]));
       };
@@ -205,9 +211,11 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
         const int st = j % NVS;
         ku_wait(ku_smem(&p_ready[t]), j & 1, failed, status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned long long vd = ku_smem_desc(v_s + st * TILE_BYTES, 16384, 1024);
+        const unsigned d = tmem_base + 256 + t * 128, a = tmem_base + t * 128;
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk)
-          ku_mma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, ku_smem_desc(v_s + st * TILE_BYTES + kk * 16 * 128, 16384, 1024), IDESC_O, (j | kk) != 0);
+          ku_mma_ts(d, a + kk * 8, vd + (unsigned long long)((kk * 16 * 128) >> 4), IDESC_O, (j | kk) != 0);
         ku_mma_commit(ku_smem(&o_full[t]));
       };
       ku_wait(ku_smem(q_full), 0, failed, status);
