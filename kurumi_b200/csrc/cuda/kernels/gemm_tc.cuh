@@ -169,18 +169,23 @@ ku_gemm_tc(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTmap
           ku_wait(ku_smem(&full_bar[s]), (it / STAGES) & 1, failed, status);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const unsigned sa = smem_s + s * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
-#pragma unroll
-          for (int k = 0; k < BKB / 32; ++k) {  // 32 bytes of K per instruction
+          // descriptors built once per stage and stepped by constants (the start-address field counts 16-byte units and
+          // does not carry out of its 14 bits inside shared memory): the issuing thread runs alone on its warp, a handful
+          // of clocks per instruction, and a narrow tile's MMA executes in 32 to 64 clocks
 #if A_MN
-            const unsigned long long ad = ku_smem_desc(sa + k * (32 / ESIZE) * 128, BK * 128, 1024);
+          const unsigned long long ad0 = ku_smem_desc(sa, BK * 128, 1024);
 #else
-            const unsigned long long ad = ku_smem_desc(sa + k * 32, 16, 1024);
+          const unsigned long long ad0 = ku_smem_desc(sa, 16, 1024);
 #endif
 #if B_MN
-            const unsigned long long bd = ku_smem_desc(sb + k * (32 / ESIZE) * 128, BK * 128, 1024);
+          const unsigned long long bd0 = ku_smem_desc(sb, BK * 128, 1024);
 #else
-            const unsigned long long bd = ku_smem_desc(sb + k * 32, 16, 1024);
+          const unsigned long long bd0 = ku_smem_desc(sb, 16, 1024);
 #endif
+#pragma unroll
+          for (int k = 0; k < BKB / 32; ++k) {  // 32 bytes of K per instruction
+            const unsigned long long ad = ad0 + (unsigned long long)((A_MN ? k * (32 / ESIZE) * 128 : k * 32) >> 4);
+            const unsigned long long bd = bd0 + (unsigned long long)((B_MN ? k * (32 / ESIZE) * 128 : k * 32) >> 4);
             ku_mma(d_tmem, ad, bd, IDESC, (kb | k) != 0);
           }
           ku_mma_commit(ku_smem(&empty_bar[s]));  // the stage is free once these MMAs have read it
