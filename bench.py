@@ -7,7 +7,8 @@
 A "step" is one evaluation of the workload graph over one batch of seeded synthetic input. The headline workload
 is configuration 2 of the baseline (view-fused row softmax through a transpose view, f32 [8192, 8192] + bias): the
 metric is achieved HBM GB/s = algorithmic bytes (one read of L, one read of the bias, one write of the output) /
-device time. The other four configurations are measured in the same run and reported under "workloads".
+device time. The other four configurations, and the decode step of a weight-only quantised projection (one GPU only),
+are measured in the same run and reported under "workloads".
 
 With N > 1 the ONE named problem is sharded by rows (ku_graph_row_split): rank r evaluates rows [r, r + 1) * M / N
 on its slices of the row-wise inputs and on all of the replicated ones; there is no collective on the data path,
@@ -555,11 +556,11 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="kurumi_b200", choices=["kurumi_b200", "reference"])
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS), help="measure this workload alone (default: configuration 2 as the headline, the other four beside it)")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS), help="measure this workload alone (default: configuration 2 as the headline, the others beside it)")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (profiling captures); 1.0 = the baseline's size")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--only-headline", action="store_true", help="skip the other four configurations")
+    ap.add_argument("--only-headline", action="store_true", help="skip the other workloads")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     name = args.workload or HEADLINE

@@ -61,7 +61,7 @@ def gpu(cuda_lib):
 
 def pytest_terminal_summary(terminalreporter):
     """Achieved errors of the narrow-format parity checks (relative where the relative band applies, and in units of
-    the row scale), and a copy under gpurun_out/ for the results table."""
+    the row scale); also written to the file KURUMI_PARITY_LOG names, when it is set."""
     from tests import util
     if not util.PARITY_LOG:
         return
@@ -69,9 +69,11 @@ def pytest_terminal_summary(terminalreporter):
     lines = [f"  {what}: {rel:.3e}, {scaled:.3e}" for what, rel, scaled in util.PARITY_LOG]
     for ln in lines:
         terminalreporter.write_line(ln)
-    try:
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-        with open(os.path.join(ROOT, "gpurun_out", "parity_errors.txt"), "w") as f:
-            f.write("\n".join(lines) + "\n")
-    except OSError:
-        pass
+    path = os.environ.get("KURUMI_PARITY_LOG")
+    if path:
+        try:
+            os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+            with open(path, "w") as f:
+                f.write("\n".join(lines) + "\n")
+        except OSError:
+            pass
