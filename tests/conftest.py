@@ -11,6 +11,11 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+    # The kernels are compiled at run time by whichever libnvrtc.so.12 the process holds first: the toolkit's, or the one
+    # bundled with torch when torch was imported before the library (the benchmark does that). KURUMI_TEST_TORCH_FIRST=1
+    # runs the suite in the second situation.
+    if os.environ.get("KURUMI_TEST_TORCH_FIRST"):
+        import torch  # noqa: F401
 
 
 @pytest.fixture(scope="session")
