@@ -81,3 +81,59 @@ def test_backward_graph_of_the_gemm_configuration_from_a_blob(oracle_lib, cuda_l
         # against the bf16 interpreter the contraction band applies; the f64 run, which rounds nothing on the way, is further off
         util.assert_band(util.to_f64(nat.numpy(), api.BF16), util.to_f64(b.numpy(), api.BF16), 2e-2, 2.0 ** -7, f"backward of gemm + bias + gelu vs bf16 interpreter, {name}")
         util.assert_band(a.numpy(), util.to_f64(b.numpy(), api.BF16), 4e-2, 2.0 ** -6, f"backward of gemm + bias + gelu vs f64 run, {name}")
+
+
+def attention_backward(g, b, h, s, dh):
+    """The reverse-mode graph of configuration 4 for a cotangent dOut, written out as the reference's VJP of Op::Sdpa emits it
+    (kurumi_core/src/grad/nn.rs:52-92): P is recomputed exactly as the forward computes it (batched dot_general, scalar
+    scale, additive causal bias, softmax over the keys), then dV = P^T dOut, dP = dOut V^T,
+    dS = P * (dP - rowsum(dP * P)), dQ = scale dS K, dK = scale dS^T Q. Primitives only; the bias arrives as an input."""
+    shape, r = [b, h, s, dh], 4
+    q, k, v, ct = (g.input(shape, api.BF16) for _ in range(4))
+    bias = g.input([s, s], api.BF16)                              # 0 on and below the diagonal, -inf above
+    batch = [0, 1]
+    scale = 1.0 / np.sqrt(dh)
+    raw = g.dot_general(q, k, [r - 1], [r - 1], batch, batch)
+    scores = g.add(g.mul(raw, g.scalar(raw, scale)), g.broadcast_to(bias, [b, h, s, s]))
+    p = g.softmax(scores, r - 1)
+    dv = g.dot_general(p, ct, [r - 2], [r - 2], batch, batch)
+    dp = g.dot_general(ct, v, [r - 1], [r - 1], batch, batch)
+    rs = g.sum(g.mul(dp, p), r - 1)
+    diff = g.add(dp, g.neg(g.broadcast_to(g.reshape(rs, [b, h, s, 1]), [b, h, s, s])))
+    draw = g.mul(g.mul(p, diff), g.scalar(p, scale))
+    dq = g.dot_general(draw, k, [r - 1], [r - 2], batch, batch)
+    dk = g.dot_general(draw, q, [r - 2], [r - 2], batch, batch)
+    return (q, k, v, ct, bias), (dq, dk, dv)
+
+
+def test_backward_graph_of_the_attention_configuration_from_a_blob(oracle_lib, cuda_lib, cpu, cpu64, gpu):
+    b, h, s, dh = 1, 2, 256, 64
+    go = api.Graph(oracle_lib)
+    ins_o, outs_o = attention_backward(go, b, h, s, dh)
+    names = ("Q", "K", "V", "dOut", "bias")
+    blob = go.serialize(list(outs_o), [(node, 1, name) for node, name in zip(ins_o, names)], reachable=True)
+    gc, entries = api.deserialize(cuda_lib, blob)
+    (_, outs, ins) = entries[0]
+    by_name = {name: node for node, _, name in ins}
+    rng = np.random.default_rng(34)
+    vals = {n: rng.standard_normal((b, h, s, dh)).astype(np.float32) for n in names[:4]}
+    vals["bias"] = np.where(np.arange(s)[None, :] > np.arange(s)[:, None], -np.inf, 0.0).astype(np.float32)
+    fo, fc = api.Feeds(oracle_lib), api.Feeds(cuda_lib)
+    for node_o, name in zip(ins_o, names):
+        bits = api.f32_to_bf16(vals[name])
+        fo.set(node_o, bits, api.BF16)
+        fc.set(by_name[name], bits, api.BF16)
+    fams = api.compile_check(cuda_lib, gc, outs)
+    assert sum(f.startswith("gemm") for f in fams) >= 5, fams     # the five batched contractions run as contraction kernels
+    got = gpu.eval_many_with(gc, outs, fc)
+    want = cpu64.eval_many_with(go, list(outs_o), fo)
+    native = cpu.eval_many_with(go, list(outs_o), fo)
+    for name, a, nat, c in zip(("dQ", "dK", "dV"), want, native, got):
+        assert c.shape == (b, h, s, dh)
+        # every intermediate ([.., S, S] scores, probabilities, their cotangents) is rounded to bf16, on the device as in the
+        # interpreter: the contraction band against the bf16 interpreter, a wider one against the f64 run that rounds nothing
+        util.assert_band(util.to_f64(nat.numpy(), api.BF16), util.to_f64(c.numpy(), api.BF16), 2e-2, 2.0 ** -7, f"backward of causal attention vs bf16 interpreter, {name}")
+        util.assert_band(a.numpy(), util.to_f64(c.numpy(), api.BF16), 4e-2, 2.0 ** -6, f"backward of causal attention vs f64 run, {name}")
+    # causality: key t receives nothing from queries before it; the last key's dK / dV come from the last query alone
+    dV = util.to_f64(got[2].numpy(), api.BF16)
+    assert np.isfinite(dV).all()
