@@ -45,10 +45,10 @@ from kurumi_b200 import api, build, configs  # noqa: E402
 NCU_TRAFFIC = {
     ("c1_fused_reduce", "reduce_rows"): (137.8e6, "profiles/reduce_rows__c1_fused_reduce.txt", "kurumi_b200/csrc/cuda/emit.cc", "cdbd748c4a972952"),
     ("c2_transposed_softmax", "softmax_groups_tma"): (478.7e6, "profiles/softmax_groups_tma__c2_transposed_softmax.txt", "kurumi_b200/csrc/cuda/kernels/softmax_groups_tma.cuh", "dd8c62b067697094"),
-    ("c3_gemm_bias_gelu", "gemm_tc"): (1231e6, "profiles/gemm_tc2__c3_gemm_bias_gelu.txt", "kurumi_b200/csrc/cuda/kernels/gemm_tc2.cuh", "c72951635c0e95f9"),
-    ("c4_causal_attention", "attention_tc"): (1057e6, "profiles/attention_tc__c4_causal_attention.txt", "kurumi_b200/csrc/cuda/kernels/attention_tc.cuh", "e610b020adc079de"),
+    ("c3_gemm_bias_gelu", "gemm_tc"): (1251e6, "profiles/gemm_tc2__c3_gemm_bias_gelu.txt", "kurumi_b200/csrc/cuda/kernels/gemm_tc2.cuh", "df0ad6236b887218"),
+    ("c4_causal_attention", "attention_tc"): (1057.5e6, "profiles/attention_tc__c4_causal_attention.txt", "kurumi_b200/csrc/cuda/kernels/attention_tc.cuh", "e76ea16f0699bdc8"),
     ("n3_quant_gemv", "quant_gemv"): (128.5e6, "profiles/quant_gemv_mma__n3_quant_gemv.txt", "kurumi_b200/csrc/cuda/kernels/quant_gemv_mma.cuh", "34c98aeb544694c7"),
-    ("c5_fp8_weight_gemm", "gemm_tc_f8"): (3556e6, "profiles/gemm_tc2_f8__c5_fp8_weight_gemm.txt", "kurumi_b200/csrc/cuda/kernels/gemm_tc2.cuh", "c72951635c0e95f9"),
+    ("c5_fp8_weight_gemm", "gemm_tc_f8"): (4236e6, "profiles/gemm_tc2_f8__c5_fp8_weight_gemm.txt", "kurumi_b200/csrc/cuda/kernels/gemm_tc2.cuh", "df0ad6236b887218"),
 }
 
 WORKLOADS = {

@@ -170,13 +170,13 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
         for (int c = 0; c < DCH; ++c) ku_tma_3d(q_s + t * Q_BYTES + c * 16384, &tmap_q, c * 64, (2 * qp + t) * BQ, bh, ku_smem(q_full));
       auto load_k = [&](int j) {
         const int st = j % NKS;
-        ku_wait(ku_smem(&k_empty[st]), ((j / NKS) & 1) ^ 1, failed, status);
+        if (!ku_wait(ku_smem(&k_empty[st]), ((j / NKS) & 1) ^ 1, failed, status)) return;   // after a failed wait no copy is started that nothing would wait for
         ku_mbar_expect(ku_smem(&k_full[st]), TILE_BYTES);
         for (int c = 0; c < DCH; ++c) ku_tma_3d(k_s + st * TILE_BYTES + c * 16384, &tmap_k, c * 64, j * BKV, bh, ku_smem(&k_full[st]));
       };
       auto load_v = [&](int j) {
         const int st = j % NVS;
-        ku_wait(ku_smem(&v_empty[st]), ((j / NVS) & 1) ^ 1, failed, status);
+        if (!ku_wait(ku_smem(&v_empty[st]), ((j / NVS) & 1) ^ 1, failed, status)) return;
         ku_mbar_expect(ku_smem(&v_full[st]), TILE_BYTES);
         for (int c = 0; c < DCH; ++c) ku_tma_3d(v_s + st * TILE_BYTES + c * 16384, &tmap_v, c * 64, j * BKV, bh, ku_smem(&v_full[st]));
       };
@@ -209,7 +209,7 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
       };
       auto issue_pv = [&](int t, int j) {   // O_t += P_t V_j: P_t from tensor memory (16 keys = 8 columns), V MN-major from shared memory
         const int st = j % NVS;
-        ku_wait(ku_smem(&p_ready[t]), j & 1, failed, status);
+        if (!ku_wait(ku_smem(&p_ready[t]), j & 1, failed, status)) return;   // no instruction is issued on operands that may not be there
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned long long vd = ku_smem_desc(v_s + st * TILE_BYTES, 16384, 1024);
         const unsigned d = tmem_base + 256 + t * 128, a = tmem_base + t * 128;
@@ -229,6 +229,7 @@ ku_attention_tc_duo(const __grid_constant__ KuTmap tmap_q, const __grid_constant
         ku_wait(ku_smem(&v_full[st]), (j / NVS) & 1, failed, status);
         if (j < n0) issue_pv(0, j);
         if (j + 1 < n1) ku_wait(ku_smem(&k_full[nx]), ((j + 1) / NKS) & 1, failed, status);
+        if (failed) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (j + 1 < n0) issue_s(0, j + 1);
         issue_pv(1, j);

@@ -133,13 +133,13 @@ ku_gemm_tc(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTmap
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer ----
       int it = 0;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
         int b, mb, nb;
         ku_tile_coords(t, b, mb, nb);
         for (int kb = 0; kb < KBLOCKS; ++kb, ++it) {
           const int s = it % STAGES;
           const unsigned ph = (it / STAGES) & 1;
-          ku_wait(ku_smem(&empty_bar[s]), ph ^ 1, failed, status);  // first pass over the ring: passes at once
+          if (!ku_wait(ku_smem(&empty_bar[s]), ph ^ 1, failed, status)) break;  // first pass over the ring: passes at once; after a failed wait no copy is started that nothing would wait for
           const unsigned fb = ku_smem(&full_bar[s]);
           ku_mbar_expect(fb, STAGE_BYTES);
           const unsigned sa = smem_s + s * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
@@ -159,14 +159,14 @@ ku_gemm_tc(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTmap
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer ----
       int it = 0, local = 0;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+      for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x, ++local) {
         const int acc = local & 1;
         ku_wait(ku_smem(&tmem_empty[acc]), ((local >> 1) & 1) ^ 1, failed, status);  // the epilogue has drained this accumulator
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < KBLOCKS; ++kb, ++it) {
           const int s = it % STAGES;
-          ku_wait(ku_smem(&full_bar[s]), (it / STAGES) & 1, failed, status);
+          if (!ku_wait(ku_smem(&full_bar[s]), (it / STAGES) & 1, failed, status)) break;   // no instruction is issued on operands that may not be there
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const unsigned sa = smem_s + s * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
           // descriptors built once per stage and stepped by constants (the start-address field counts 16-byte units and

@@ -138,14 +138,14 @@ ku_gemm_tc2(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTma
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer (both CTAs) ----
       int it = 0;
-      for (int t = pair; t < total_tiles; t += npairs) {
+      for (int t = pair; t < total_tiles && !failed; t += npairs) {
         int b, mb, nb;
         ku_tile_coords(t, b, mb, nb);
         const int row0 = mb * 256 + (int)rank * BM, col0 = nb * BN + (int)rank * BNH;
         for (int kb = 0; kb < KBLOCKS; ++kb, ++it) {
           const int s = it % STAGES;
           const unsigned ph = (it / STAGES) & 1;
-          ku_wait(ku_smem(&empty_bar[s]), ph ^ 1, failed, status);  // first pass over the ring: passes at once
+          if (!ku_wait(ku_smem(&empty_bar[s]), ph ^ 1, failed, status)) break;  // first pass over the ring: passes at once; after a failed wait no copy is started that nothing would wait for
           const unsigned fb = ku_mapa(ku_smem(&full_bar[s]), 0);    // the leader's barrier collects both halves
           if (rank == 0) ku_mbar_expect(ku_smem(&full_bar[s]), 2 * STAGE_BYTES);
           const unsigned sa = smem_s + s * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
@@ -165,14 +165,14 @@ ku_gemm_tc2(const __grid_constant__ KuTmap tmap_a, const __grid_constant__ KuTma
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {  // ---- MMA issuer (leader only) ----
       int it = 0, local = 0;
-      for (int t = pair; t < total_tiles; t += npairs, ++local) {
+      for (int t = pair; t < total_tiles && !failed; t += npairs, ++local) {
         const int acc = local & 1;
         ku_wait(ku_smem(&tmem_empty[acc]), ((local >> 1) & 1) ^ 1, failed, status);  // both epilogues have drained this accumulator
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < KBLOCKS; ++kb, ++it) {
           const int s = it % STAGES;
-          ku_wait(ku_smem(&full_bar[s]), (it / STAGES) & 1, failed, status);
+          if (!ku_wait(ku_smem(&full_bar[s]), (it / STAGES) & 1, failed, status)) break;   // no instruction is issued on operands that may not be there
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const unsigned sa = smem_s + s * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
 #pragma unroll
