@@ -652,6 +652,45 @@ Emitted emit_arg_reduce(const Fused& f, size_t axis, bool arg_min, int sm_count)
   o << device_prelude();
   Emitted e;
   e.leaf_args = g.args;
+  if (inner == 1 && len >= 256) {
+    // The axis is the innermost one and long: a CTA per line. A thread walks positions t, t + 256, ... in index order with
+    // the interpreter's rule among the elements it sees (a NaN never becomes the best; strict comparison, so the first of
+    // equal values stays); partial results merge by value, then by lower index, which is the same first-maximum; a NaN in
+    // position 0 is never replaced, so that line answers 0.
+    const std::string T = ctype(d);
+    o << "template <class T> __device__ __forceinline__ T ku_shfl_down_any(T v, int dlt) {\n"
+         "  union { T t; unsigned long long u; } x; x.u = 0ull; x.t = v; x.u = __shfl_down_sync(0xffffffffu, x.u, dlt); return x.t;\n}\n";
+    o << "#define KU_BETTER(av, ak, bv, bk) ((av) " << (arg_min ? "<" : ">") << " (bv) || ((av) == (bv) && (ak) < (bk)))\n";
+    o << "extern \"C\" __global__ void __launch_bounds__(256) ku_arg_rows(" << g.params() << "void* __restrict__ out) {\n";
+    o << "  __shared__ " << T << " s_v[8];\n  __shared__ i64 s_k[8];\n  __shared__ int s_h[8];\n";
+    o << "  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;\n";
+    o << "  for (" << g.idx_t << " o = blockIdx.x; o < " << outs << "; o += gridDim.x) {\n";
+    o << "    const " << g.idx_t << " oo = o;\n";
+    if (ax > 0) o << decompose("oo", sp.dims, 0, ax, g.idx_t, "c", "    ");
+    o << "    " << T << " best = 0;\n    i64 best_k = 0;\n    int has = 0, first_nan = 0;\n";
+    o << "    for (" << g.idx_t << " k = threadIdx.x; k < " << len << "; k += 256) {\n";
+    {
+      std::vector<std::string> lv(f.leaves.size());
+      for (size_t li = 0; li < f.leaves.size(); ++li) lv[li] = g.leaf_value(li, coords);
+      o << g.body(lv, "      ");
+    }
+    o << "      const " << T << " v = v" << f.root << ";\n";
+    o << "      if (k == 0 && v != v) first_nan = 1;\n";
+    o << "      if (v == v && (!has || v " << (arg_min ? "<" : ">") << " best)) { best = v; best_k = (i64)k; has = 1; }\n    }\n";
+    o << "    for (int dlt = 16; dlt > 0; dlt >>= 1) {\n";
+    o << "      const " << T << " ov = ku_shfl_down_any(best, dlt); const i64 ok = ku_shfl_down_any(best_k, dlt); const int oh = __shfl_down_sync(0xffffffffu, has, dlt);\n";
+    o << "      if (oh && (!has || KU_BETTER(ov, ok, best, best_k))) { best = ov; best_k = ok; has = 1; }\n    }\n";
+    o << "    if (lane == 0) { s_v[warp] = best; s_k[warp] = best_k; s_h[warp] = has; }\n    __syncthreads();\n";
+    o << "    if (threadIdx.x == 0) {\n";
+    o << "      for (int w = 1; w < 8; ++w) if (s_h[w] && (!has || KU_BETTER(s_v[w], s_k[w], best, best_k))) { best = s_v[w]; best_k = s_k[w]; has = 1; }\n";
+    o << "      ((i64*)out)[o] = (first_nan || !has) ? (i64)0 : best_k;\n    }\n    __syncthreads();\n  }\n}\n";
+    e.entry = "ku_arg_rows";
+    e.block = 256;
+    e.grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(outs, static_cast<int64_t>(sm_count) * 8)));
+    e.family = "arg_rows";
+    e.source = o.str();
+    return e;
+  }
   o << "extern \"C\" __global__ void __launch_bounds__(256) ku_arg_fold(" << g.params() << "void* __restrict__ out) {\n";
   o << "  for (" << g.idx_t << " o = blockIdx.x * 256 + threadIdx.x; o < " << outs << "; o += (" << g.idx_t << ")gridDim.x * 256) {\n";
   o << "    const " << g.idx_t << " oi = o % " << inner << ", oo = o / " << inner << ";\n";

@@ -90,3 +90,39 @@ def test_device_matches_the_oracle(oracle_lib, cuda_lib, cpu, gpu, dtype):
                 out = (g.argmin if arg_min else g.argmax)(y, axis)
                 outs.append(be.eval_with(g, out, api.Feeds(lib).set(x, v, dtype)).numpy())
             np.testing.assert_array_equal(outs[0], outs[1])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [api.F32, api.F64, api.BF16, api.I32, api.I8, api.U64])
+def test_long_innermost_lines_take_a_cta_per_line(oracle_lib, cuda_lib, cpu, gpu, dtype):
+    """A long innermost axis (the sampling head: argmax over the vocabulary) runs one CTA per line; partial results merge by
+    value and then by lower index, which must equal the interpreter's first-maximum walk: ties everywhere, NaNs at the
+    start, in the middle and at the end of a line, a line of NaNs, a line of one repeated value, +-inf and +-0."""
+    rng = np.random.default_rng(6)
+    lines, n = 9, 3001
+    if dtype in (api.F32, api.F64, api.BF16):
+        v = rng.integers(-4, 5, (lines, n)).astype(np.float64)      # many ties
+        v[1, 0] = np.nan                                            # a leading NaN is never replaced
+        v[2, 1500] = np.nan; v[2, n - 1] = np.nan
+        v[3, :] = np.nan
+        v[4, :] = 2.0
+        v[5, 17] = np.inf; v[5, 2900] = np.inf; v[5, 40] = -np.inf
+        v[6, :] = 0.0; v[6, 5] = -0.0; v[6, 2000] = -0.0              # -0 == +0: the first position wins either way
+        v[7, 1:] = np.nan                                           # only position 0 is a number
+        carrier = v.astype(np.float32) if dtype == api.F32 else v if dtype == api.F64 else api.f32_to_bf16(v.astype(np.float32))
+    elif dtype == api.U64:
+        carrier = rng.integers(0, 3, (lines, n)).astype(np.uint64) + np.uint64(2 ** 63)
+    else:
+        carrier = rng.integers(-3, 4, (lines, n)).astype(np.int32 if dtype == api.I32 else np.int8)
+    for arg_min in (False, True):
+        outs = []
+        for lib, be in ((oracle_lib, cpu), (cuda_lib, gpu)):
+            g = api.Graph(lib)
+            x = g.input([lines, n], dtype)
+            out = (g.argmin if arg_min else g.argmax)(x, 1)
+            if lib is cuda_lib:
+                assert api.compile_check(lib, g, [out]) == ["arg_rows"]
+            outs.append(be.eval_with(g, out, api.Feeds(lib).set(x, carrier, dtype)).numpy())
+        np.testing.assert_array_equal(outs[0], outs[1])
+        if dtype == api.F32:
+            np.testing.assert_array_equal(outs[0], reference(carrier, 1, arg_min))
