@@ -1060,24 +1060,76 @@ Emitted emit_scatter(DType d, DType idx_dt, bool along, uint8_t combine, int64_t
   std::ostringstream o;
   o << device_prelude();
   const int64_t total = pre * post;
-  const std::string S = stype(d), C = ctype(d);
+  // A destination element belongs to exactly one thread, which walks the indices in order: bit-exact and deterministic
+  // whatever the combine. With few columns and many indices that is too few threads, so the destination axis is cut
+  // into NB blocks as well: thread (column, block) scans all of the column's indices, four at a time, and applies those
+  // that fall into its block. The scan is cheap next to the dependent update-row / destination-row accesses it skips.
+  const int64_t want = static_cast<int64_t>(sm_count) * 2048 * 2;
+  const int64_t nb = std::max<int64_t>(1, std::min<int64_t>({(want + total - 1) / std::max<int64_t>(total, 1), da, k / 64 > 0 ? k / 64 : 1, 256}));
+  const int64_t rbs = (da + nb - 1) / nb;
+  const std::string S = stype(d), C = ctype(d), I = stype(idx_dt);
+  auto apply = [&](const std::string& raw, const std::string& ki, const std::string& ind) {
+    o << ind << "const i64 u = (p * " << k << "ll + " << ki << ") * " << post << "ll + j;\n";
+    o << ind << S << "* dst = (" << S << "*)out + (p * " << da << "ll + " << raw << ") * " << post << "ll + j;\n";
+    if (combine == 0) {
+      o << ind << "*dst = ((const " << S << "*)upd)[u];\n";
+    } else {
+      o << ind << "const " << C << " a = " << dec(d, "*dst") << ", b = " << dec(d, "((const " + S + "*)upd)[u]") << ";\n";
+      o << ind << "*dst = (" << S << ")" << enc(d, combine_expr(combine, d)) << ";\n";
+    }
+  };
   o << "extern \"C\" __global__ void __launch_bounds__(128) ku_scatter(const void* __restrict__ idx, const void* __restrict__ upd, void* __restrict__ out) {\n";
-  o << "  for (i64 t = (i64)blockIdx.x * 128 + threadIdx.x; t < " << total << "ll; t += (i64)gridDim.x * 128) {\n";
-  o << "    const i64 j = t % " << post << "ll, p = t / " << post << "ll;\n";
-  o << "    for (i64 ki = 0; ki < " << k << "ll; ++ki) {\n";
-  o << "      const i64 u = (p * " << k << "ll + ki) * " << post << "ll + j;\n";
-  o << "      const i64 raw = (i64)((const " << stype(idx_dt) << "*)idx)[" << (along ? "u" : "ki") << "];\n";
-  o << "      if (raw < 0 || raw >= " << da << "ll) continue;\n";
-  o << "      " << S << "* dst = (" << S << "*)out + (p * " << da << "ll + raw) * " << post << "ll + j;\n";
-  if (combine == 0) {
-    o << "      *dst = ((const " << S << "*)upd)[u];\n";
+  if (!along) {
+    // One index list for every column. A CTA is 128 columns of one destination block, so its threads all want the same
+    // indices: a tile of 512 is tested by the CTA once (four indices per thread), the matching positions are packed in
+    // index order (ballot + prefix sums) and every thread applies just those, in that order.
+    const int64_t cchunks = (total + 127) / 128;
+    o << "  __shared__ int s_pos[512];\n  __shared__ i64 s_row[512];\n  __shared__ int s_wsum[4];\n";
+    o << "  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;\n";
+    o << "  for (i64 unit = blockIdx.x; unit < " << nb * cchunks << "ll; unit += gridDim.x) {\n";
+    o << "    const i64 rb = unit / " << cchunks << "ll, t = (unit % " << cchunks << "ll) * 128 + threadIdx.x;\n";
+    o << "    const bool live = t < " << total << "ll;\n";
+    o << "    const i64 lo = rb * " << rbs << "ll, hi = (lo + " << rbs << "ll) < " << da << "ll ? (lo + " << rbs << "ll) : " << da << "ll;\n";
+    o << "    const i64 j = t % " << post << "ll, p = t / " << post << "ll;\n";
+    o << "    for (i64 k0 = 0; k0 < " << k << "ll; k0 += 512) {\n";
+    o << "      i64 raw[4];\n      int cnt = 0;\n";
+    o << "#pragma unroll\n      for (int q = 0; q < 4; ++q) {\n";
+    o << "        const i64 ki = k0 + threadIdx.x * 4 + q;\n";
+    o << "        raw[q] = ki < " << k << "ll ? (i64)((const " << I << "*)idx)[ki] : (i64)-1;\n";
+    o << "        cnt += (raw[q] >= lo && raw[q] < hi) ? 1 : 0;\n      }\n";
+    o << "      int pre = cnt;\n";
+    o << "#pragma unroll\n      for (int dlt = 1; dlt < 32; dlt <<= 1) { const int v = __shfl_up_sync(0xffffffffu, pre, dlt); if (lane >= dlt) pre += v; }\n";
+    o << "      __syncthreads();   // the list of the tile before has been applied\n";
+    o << "      if (lane == 31) s_wsum[warp] = pre;\n      __syncthreads();\n";
+    o << "      int base = pre - cnt;\n      for (int w = 0; w < warp; ++w) base += s_wsum[w];\n";
+    o << "      const int n = s_wsum[0] + s_wsum[1] + s_wsum[2] + s_wsum[3];\n";
+    o << "#pragma unroll\n      for (int q = 0; q < 4; ++q)\n";
+    o << "        if (raw[q] >= lo && raw[q] < hi) { s_pos[base] = threadIdx.x * 4 + q; s_row[base] = raw[q]; ++base; }\n";
+    o << "      __syncthreads();\n";
+    o << "      if (live) {\n        for (int q = 0; q < n; ++q) {\n          const i64 row = s_row[q];\n";
+    apply("row", "(k0 + s_pos[q])", "          ");
+    o << "        }\n      }\n    }\n    __syncthreads();\n  }\n}\n";
   } else {
-    o << "      const " << C << " a = " << dec(d, "*dst") << ", b = " << dec(d, "((const " + S + "*)upd)[u]") << ";\n";
-    o << "      *dst = (" << S << ")" << enc(d, combine_expr(combine, d)) << ";\n";
+    o << "  for (i64 tt = (i64)blockIdx.x * 128 + threadIdx.x; tt < " << total * nb << "ll; tt += (i64)gridDim.x * 128) {\n";
+    o << "    const i64 t = tt % " << total << "ll, rb = tt / " << total << "ll;\n";
+    o << "    const i64 lo = rb * " << rbs << "ll, hi = (lo + " << rbs << "ll) < " << da << "ll ? (lo + " << rbs << "ll) : " << da << "ll;\n";
+    o << "    const i64 j = t % " << post << "ll, p = t / " << post << "ll;\n";
+    o << "    for (i64 k0 = 0; k0 < " << k << "ll; k0 += 4) {\n";
+    o << "      i64 raw[4];\n";
+    o << "#pragma unroll\n      for (int q = 0; q < 4; ++q) {\n";
+    o << "        const i64 ki = k0 + q;\n";
+    o << "        raw[q] = ki < " << k << "ll ? (i64)((const " << I << "*)idx)[(p * " << k << "ll + ki) * " << post << "ll + j] : (i64)-1;\n";
+    o << "      }\n";
+    o << "#pragma unroll\n      for (int q = 0; q < 4; ++q) {\n";
+    o << "        if (raw[q] < lo || raw[q] >= hi) continue;\n";
+    apply("raw[q]", "(k0 + q)", "        ");
+    o << "      }\n    }\n  }\n}\n";
   }
-  o << "    }\n  }\n}\n";
   Emitted e;
-  e.source = o.str(); e.entry = "ku_scatter"; e.block = 128; e.grid = pick_grid(total, 128, sm_count, 8); e.family = along ? "scatter_along" : "scatter";
+  e.source = o.str(); e.entry = "ku_scatter"; e.block = 128;
+  e.grid = along ? pick_grid(total * nb, 128, sm_count, 8)
+                 : static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(nb * ((total + 127) / 128), static_cast<int64_t>(sm_count) * 16)));
+  e.family = along ? "scatter_along" : "scatter";
   return e;
 }
 

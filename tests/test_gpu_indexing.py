@@ -85,3 +85,26 @@ def test_embedding_lookup_and_its_gradient_shape(oracle_lib, cuda_lib, cpu, gpu)
     util.assert_exact(o[0], c[0], "embedding rows")
     util.assert_exact(o[1], c[1], "embedding gradient (scatter-add in index order)")
     assert api.compile_check(cuda_lib, p.gc, [rows]) == ["gather"]
+
+
+@pytest.mark.parametrize("combine", [0, 1, 3])
+def test_scatter_with_many_indices_and_few_columns(oracle_lib, cuda_lib, cpu, gpu, combine):
+    """Few destination columns and thousands of indices: the device cuts the destination axis into blocks (a thread per
+    column and block scans all indices, four at a time, and applies its own in order). Still bit for bit the
+    interpreter's index-order fold: duplicates pile up on some rows, out-of-range indices are skipped, the index count is
+    not a multiple of four, float sums depend on the order."""
+    rng = np.random.default_rng(60 + combine)
+    rows, cols, k = 1003, 24, 5003
+    p = Pair(oracle_lib, cuda_lib)
+    x = p.feed((rows, cols), api.F32, rng.standard_normal((rows, cols)).astype(np.float32))
+    iv = rng.integers(-5, rows + 5, k).astype(np.int64)
+    iv[:200] = 17; iv[-3:] = rows - 1                                    # a hot row, and the tail of the last group of four
+    idx = p.feed((k,), api.I64, iv)
+    up = p.feed((k, cols), api.F32, (rng.standard_normal((k, cols)) * 100).astype(np.float32))
+    xa = p.feed((cols, rows), api.BF16, api.f32_to_bf16(rng.standard_normal((cols, rows)).astype(np.float32)))
+    ia = p.feed((cols, k), api.I32, rng.integers(-3, rows + 3, (cols, k)).astype(np.int32))
+    ua = p.feed((cols, k), api.BF16, api.f32_to_bf16(rng.standard_normal((cols, k)).astype(np.float32)))
+    nodes = [p.scatter(x, idx, up, 0, combine), p.scatter_along(xa, ia, ua, 1, combine)]
+    o, c, _ = p.run(cpu, gpu, nodes)
+    for n, (a, b) in enumerate(zip(o, c)):
+        util.assert_exact(a, b, f"scatter node {n}, combine {combine}")
