@@ -1176,4 +1176,69 @@ Emitted emit_argsort(DType d, bool descending, int64_t outer, int64_t len, int64
   return e;
 }
 
+// Argsort along an axis longer than one CTA's shared memory holds: the same bitonic network over (key, original index)
+// pairs, run on a padded copy in global scratch. Chunks of ASL_CH pairs are sorted in shared memory (all stages up to
+// k = ASL_CH); for the larger k the steps with j >= ASL_CH are one global compare-exchange launch each and the steps
+// below are finished per chunk in shared memory again. The direction of a compare depends on the pair's position in
+// the whole line, so the pieces compose to the one network, and the result is the same stable permutation.
+// Entry points: ku_asl_chunks(src, keys, ids), ku_asl_global(keys, ids, k, j), ku_asl_local(keys, ids, k), ku_asl_out(ids, out).
+Emitted emit_argsort_long(DType d, bool descending, int64_t outer, int64_t len, int64_t inner, int64_t* lpad_out, size_t* key_bytes_out) {
+  int64_t lpad = 1;
+  while (lpad < len) lpad <<= 1;
+  const size_t key_bytes = d == DType::F64 || dtype_width(d) == 8 ? 8 : 4;
+  const std::string S = stype(d), C = is_float(d) ? (d == DType::F64 ? "double" : "float") : key_bytes == 8 ? ctype(d) : is_signed(d) ? "i32" : "u32";
+  std::ostringstream o;
+  o << device_prelude();
+  o << "#define LEN " << len << "ll\n#define LPAD " << lpad << "ll\n#define INNER " << inner << "ll\n#define LINES " << outer * inner << "ll\n#define ASL_CH 4096\n";
+  o << "typedef " << C << " key_t;\n";
+  o << "__device__ __forceinline__ bool ku_before(key_t ka, int ia, key_t kb, int ib) {\n";
+  o << "  if (ia >= LEN || ib >= LEN) return ia < ib;\n";
+  o << "  const bool lt = " << (descending ? "ka > kb" : "ka < kb") << ", gt = " << (descending ? "ka < kb" : "ka > kb") << ";\n";
+  o << "  return lt || (!gt && ia < ib);\n}\n";
+  // steps j = j_hi .. 1 of stage k on one chunk in shared memory; gi0 = position of the chunk's first pair in its line
+  o << "__device__ __forceinline__ void ku_asl_steps(key_t* keys, int* ids, i64 gi0, i64 k, int j_hi) {\n";
+  o << "  for (int j = j_hi; j > 0; j >>= 1) {\n";
+  o << "    for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) {\n";
+  o << "      const int l = i ^ j;\n      if (l > i) {\n";
+  o << "        const key_t ka = keys[i], kb = keys[l];\n        const int ia = ids[i], ib = ids[l];\n";
+  o << "        const bool up = ((gi0 + i) & k) == 0;\n";
+  o << "        if (ku_before(kb, ib, ka, ia) == up) { keys[i] = kb; keys[l] = ka; ids[i] = ib; ids[l] = ia; }\n";
+  o << "      }\n    }\n    __syncthreads();\n  }\n}\n";
+  o << "extern \"C\" __global__ void __launch_bounds__(1024) ku_asl_chunks(const void* __restrict__ src, key_t* __restrict__ gkeys, int* __restrict__ gids) {\n";
+  o << "  __shared__ key_t keys[ASL_CH];\n  __shared__ int ids[ASL_CH];\n";
+  o << "  const i64 cpl = LPAD / ASL_CH, line = blockIdx.x / cpl, gi0 = (blockIdx.x % cpl) * ASL_CH;\n";
+  o << "  const i64 po = line / INNER, pi = line % INNER;\n";
+  o << "  const " << S << "* base = (const " << S << "*)src + po * LEN * INNER + pi;\n";
+  o << "  for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) {\n";
+  o << "    const i64 gi = gi0 + i;\n    ids[i] = (int)gi;\n    keys[i] = gi < LEN ? (key_t)" << dec(d, "base[gi * INNER]") << " : (key_t)0;\n  }\n";
+  o << "  __syncthreads();\n";
+  o << "  for (i64 k = 2; k <= ASL_CH; k <<= 1) ku_asl_steps(keys, ids, gi0, k, (int)(k >> 1));\n";
+  o << "  for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) { gkeys[line * LPAD + gi0 + i] = keys[i]; gids[line * LPAD + gi0 + i] = ids[i]; }\n}\n";
+  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_asl_global(key_t* __restrict__ gkeys, int* __restrict__ gids, long long k, long long j) {\n";
+  o << "  const i64 pairs = LINES * (LPAD / 2);\n";
+  o << "  for (i64 q = (i64)blockIdx.x * 256 + threadIdx.x; q < pairs; q += (i64)gridDim.x * 256) {\n";
+  o << "    const i64 line = q / (LPAD / 2), pq = q % (LPAD / 2);\n";
+  o << "    const i64 i = (pq / j) * 2 * j + (pq % j), l = i + j;\n";
+  o << "    key_t* kk = gkeys + line * LPAD;\n    int* ii = gids + line * LPAD;\n";
+  o << "    const key_t ka = kk[i], kb = kk[l];\n    const int ia = ii[i], ib = ii[l];\n";
+  o << "    const bool up = (i & k) == 0;\n";
+  o << "    if (ku_before(kb, ib, ka, ia) == up) { kk[i] = kb; kk[l] = ka; ii[i] = ib; ii[l] = ia; }\n  }\n}\n";
+  o << "extern \"C\" __global__ void __launch_bounds__(1024) ku_asl_local(key_t* __restrict__ gkeys, int* __restrict__ gids, long long k) {\n";
+  o << "  __shared__ key_t keys[ASL_CH];\n  __shared__ int ids[ASL_CH];\n";
+  o << "  const i64 cpl = LPAD / ASL_CH, line = blockIdx.x / cpl, gi0 = (blockIdx.x % cpl) * ASL_CH;\n";
+  o << "  for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) { keys[i] = gkeys[line * LPAD + gi0 + i]; ids[i] = gids[line * LPAD + gi0 + i]; }\n";
+  o << "  __syncthreads();\n";
+  o << "  ku_asl_steps(keys, ids, gi0, k, ASL_CH / 2);\n";
+  o << "  for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) { gkeys[line * LPAD + gi0 + i] = keys[i]; gids[line * LPAD + gi0 + i] = ids[i]; }\n}\n";
+  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_asl_out(const int* __restrict__ gids, void* __restrict__ out) {\n";
+  o << "  const i64 total = LINES * LEN;\n";
+  o << "  for (i64 q = (i64)blockIdx.x * 256 + threadIdx.x; q < total; q += (i64)gridDim.x * 256) {\n";
+  o << "    const i64 line = q / LEN, r = q % LEN, po = line / INNER, pi = line % INNER;\n";
+  o << "    ((i64*)out)[po * LEN * INNER + r * INNER + pi] = (i64)gids[line * LPAD + r];\n  }\n}\n";
+  Emitted e;
+  e.source = o.str(); e.entry = "ku_asl_chunks"; e.family = "argsort";
+  *lpad_out = lpad; *key_bytes_out = key_bytes;
+  return e;
+}
+
 }  // namespace ku::cu

@@ -144,6 +144,8 @@ Emitted emit_softmax(const Fused& f, OpKind kind, size_t axis, float eps, int sm
 Emitted emit_gather(DType d, DType idx_dt, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count);
 Emitted emit_gather_along(DType d, DType idx_dt, int64_t outer, int64_t da, int64_t la, int64_t inner, int sm_count);
 Emitted emit_scatter(DType d, DType idx_dt, bool along, uint8_t combine, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count);
+// The same for longer lines: four entry points over a padded copy in global scratch (see emit.cc)
+Emitted emit_argsort_long(DType d, bool descending, int64_t outer, int64_t len, int64_t inner, int64_t* lpad_out, size_t* key_bytes_out);
 Emitted emit_argsort(DType d, bool descending, int64_t outer, int64_t len, int64_t inner, int sm_count);
 
 struct GemmDesc {

@@ -1,3 +1,4 @@
+#include <cstring>
 #include "sched.h"
 
 #include <cstdio>
@@ -645,8 +646,40 @@ Fused Scheduler::indexing(const Node& n, const std::vector<Fused>& in) {
       int64_t lpad = 1;
       while (lpad < da) lpad <<= 1;
       const int64_t key = (dt == DType::F64 || dtype_width(dt) == 8) ? 8 : 4;
-      if (lpad * (key + 4) > 200 * 1024) throw Error::backend("argsort along an axis of " + std::to_string(da) + " elements is longer than the sorting kernel holds in shared memory");
-      launch(emit_argsort(dt, op.descending, pre, da, post, sm_), {x.root_leaf().slot, slot});
+      if (lpad * (key + 4) > 200 * 1024) {
+        // longer than one CTA's shared memory: the same network over a padded copy in global scratch, chunk sorts and the
+        // narrow steps in shared memory, the wide steps one launch each
+        if (da >= (int64_t(1) << 30)) throw Error::backend("argsort along an axis of " + std::to_string(da) + " elements: positions are kept in 32 bits");
+        int64_t lp = 0;
+        size_t kb = 0;
+        const Emitted e = emit_argsort_long(dt, op.descending, pre, da, post, &lp, &kb);
+        const int64_t lines = pre * post, ch = 4096;
+        const size_t ids_off = (static_cast<size_t>(lines * lp) * kb + 255) / 256 * 256;
+        const int scratch = new_slot(Slot::Temp, DType::U8, {ids_off + static_cast<size_t>(lines * lp) * 4});
+        auto step = [&](const char* entry, unsigned grid, unsigned block, std::initializer_list<Arg> args, double bytes) {
+          Launch L;
+          L.name = e.family;
+          L.kernel = (*load_)(e.source, entry, false);
+          L.grid[0] = grid; L.block[0] = block;
+          for (const Arg& a : args) L.args.push_back(a);
+          L.algo_bytes = bytes;
+          prog_.launches.push_back(std::move(L));
+        };
+        auto ptr_arg = [](int sl, size_t off) { Arg a; a.kind = Arg::SlotPtr; a.slot = sl; a.byte_offset = static_cast<int64_t>(off); return a; };
+        auto int_arg = [](int64_t v) { Arg a; a.kind = Arg::Bytes; a.bytes.resize(8); std::memcpy(a.bytes.data(), &v, 8); return a; };
+        const unsigned chunk_ctas = static_cast<unsigned>(lines * (lp / ch));
+        const unsigned wide = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((lines * (lp / 2) + 255) / 256, static_cast<int64_t>(sm_) * 16)));
+        step("ku_asl_chunks", chunk_ctas, 1024, {ptr_arg(x.root_leaf().slot, 0), ptr_arg(scratch, 0), ptr_arg(scratch, ids_off)},
+             static_cast<double>(prog_.slots[static_cast<size_t>(x.root_leaf().slot)].bytes));
+        for (int64_t k = 2 * ch; k <= lp; k <<= 1) {
+          for (int64_t j = k / 2; j >= ch; j >>= 1) step("ku_asl_global", wide, 256, {ptr_arg(scratch, 0), ptr_arg(scratch, ids_off), int_arg(k), int_arg(j)}, 0.0);
+          step("ku_asl_local", chunk_ctas, 1024, {ptr_arg(scratch, 0), ptr_arg(scratch, ids_off), int_arg(k)}, 0.0);
+        }
+        step("ku_asl_out", static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((lines * da + 255) / 256, static_cast<int64_t>(sm_) * 16))), 256,
+             {ptr_arg(scratch, ids_off), ptr_arg(slot, 0)}, static_cast<double>(prog_.slots[static_cast<size_t>(slot)].bytes));
+      } else {
+        launch(emit_argsort(dt, op.descending, pre, da, post, sm_), {x.root_leaf().slot, slot});
+      }
     }
     return buffer_value(slot, DType::I64, n.shape);
   }

@@ -108,3 +108,25 @@ def test_scatter_with_many_indices_and_few_columns(oracle_lib, cuda_lib, cpu, gp
     o, c, _ = p.run(cpu, gpu, nodes)
     for n, (a, b) in enumerate(zip(o, c)):
         util.assert_exact(a, b, f"scatter node {n}, combine {combine}")
+
+
+@pytest.mark.parametrize("descending", [False, True])
+def test_argsort_of_lines_longer_than_shared_memory(oracle_lib, cuda_lib, cpu, gpu, descending):
+    """Lines of more than 16384 elements (a vocabulary) do not fit one CTA's shared memory: the same bitonic network runs over
+    a padded copy in global scratch, 4096-pair chunks and the narrow steps in shared memory, the wide steps one launch
+    each. Same stable permutation as the oracle: many ties, a length that is no power of two, an axis that is not the
+    last one, 64-bit keys, and sort() through the gather that follows."""
+    rng = np.random.default_rng(61)
+    p = Pair(oracle_lib, cuda_lib)
+    ties = rng.integers(0, 50, (2, 40000)).astype(np.float32)          # 3 steps above the chunk size, 16384 < 40000 < 65536
+    x = p.feed((2, 40000), api.F32, ties)
+    xm = p.feed((17001, 3), api.F32, rng.standard_normal((17001, 3)).astype(np.float32))       # sorted along axis 0, inner stride 3
+    xi = p.feed((1, 16400), api.I64, rng.integers(-2 ** 62, 2 ** 62, (1, 16400)).astype(np.int64))
+    xb = p.feed((3, 20000), api.BF16, api.f32_to_bf16(rng.integers(-9, 9, (3, 20000)).astype(np.float32)))
+    nodes = [p.argsort(x, 1, descending), p.argsort(xm, 0, descending), p.argsort(xi, 1, descending), p.argsort(xb, 1, descending), p.sort(x, 1, descending)]
+    # padded to 65536: the chunk sort, then for k = 8192, 16384, 32768, 65536 the 1, 2, 3, 4 wide steps and a local pass each, then the copy out
+    assert api.compile_check(cuda_lib, p.gc, [nodes[0]]).count("argsort") == 1 + (1 + 2 + 3 + 4) + 4 + 1
+    o, c, _ = p.run(cpu, gpu, nodes)
+    for k, (a, b) in enumerate(zip(o, c)):
+        util.assert_exact(a, b, f"long argsort descending={descending} node {k}")
+    assert np.array_equal(c[0], np.argsort(-ties if descending else ties, axis=1, kind="stable"))
