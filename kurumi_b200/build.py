@@ -21,7 +21,7 @@ CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
-SOURCES = ["core/graph.cc", "core/serialize.cc", "core/split.cc", "capi/capi.cc", "lower/view.cc", "cuda/hostmem.cc", "cuda/runtime.cc", "cuda/fuse.cc", "cuda/emit.cc", "cuda/sched.cc",
+SOURCES = ["core/graph.cc", "core/serialize.cc", "core/split.cc", "capi/capi.cc", "lower/view.cc", "cuda/hostmem.cc", "cuda/runtime.cc", "cuda/fuse.cc", "cuda/emit.cc", "cuda/emit_index.cc", "cuda/sched.cc",
            "cuda/kernels.cc", "cuda/backend.cc", "cuda/pipeline.cc", "cuda/comm.cc", "cuda/capi_cuda.cc"]
 
 

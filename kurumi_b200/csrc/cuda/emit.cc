@@ -17,6 +17,7 @@
 #include <functional>
 #include <sstream>
 
+#include "emit_util.h"
 #include "fuse.h"
 
 namespace ku::cu {
@@ -101,14 +102,30 @@ __device__ __forceinline__ float ku_uniform(u64 bits) { return (float)(((u32)bit
 )KU";
 }
 
-namespace {
-
+namespace emitutil {   // shared with emit_index.cc (emit_util.h)
 bool is_lowf(DType d) { return is_low_float(d); }
 std::string rnd(DType d, const std::string& e) { return is_lowf(d) ? "ku_rnd_" + lname(d) + "(" + e + ")" : e; }
 std::string dec(DType d, const std::string& e) { return is_lowf(d) ? "ku_dec_" + lname(d) + "(" + e + ")" : e; }
 std::string enc(DType d, const std::string& e) { return is_lowf(d) ? "ku_enc_" + lname(d) + "(" + e + ")" : e; }
 int bits_of(DType d) { return static_cast<int>(dtype_width(d)) * 8; }
 const char* wrap_utype(DType d) { return dtype_width(d) == 8 ? "u64" : "u32"; }
+unsigned pick_grid(int64_t work_items, unsigned per_block, int sm_count, unsigned blocks_per_sm) {
+  int64_t blocks = (work_items + per_block - 1) / per_block;
+  int64_t cap = static_cast<int64_t>(sm_count) * blocks_per_sm;
+  return static_cast<unsigned>(std::max<int64_t>(1, std::min(blocks, cap)));
+}
+// Grid of a kernel whose CTAs loop over `items` lines, `cap` of them resident at once. Up to eight residencies' worth
+// get a CTA per line: the hardware hands the next line to whichever SM has room, which measured better than a resident
+// grid whose CTAs take 3 or 4 turns each (4096 lines on 1184 CTAs: 0.87 -> 0.90 of the copy rate), and better than
+// fewer CTAs with equal turns (0.78). Beyond that a resident grid loops; the uneven last turn is then under an eighth.
+unsigned line_grid(int64_t items, int64_t cap) {
+  if (items <= cap * 8) return static_cast<unsigned>(std::max<int64_t>(1, items));
+  return static_cast<unsigned>(cap);
+}
+}  // namespace emitutil
+using namespace emitutil;
+
+namespace {
 
 std::string imm_literal(DType d, uint64_t bits) {
   std::ostringstream o;
@@ -382,12 +399,6 @@ std::string decompose(const std::string& lin, const std::vector<int64_t>& dims, 
   return o.str();
 }
 
-unsigned pick_grid(int64_t work_items, unsigned per_block, int sm_count, unsigned blocks_per_sm) {
-  int64_t blocks = (work_items + per_block - 1) / per_block;
-  int64_t cap = static_cast<int64_t>(sm_count) * blocks_per_sm;
-  return static_cast<unsigned>(std::max<int64_t>(1, std::min(blocks, cap)));
-}
-
 // can leaf li be read with one aligned vector of `vec` elements along the innermost dim?
 bool vec_ok(const Fused& f, const Space& sp, size_t li, int vec) {
   const Leaf& l = f.leaves[li];
@@ -565,7 +576,7 @@ Emitted emit_reduce(const Fused& f, OpKind kind, size_t axis, int sm_count) {
     o << "    if (threadIdx.x == 0) ((" << stype(d) << "*)out)[row] = " << enc(d, "a") << ";\n  }\n}\n";
     e.entry = "ku_reduce_rows";
     e.block = 256;
-    e.grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(outer, static_cast<int64_t>(sm_count) * 8)));
+    e.grid = line_grid(outer, static_cast<int64_t>(sm_count) * 8);
     e.family = "reduce_rows";
   } else if (len >= 64 && outer * inner <= static_cast<int64_t>(sm_count) * 512) {
     // few outputs, a long axis (a reduction over rows, a short tensor's last axis): a CTA owns 32 neighbouring outputs and
@@ -668,15 +679,42 @@ Emitted emit_arg_reduce(const Fused& f, size_t axis, bool arg_min, int sm_count)
     o << "    const " << g.idx_t << " oo = o;\n";
     if (ax > 0) o << decompose("oo", sp.dims, 0, ax, g.idx_t, "c", "    ");
     o << "    " << T << " best = 0;\n    i64 best_k = 0;\n    int has = 0, first_nan = 0;\n";
-    o << "    for (" << g.idx_t << " k = threadIdx.x; k < " << len << "; k += 256) {\n";
+    // A thread takes `vec` neighbouring positions per turn (one 128-bit load where a leaf allows it), still in rising
+    // order. Eight turns' loads are issued together before the first comparison: the comparisons form one dependent chain
+    // and the compiler does not lift the loads over it by itself.
+    int vec = 4;
+    while (vec > 1 && len % vec) vec >>= 1;
+    const int turns = 8;
+    std::vector<bool> pre(f.leaves.size(), false);
+    for (size_t li = 0; li < f.leaves.size(); ++li) pre[li] = vec > 1 && vec_ok(f, sp, li, vec);
+    o << "    for (" << g.idx_t << " kk = threadIdx.x * " << vec << "; kk < " << len << "; kk += " << 256 * vec * turns << ") {\n";
+    for (size_t li = 0; li < f.leaves.size(); ++li)
+      if (pre[li]) o << "      " << stype(f.leaves[li].dtype) << " b" << li << "[" << turns << "][" << vec << "];\n";
+    o << "#pragma unroll\n      for (int u = 0; u < " << turns << "; ++u) {\n";
+    o << "        const " << g.idx_t << " k0 = kk + u * " << 256 * vec << ";\n        if (k0 < " << len << ") {\n";
+    std::vector<std::string> c0 = coords;
+    c0[ax] = "k0";
+    for (size_t li = 0; li < f.leaves.size(); ++li) {
+      if (!pre[li]) continue;
+      const std::string st = stype(f.leaves[li].dtype);
+      const size_t bytes = dtype_width(f.leaves[li].dtype) * static_cast<size_t>(vec);
+      const std::string src = "((const " + st + "*)p" + std::to_string(g.ptr_arg[li]) + " + (" + g.offset(li, c0) + "))";
+      if (bytes % 16 == 0) for (size_t q = 0; q < bytes / 16; ++q) o << "          ((uint4*)b" << li << "[u])[" << q << "] = ((const uint4*)" << src << ")[" << q << "];\n";
+      else if (bytes == 8) o << "          *(uint2*)b" << li << "[u] = *(const uint2*)" << src << ";\n";
+      else o << "          *(u32*)b" << li << "[u] = *(const u32*)" << src << ";\n";
+    }
+    o << "        }\n      }\n";
+    o << "#pragma unroll\n      for (int u = 0; u < " << turns << "; ++u) {\n";
+    o << "        const " << g.idx_t << " k0 = kk + u * " << 256 * vec << ";\n        if (k0 >= " << len << ") break;\n";
+    o << "#pragma unroll\n        for (int l = 0; l < " << vec << "; ++l) {\n          const " << g.idx_t << " k = k0 + l;\n";
     {
       std::vector<std::string> lv(f.leaves.size());
-      for (size_t li = 0; li < f.leaves.size(); ++li) lv[li] = g.leaf_value(li, coords);
-      o << g.body(lv, "      ");
+      for (size_t li = 0; li < f.leaves.size(); ++li) lv[li] = pre[li] ? dec(f.leaves[li].dtype, "b" + std::to_string(li) + "[u][l]") : g.leaf_value(li, coords);
+      o << g.body(lv, "          ");
     }
-    o << "      const " << T << " v = v" << f.root << ";\n";
-    o << "      if (k == 0 && v != v) first_nan = 1;\n";
-    o << "      if (v == v && (!has || v " << (arg_min ? "<" : ">") << " best)) { best = v; best_k = (i64)k; has = 1; }\n    }\n";
+    o << "          const " << T << " v = v" << f.root << ";\n";
+    o << "          if (k == 0 && v != v) first_nan = 1;\n";
+    o << "          if (v == v && (!has || v " << (arg_min ? "<" : ">") << " best)) { best = v; best_k = (i64)k; has = 1; }\n        }\n      }\n    }\n";
     o << "    for (int dlt = 16; dlt > 0; dlt >>= 1) {\n";
     o << "      const " << T << " ov = ku_shfl_down_any(best, dlt); const i64 ok = ku_shfl_down_any(best_k, dlt); const int oh = __shfl_down_sync(0xffffffffu, has, dlt);\n";
     o << "      if (oh && (!has || KU_BETTER(ov, ok, best, best_k))) { best = ov; best_k = ok; has = 1; }\n    }\n";
@@ -686,7 +724,7 @@ Emitted emit_arg_reduce(const Fused& f, size_t axis, bool arg_min, int sm_count)
     o << "      ((i64*)out)[o] = (first_nan || !has) ? (i64)0 : best_k;\n    }\n    __syncthreads();\n  }\n}\n";
     e.entry = "ku_arg_rows";
     e.block = 256;
-    e.grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(outs, static_cast<int64_t>(sm_count) * 8)));
+    e.grid = line_grid(outs, static_cast<int64_t>(sm_count) * 8);
     e.family = "arg_rows";
     e.source = o.str();
     return e;
@@ -771,7 +809,7 @@ Emitted emit_softmax(const Fused& f, OpKind kind, size_t axis, float eps, int sm
     o << "      ((" << stype(d) << "*)out)[row * " << len << " + k] = " << enc(d, sm ? "(expf(" + X + " - m) / s)" : "(" + X + " / s)") << ";\n    }\n  }\n}\n";
     e.entry = "ku_line_passes";
     e.block = 256;
-    e.grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(outer, static_cast<int64_t>(sm_count) * 8)));
+    e.grid = line_grid(outer, static_cast<int64_t>(sm_count) * 8);
     e.family = sm ? "softmax_passes" : "rmsnorm_passes";
   } else if (inner == 1 && !dbl && len >= 64 && per <= 64) {
     // one CTA per line; the line lives in registers between the passes: one read, one write
@@ -830,7 +868,7 @@ Emitted emit_softmax(const Fused& f, OpKind kind, size_t axis, float eps, int sm
     o << "      }\n    }\n  }\n}\n";
     e.entry = "ku_line_regs";
     e.block = NT;
-    e.grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(outer, static_cast<int64_t>(sm_count) * 8)));
+    e.grid = line_grid(outer, static_cast<int64_t>(sm_count) * 8);
     e.family = sm ? "softmax_rows" : "rmsnorm_rows";
   } else {
     // one thread per line, three passes; adjacent threads take adjacent inner positions
@@ -1003,241 +1041,6 @@ Emitted emit_gemm_simt(const GemmDesc& gd, const Fused* epi, int sm_count) {
   e.block = 256;
   e.family = "gemm_simt";
   (void)sm_count;
-  return e;
-}
-
-// ---- indexing and sorting -------------------------------------------------------------------------
-// Kernels over contiguous row-major buffers (the scheduler writes operands out first). The semantics are the
-// interpreter's, kurumi_core/src/interp/indexing/{gather,scatter}.rs and interp/sort.rs: gathers clamp an out-of-range
-// index, scatters drop it, updates fold into the copy of the operand in index order (so results are bit-exact and
-// deterministic: every destination element is owned by one thread, which walks the indices in order), sorting is stable.
-namespace {
-std::string combine_expr(uint8_t combine, DType d) {   // old value `a`, update `b`, both in the dtype's register type
-  const std::string C = ctype(d), U = wrap_utype(d);
-  const bool flt = is_float(d);
-  switch (combine) {
-    case 0: return "b";
-    case 1: return flt ? "(a + b)" : "(" + C + ")((" + U + ")a + (" + U + ")b)";
-    case 2: return flt ? (d == DType::F64 ? "fmax(a, b)" : "fmaxf(a, b)") : "(a > b ? a : b)";
-    default: return flt ? (d == DType::F64 ? "fmin(a, b)" : "fminf(a, b)") : "(a < b ? a : b)";
-  }
-}
-}  // namespace
-
-Emitted emit_gather(DType d, DType idx_dt, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count) {
-  std::ostringstream o;
-  o << device_prelude();
-  const int64_t total = pre * k * post;
-  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_gather(const void* __restrict__ src, const void* __restrict__ idx, void* __restrict__ out) {\n";
-  o << "  for (i64 e = (i64)blockIdx.x * 256 + threadIdx.x; e < " << total << "ll; e += (i64)gridDim.x * 256) {\n";
-  o << "    const i64 j = e % " << post << "ll, ki = (e / " << post << "ll) % " << k << "ll, p = e / " << (post * k) << "ll;\n";
-  o << "    i64 a = (i64)((const " << stype(idx_dt) << "*)idx)[ki];\n";
-  o << "    a = a < 0 ? 0 : (a > " << (da - 1) << "ll ? " << (da - 1) << "ll : a);\n";
-  o << "    ((" << stype(d) << "*)out)[e] = ((const " << stype(d) << "*)src)[(p * " << da << "ll + a) * " << post << "ll + j];\n  }\n}\n";
-  Emitted e;
-  e.source = o.str(); e.entry = "ku_gather"; e.block = 256; e.grid = pick_grid(total, 256, sm_count, 8); e.family = "gather";
-  return e;
-}
-
-Emitted emit_gather_along(DType d, DType idx_dt, int64_t outer, int64_t da, int64_t la, int64_t inner, int sm_count) {
-  std::ostringstream o;
-  o << device_prelude();
-  const int64_t total = outer * la * inner;
-  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_gather_along(const void* __restrict__ src, const void* __restrict__ idx, void* __restrict__ out) {\n";
-  o << "  for (i64 e = (i64)blockIdx.x * 256 + threadIdx.x; e < " << total << "ll; e += (i64)gridDim.x * 256) {\n";
-  o << "    const i64 pi = e % " << inner << "ll, po = e / " << (la * inner) << "ll;\n";
-  o << "    i64 a = (i64)((const " << stype(idx_dt) << "*)idx)[e];\n";
-  o << "    a = a < 0 ? 0 : (a > " << (da - 1) << "ll ? " << (da - 1) << "ll : a);\n";
-  o << "    ((" << stype(d) << "*)out)[e] = ((const " << stype(d) << "*)src)[(po * " << da << "ll + a) * " << inner << "ll + pi];\n  }\n}\n";
-  Emitted e;
-  e.source = o.str(); e.entry = "ku_gather_along"; e.block = 256; e.grid = pick_grid(total, 256, sm_count, 8); e.family = "gather_along";
-  return e;
-}
-
-// `out` already holds the copy of the operand. Scatter: thread per (p, j) walks the k indices; ScatterAlong (along = true):
-// thread per line (po, pi) walks the la positions of the index tensor. [pre | outer, da, post | inner] is the operand.
-Emitted emit_scatter(DType d, DType idx_dt, bool along, uint8_t combine, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count) {
-  std::ostringstream o;
-  o << device_prelude();
-  const int64_t total = pre * post;
-  // A destination element belongs to exactly one thread, which walks the indices in order: bit-exact and deterministic
-  // whatever the combine. With few columns and many indices that is too few threads, so the destination axis is cut
-  // into NB blocks as well: thread (column, block) scans all of the column's indices, four at a time, and applies those
-  // that fall into its block. The scan is cheap next to the dependent update-row / destination-row accesses it skips.
-  const int64_t want = static_cast<int64_t>(sm_count) * 2048 * 2;
-  const int64_t nb = std::max<int64_t>(1, std::min<int64_t>({(want + total - 1) / std::max<int64_t>(total, 1), da, k / 64 > 0 ? k / 64 : 1, 256}));
-  const int64_t rbs = (da + nb - 1) / nb;
-  const std::string S = stype(d), C = ctype(d), I = stype(idx_dt);
-  auto apply = [&](const std::string& raw, const std::string& ki, const std::string& ind) {
-    o << ind << "const i64 u = (p * " << k << "ll + " << ki << ") * " << post << "ll + j;\n";
-    o << ind << S << "* dst = (" << S << "*)out + (p * " << da << "ll + " << raw << ") * " << post << "ll + j;\n";
-    if (combine == 0) {
-      o << ind << "*dst = ((const " << S << "*)upd)[u];\n";
-    } else {
-      o << ind << "const " << C << " a = " << dec(d, "*dst") << ", b = " << dec(d, "((const " + S + "*)upd)[u]") << ";\n";
-      o << ind << "*dst = (" << S << ")" << enc(d, combine_expr(combine, d)) << ";\n";
-    }
-  };
-  o << "extern \"C\" __global__ void __launch_bounds__(128) ku_scatter(const void* __restrict__ idx, const void* __restrict__ upd, void* __restrict__ out) {\n";
-  if (!along) {
-    // One index list for every column. A CTA is 128 columns of one destination block, so its threads all want the same
-    // indices: a tile of 512 is tested by the CTA once (four indices per thread), the matching positions are packed in
-    // index order (ballot + prefix sums) and every thread applies just those, in that order.
-    const int64_t cchunks = (total + 127) / 128;
-    o << "  __shared__ int s_pos[512];\n  __shared__ i64 s_row[512];\n  __shared__ int s_wsum[4];\n";
-    o << "  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;\n";
-    o << "  for (i64 unit = blockIdx.x; unit < " << nb * cchunks << "ll; unit += gridDim.x) {\n";
-    o << "    const i64 rb = unit / " << cchunks << "ll, t = (unit % " << cchunks << "ll) * 128 + threadIdx.x;\n";
-    o << "    const bool live = t < " << total << "ll;\n";
-    o << "    const i64 lo = rb * " << rbs << "ll, hi = (lo + " << rbs << "ll) < " << da << "ll ? (lo + " << rbs << "ll) : " << da << "ll;\n";
-    o << "    const i64 j = t % " << post << "ll, p = t / " << post << "ll;\n";
-    o << "    for (i64 k0 = 0; k0 < " << k << "ll; k0 += 512) {\n";
-    o << "      i64 raw[4];\n      int cnt = 0;\n";
-    o << "#pragma unroll\n      for (int q = 0; q < 4; ++q) {\n";
-    o << "        const i64 ki = k0 + threadIdx.x * 4 + q;\n";
-    o << "        raw[q] = ki < " << k << "ll ? (i64)((const " << I << "*)idx)[ki] : (i64)-1;\n";
-    o << "        cnt += (raw[q] >= lo && raw[q] < hi) ? 1 : 0;\n      }\n";
-    o << "      int pre = cnt;\n";
-    o << "#pragma unroll\n      for (int dlt = 1; dlt < 32; dlt <<= 1) { const int v = __shfl_up_sync(0xffffffffu, pre, dlt); if (lane >= dlt) pre += v; }\n";
-    o << "      __syncthreads();   // the list of the tile before has been applied\n";
-    o << "      if (lane == 31) s_wsum[warp] = pre;\n      __syncthreads();\n";
-    o << "      int base = pre - cnt;\n      for (int w = 0; w < warp; ++w) base += s_wsum[w];\n";
-    o << "      const int n = s_wsum[0] + s_wsum[1] + s_wsum[2] + s_wsum[3];\n";
-    o << "#pragma unroll\n      for (int q = 0; q < 4; ++q)\n";
-    o << "        if (raw[q] >= lo && raw[q] < hi) { s_pos[base] = threadIdx.x * 4 + q; s_row[base] = raw[q]; ++base; }\n";
-    o << "      __syncthreads();\n";
-    o << "      if (live) {\n        for (int q = 0; q < n; ++q) {\n          const i64 row = s_row[q];\n";
-    apply("row", "(k0 + s_pos[q])", "          ");
-    o << "        }\n      }\n    }\n    __syncthreads();\n  }\n}\n";
-  } else {
-    o << "  for (i64 tt = (i64)blockIdx.x * 128 + threadIdx.x; tt < " << total * nb << "ll; tt += (i64)gridDim.x * 128) {\n";
-    o << "    const i64 t = tt % " << total << "ll, rb = tt / " << total << "ll;\n";
-    o << "    const i64 lo = rb * " << rbs << "ll, hi = (lo + " << rbs << "ll) < " << da << "ll ? (lo + " << rbs << "ll) : " << da << "ll;\n";
-    o << "    const i64 j = t % " << post << "ll, p = t / " << post << "ll;\n";
-    o << "    for (i64 k0 = 0; k0 < " << k << "ll; k0 += 4) {\n";
-    o << "      i64 raw[4];\n";
-    o << "#pragma unroll\n      for (int q = 0; q < 4; ++q) {\n";
-    o << "        const i64 ki = k0 + q;\n";
-    o << "        raw[q] = ki < " << k << "ll ? (i64)((const " << I << "*)idx)[(p * " << k << "ll + ki) * " << post << "ll + j] : (i64)-1;\n";
-    o << "      }\n";
-    o << "#pragma unroll\n      for (int q = 0; q < 4; ++q) {\n";
-    o << "        if (raw[q] < lo || raw[q] >= hi) continue;\n";
-    apply("raw[q]", "(k0 + q)", "        ");
-    o << "      }\n    }\n  }\n}\n";
-  }
-  Emitted e;
-  e.source = o.str(); e.entry = "ku_scatter"; e.block = 128;
-  e.grid = along ? pick_grid(total * nb, 128, sm_count, 8)
-                 : static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(nb * ((total + 127) / 128), static_cast<int64_t>(sm_count) * 16)));
-  e.family = along ? "scatter_along" : "scatter";
-  return e;
-}
-
-// One CTA per line: a bitonic network over (key, original index) pairs in shared memory. The pairs are totally ordered
-// (equal keys order by index), so the network's result is the stable permutation; padding sorts last.
-Emitted emit_argsort(DType d, bool descending, int64_t outer, int64_t len, int64_t inner, int sm_count) {
-  int64_t lpad = 1;
-  while (lpad < len) lpad <<= 1;
-  // keys are held in at least 32 bits (the index array behind them stays aligned)
-  const size_t key_bytes = d == DType::F64 || dtype_width(d) == 8 ? 8 : 4;
-  const std::string S = stype(d), C = is_float(d) ? (d == DType::F64 ? "double" : "float") : key_bytes == 8 ? ctype(d) : is_signed(d) ? "i32" : "u32";
-  std::ostringstream o;
-  o << device_prelude();
-  o << "#define LEN " << len << "\n#define LPAD " << lpad << "\n#define INNER " << inner << "ll\n";
-  o << "typedef " << C << " key_t;\n";
-  o << "__device__ __forceinline__ bool ku_before(key_t ka, int ia, key_t kb, int ib) {\n";
-  o << "  if (ia >= LEN || ib >= LEN) return ia < ib;\n";
-  o << "  const bool lt = " << (descending ? "ka > kb" : "ka < kb") << ", gt = " << (descending ? "ka < kb" : "ka > kb") << ";\n";
-  o << "  return lt || (!gt && ia < ib);\n}\n";
-  o << "extern \"C\" __global__ void ku_argsort(const void* __restrict__ src, void* __restrict__ out) {\n";
-  o << "  extern __shared__ __align__(16) unsigned char raw[];\n";
-  o << "  key_t* keys = (key_t*)raw;\n  int* ids = (int*)(raw + (size_t)LPAD * sizeof(key_t));\n";
-  o << "  const i64 line = blockIdx.x, po = line / INNER, pi = line % INNER;\n";
-  o << "  const " << S << "* base = (const " << S << "*)src + po * LEN * INNER + pi;\n";
-  o << "  for (int i = threadIdx.x; i < LPAD; i += blockDim.x) {\n";
-  o << "    ids[i] = i;\n    keys[i] = i < LEN ? (key_t)" << dec(d, "base[(i64)i * INNER]") << " : (key_t)0;\n  }\n";
-  o << "  __syncthreads();\n";
-  o << "  for (int k = 2; k <= LPAD; k <<= 1)\n    for (int j = k >> 1; j > 0; j >>= 1) {\n";
-  o << "      for (int i = threadIdx.x; i < LPAD; i += blockDim.x) {\n";
-  o << "        const int l = i ^ j;\n        if (l > i) {\n";
-  o << "          const key_t ka = keys[i], kb = keys[l];\n          const int ia = ids[i], ib = ids[l];\n";
-  o << "          const bool up = (i & k) == 0;\n";
-  o << "          if (ku_before(kb, ib, ka, ia) == up) { keys[i] = kb; keys[l] = ka; ids[i] = ib; ids[l] = ia; }\n";
-  o << "        }\n      }\n      __syncthreads();\n    }\n";
-  o << "  i64* dst = (i64*)out + po * LEN * INNER + pi;\n";
-  o << "  for (int r = threadIdx.x; r < LEN; r += blockDim.x) dst[(i64)r * INNER] = (i64)ids[r];\n}\n";
-  Emitted e;
-  e.source = o.str(); e.entry = "ku_argsort";
-  e.block = static_cast<unsigned>(std::max<int64_t>(32, std::min<int64_t>(1024, lpad / 2)));
-  e.grid = static_cast<unsigned>(outer * inner);
-  e.smem = static_cast<unsigned>(lpad * (key_bytes + 4));
-  e.family = "argsort";
-  (void)sm_count;
-  return e;
-}
-
-// Argsort along an axis longer than one CTA's shared memory holds: the same bitonic network over (key, original index)
-// pairs, run on a padded copy in global scratch. Chunks of ASL_CH pairs are sorted in shared memory (all stages up to
-// k = ASL_CH); for the larger k the steps with j >= ASL_CH are one global compare-exchange launch each and the steps
-// below are finished per chunk in shared memory again. The direction of a compare depends on the pair's position in
-// the whole line, so the pieces compose to the one network, and the result is the same stable permutation.
-// Entry points: ku_asl_chunks(src, keys, ids), ku_asl_global(keys, ids, k, j), ku_asl_local(keys, ids, k), ku_asl_out(ids, out).
-Emitted emit_argsort_long(DType d, bool descending, int64_t outer, int64_t len, int64_t inner, int64_t* lpad_out, size_t* key_bytes_out) {
-  int64_t lpad = 1;
-  while (lpad < len) lpad <<= 1;
-  const size_t key_bytes = d == DType::F64 || dtype_width(d) == 8 ? 8 : 4;
-  const std::string S = stype(d), C = is_float(d) ? (d == DType::F64 ? "double" : "float") : key_bytes == 8 ? ctype(d) : is_signed(d) ? "i32" : "u32";
-  std::ostringstream o;
-  o << device_prelude();
-  o << "#define LEN " << len << "ll\n#define LPAD " << lpad << "ll\n#define INNER " << inner << "ll\n#define LINES " << outer * inner << "ll\n#define ASL_CH 4096\n";
-  o << "typedef " << C << " key_t;\n";
-  o << "__device__ __forceinline__ bool ku_before(key_t ka, int ia, key_t kb, int ib) {\n";
-  o << "  if (ia >= LEN || ib >= LEN) return ia < ib;\n";
-  o << "  const bool lt = " << (descending ? "ka > kb" : "ka < kb") << ", gt = " << (descending ? "ka < kb" : "ka > kb") << ";\n";
-  o << "  return lt || (!gt && ia < ib);\n}\n";
-  // steps j = j_hi .. 1 of stage k on one chunk in shared memory; gi0 = position of the chunk's first pair in its line
-  o << "__device__ __forceinline__ void ku_asl_steps(key_t* keys, int* ids, i64 gi0, i64 k, int j_hi) {\n";
-  o << "  for (int j = j_hi; j > 0; j >>= 1) {\n";
-  o << "    for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) {\n";
-  o << "      const int l = i ^ j;\n      if (l > i) {\n";
-  o << "        const key_t ka = keys[i], kb = keys[l];\n        const int ia = ids[i], ib = ids[l];\n";
-  o << "        const bool up = ((gi0 + i) & k) == 0;\n";
-  o << "        if (ku_before(kb, ib, ka, ia) == up) { keys[i] = kb; keys[l] = ka; ids[i] = ib; ids[l] = ia; }\n";
-  o << "      }\n    }\n    __syncthreads();\n  }\n}\n";
-  o << "extern \"C\" __global__ void __launch_bounds__(1024) ku_asl_chunks(const void* __restrict__ src, key_t* __restrict__ gkeys, int* __restrict__ gids) {\n";
-  o << "  __shared__ key_t keys[ASL_CH];\n  __shared__ int ids[ASL_CH];\n";
-  o << "  const i64 cpl = LPAD / ASL_CH, line = blockIdx.x / cpl, gi0 = (blockIdx.x % cpl) * ASL_CH;\n";
-  o << "  const i64 po = line / INNER, pi = line % INNER;\n";
-  o << "  const " << S << "* base = (const " << S << "*)src + po * LEN * INNER + pi;\n";
-  o << "  for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) {\n";
-  o << "    const i64 gi = gi0 + i;\n    ids[i] = (int)gi;\n    keys[i] = gi < LEN ? (key_t)" << dec(d, "base[gi * INNER]") << " : (key_t)0;\n  }\n";
-  o << "  __syncthreads();\n";
-  o << "  for (i64 k = 2; k <= ASL_CH; k <<= 1) ku_asl_steps(keys, ids, gi0, k, (int)(k >> 1));\n";
-  o << "  for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) { gkeys[line * LPAD + gi0 + i] = keys[i]; gids[line * LPAD + gi0 + i] = ids[i]; }\n}\n";
-  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_asl_global(key_t* __restrict__ gkeys, int* __restrict__ gids, long long k, long long j) {\n";
-  o << "  const i64 pairs = LINES * (LPAD / 2);\n";
-  o << "  for (i64 q = (i64)blockIdx.x * 256 + threadIdx.x; q < pairs; q += (i64)gridDim.x * 256) {\n";
-  o << "    const i64 line = q / (LPAD / 2), pq = q % (LPAD / 2);\n";
-  o << "    const i64 i = (pq / j) * 2 * j + (pq % j), l = i + j;\n";
-  o << "    key_t* kk = gkeys + line * LPAD;\n    int* ii = gids + line * LPAD;\n";
-  o << "    const key_t ka = kk[i], kb = kk[l];\n    const int ia = ii[i], ib = ii[l];\n";
-  o << "    const bool up = (i & k) == 0;\n";
-  o << "    if (ku_before(kb, ib, ka, ia) == up) { kk[i] = kb; kk[l] = ka; ii[i] = ib; ii[l] = ia; }\n  }\n}\n";
-  o << "extern \"C\" __global__ void __launch_bounds__(1024) ku_asl_local(key_t* __restrict__ gkeys, int* __restrict__ gids, long long k) {\n";
-  o << "  __shared__ key_t keys[ASL_CH];\n  __shared__ int ids[ASL_CH];\n";
-  o << "  const i64 cpl = LPAD / ASL_CH, line = blockIdx.x / cpl, gi0 = (blockIdx.x % cpl) * ASL_CH;\n";
-  o << "  for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) { keys[i] = gkeys[line * LPAD + gi0 + i]; ids[i] = gids[line * LPAD + gi0 + i]; }\n";
-  o << "  __syncthreads();\n";
-  o << "  ku_asl_steps(keys, ids, gi0, k, ASL_CH / 2);\n";
-  o << "  for (int i = threadIdx.x; i < ASL_CH; i += blockDim.x) { gkeys[line * LPAD + gi0 + i] = keys[i]; gids[line * LPAD + gi0 + i] = ids[i]; }\n}\n";
-  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_asl_out(const int* __restrict__ gids, void* __restrict__ out) {\n";
-  o << "  const i64 total = LINES * LEN;\n";
-  o << "  for (i64 q = (i64)blockIdx.x * 256 + threadIdx.x; q < total; q += (i64)gridDim.x * 256) {\n";
-  o << "    const i64 line = q / LEN, r = q % LEN, po = line / INNER, pi = line % INNER;\n";
-  o << "    ((i64*)out)[po * LEN * INNER + r * INNER + pi] = (i64)gids[line * LPAD + r];\n  }\n}\n";
-  Emitted e;
-  e.source = o.str(); e.entry = "ku_asl_chunks"; e.family = "argsort";
-  *lpad_out = lpad; *key_bytes_out = key_bytes;
   return e;
 }
 

@@ -121,7 +121,7 @@ struct Program {
 // Compiles (or fetches from a cache) one entry point of a generated source.
 using KernelLoader = std::function<Kernel(const std::string& source, const std::string& entry, bool fmad)>;
 
-// ---- source emission (emit.cc) ------------------------------------------------------------------
+// ---- source emission (emit.cc, emit_index.cc) ------------------------------------------------------------------
 struct Emitted {
   std::string source, entry;
   std::vector<int> leaf_args;  // kernel pointer parameters, in order: leaf indices (then the output pointer)
@@ -140,11 +140,11 @@ Emitted emit_arg_reduce(const Fused& f, size_t axis, bool arg_min, int sm_count)
 // Softmax / RmsNorm over `axis` of `f`; output has f's shape, row-major.
 Emitted emit_softmax(const Fused& f, OpKind kind, size_t axis, float eps, int sm_count);
 
-// Indexing along one axis and per-line sorting over contiguous buffers (kernel parameters: see emit.cc).
+// Indexing along one axis and per-line sorting over contiguous buffers (kernel parameters: see emit_index.cc).
 Emitted emit_gather(DType d, DType idx_dt, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count);
 Emitted emit_gather_along(DType d, DType idx_dt, int64_t outer, int64_t da, int64_t la, int64_t inner, int sm_count);
 Emitted emit_scatter(DType d, DType idx_dt, bool along, uint8_t combine, int64_t pre, int64_t da, int64_t post, int64_t k, int sm_count);
-// The same for longer lines: four entry points over a padded copy in global scratch (see emit.cc)
+// The same for longer lines: four entry points over a padded copy in global scratch (see emit_index.cc)
 Emitted emit_argsort_long(DType d, bool descending, int64_t outer, int64_t len, int64_t inner, int64_t* lpad_out, size_t* key_bytes_out);
 Emitted emit_argsort(DType d, bool descending, int64_t outer, int64_t len, int64_t inner, int sm_count);
 
