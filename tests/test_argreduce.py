@@ -93,13 +93,16 @@ def test_device_matches_the_oracle(oracle_lib, cuda_lib, cpu, gpu, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("n", [3001, 4100, 10240])
 @pytest.mark.parametrize("dtype", [api.F32, api.F64, api.BF16, api.I32, api.I8, api.U64])
-def test_long_innermost_lines_take_a_cta_per_line(oracle_lib, cuda_lib, cpu, gpu, dtype):
+def test_long_innermost_lines_take_a_cta_per_line(oracle_lib, cuda_lib, cpu, gpu, dtype, n):
     """A long innermost axis (the sampling head: argmax over the vocabulary) runs one CTA per line; partial results merge by
     value and then by lower index, which must equal the interpreter's first-maximum walk: ties everywhere, NaNs at the
-    start, in the middle and at the end of a line, a line of NaNs, a line of one repeated value, +-inf and +-0."""
+    start, in the middle and at the end of a line, a line of NaNs, a line of one repeated value, +-inf and +-0. An odd
+    length is read element by element; 4100 and 10240 in 128-bit pieces, eight turns of loads at a time (4100 ends inside a
+    batch of turns, 10240 takes more than one batch)."""
     rng = np.random.default_rng(6)
-    lines, n = 9, 3001
+    lines = 9
     if dtype in (api.F32, api.F64, api.BF16):
         v = rng.integers(-4, 5, (lines, n)).astype(np.float64)      # many ties
         v[1, 0] = np.nan                                            # a leading NaN is never replaced
@@ -126,3 +129,18 @@ def test_long_innermost_lines_take_a_cta_per_line(oracle_lib, cuda_lib, cpu, gpu
         np.testing.assert_array_equal(outs[0], outs[1])
         if dtype == api.F32:
             np.testing.assert_array_equal(outs[0], reference(carrier, 1, arg_min))
+
+
+@pytest.mark.gpu
+def test_more_lines_than_ctas_in_flight(oracle_lib, cuda_lib, cpu, gpu):
+    """12000 lines are more than eight residencies of CTAs: the grid stays resident and its CTAs loop over the lines."""
+    rng = np.random.default_rng(9)
+    v = rng.integers(-50, 50, (12000, 256)).astype(np.float32)
+    outs = []
+    for lib, be in ((oracle_lib, cpu), (cuda_lib, gpu)):
+        g = api.Graph(lib)
+        x = g.input([12000, 256], api.F32)
+        out = g.argmax(x, 1)
+        outs.append(be.eval_with(g, out, api.Feeds(lib).set(x, v, api.F32)).numpy())
+    np.testing.assert_array_equal(outs[0], outs[1])
+    np.testing.assert_array_equal(outs[1], reference(v, 1, False))

@@ -168,7 +168,8 @@ def test_empty_and_rank0(oracle_lib, cuda_lib, cpu, gpu):
         util.assert_exact(a, b, f"edge {i}")
 
 
-@pytest.mark.parametrize("shape,axis", [((64, 4096), 1), ((7, 1000), 1), ((300, 33), 0), ((5, 64, 9), 1), ((3, 129), 1), ((1, 100000), 1), ((2049,), 0)])
+# (12000 rows: more than eight residencies of CTAs, so the row kernel's CTAs loop over rows instead of taking one each)
+@pytest.mark.parametrize("shape,axis", [((64, 4096), 1), ((7, 1000), 1), ((300, 33), 0), ((5, 64, 9), 1), ((3, 129), 1), ((1, 100000), 1), ((2049,), 0), ((12000, 256), 1)])
 def test_f32_reductions(oracle_lib, cuda_lib, cpu, cpu64, gpu, shape, axis):
     rng = np.random.default_rng(7)
     p = Pair(oracle_lib, cuda_lib)
@@ -223,7 +224,7 @@ def test_low_precision_pointwise_and_reduce(oracle_lib, cuda_lib, cpu, gpu):
         assert (va != vb).mean() < 0.02, f"chain {i}: {(va != vb).mean():.4f} of elements differ"
 
 
-@pytest.mark.parametrize("shape,axis", [((16, 8192), 1), ((33, 1000), 1), ((8, 77), 1), ((40, 50), 0), ((3, 20, 7), 1), ((2, 20000), 1)])
+@pytest.mark.parametrize("shape,axis", [((16, 8192), 1), ((33, 1000), 1), ((8, 77), 1), ((40, 50), 0), ((3, 20, 7), 1), ((2, 20000), 1), ((12000, 256), 1)])
 def test_softmax_and_rmsnorm(oracle_lib, cuda_lib, cpu, cpu64, gpu, shape, axis):
     rng = np.random.default_rng(9)
     p = Pair(oracle_lib, cuda_lib)
