@@ -429,10 +429,97 @@ template <typename T, typename F> __device__ __forceinline__ T ku_block_reduce(T
 }  // namespace
 
 // ---- pointwise ------------------------------------------------------------------------------------
+namespace {
+// Dim along which the leaves that are strided along the output's innermost dim are contiguous instead (a transposed
+// operand), or -1. Such a leaf read at the output's coordinates touches one element per 32-byte sector.
+int transposed_dim(const Fused& f, const Space& sp) {
+  const size_t nd = sp.dims.size();
+  if (nd < 2 || sp.dims.back() < 32) return -1;
+  for (size_t li = 0; li < f.leaves.size(); ++li) {
+    const Leaf& l = f.leaves[li];
+    if (l.kind != LeafKind::Buffer || !l.view.guards.empty()) continue;
+    const int64_t sl = sp.ls[li].back();
+    if (sl == 0 || sl == 1) continue;
+    for (size_t d = 0; d + 1 < nd; ++d)
+      if (sp.ls[li][d] == 1 && sp.dims[d] >= 32) return static_cast<int>(d);
+  }
+  return -1;
+}
+
+// Pointwise pass with transposed operands: a CTA takes a T x T tile over (dim a, innermost dim b). The leaves that are
+// contiguous along a are read along a (coalesced) into shared memory and read back transposed; every other leaf is read
+// at the output's coordinates; the stores run along b. Same expression body as ku_pointwise, so the same values.
+Emitted emit_pointwise_transposed(const Fused& f, const Space& sp, const Gen& g, int a_dim, int sm_count) {
+  const size_t nd = sp.dims.size(), a = static_cast<size_t>(a_dim), b = nd - 1;
+  const DType od = f.dtype();
+  std::vector<bool> staged(f.leaves.size(), false);
+  size_t min_w = dtype_width(od);
+  for (size_t li = 0; li < f.leaves.size(); ++li) {
+    const Leaf& l = f.leaves[li];
+    const int64_t sl = sp.ls[li].back();
+    if (l.kind == LeafKind::Buffer && l.view.guards.empty() && sl != 0 && sl != 1 && sp.ls[li][a] == 1) {
+      staged[li] = true;
+      min_w = std::min(min_w, dtype_width(l.dtype));
+    }
+  }
+  const int T = min_w <= 2 ? 64 : 32, RS = 256 / T;
+  std::vector<int64_t> tdims(sp.dims);
+  tdims[a] = (sp.dims[a] + T - 1) / T;
+  tdims[b] = (sp.dims[b] + T - 1) / T;
+  int64_t ntiles = 1;
+  for (int64_t d : tdims) ntiles *= d;
+  std::ostringstream o;
+  o << device_prelude();
+  o << "extern \"C\" __global__ void __launch_bounds__(256) ku_pointwise_t(" << g.params() << "void* __restrict__ out) {\n";
+  for (size_t li = 0; li < f.leaves.size(); ++li)
+    if (staged[li]) o << "  __shared__ " << stype(f.leaves[li].dtype) << " s" << li << "[" << T << "][" << T + std::max<size_t>(1, 4 / dtype_width(f.leaves[li].dtype)) << "];\n";
+  o << "  const int tx = threadIdx.x % " << T << ", ty = threadIdx.x / " << T << ";\n";
+  o << "  for (" << g.idx_t << " tile = blockIdx.x; tile < " << ntiles << "; tile += gridDim.x) {\n";
+  o << decompose("tile", tdims, 0, nd, g.idx_t, "q", "    ");
+  o << "    const " << g.idx_t << " a0 = q" << a << " * " << T << ", b0 = q" << b << " * " << T << ";\n";
+  std::vector<std::string> coords(nd);
+  for (size_t d = 0; d < nd; ++d) coords[d] = "q" + std::to_string(d);
+  coords[a] = "ca"; coords[b] = "cb";
+  o << "    __syncthreads();   // the tile before has been read out\n";
+  o << "#pragma unroll\n    for (int r = 0; r < " << T << "; r += " << RS << ") {\n";
+  o << "      const " << g.idx_t << " ca = a0 + tx, cb = b0 + ty + r;\n";
+  o << "      if (ca < " << sp.dims[a] << " && cb < " << sp.dims[b] << ") {\n";
+  for (size_t li = 0; li < f.leaves.size(); ++li)
+    if (staged[li]) o << "        s" << li << "[ty + r][tx] = ((const " << stype(f.leaves[li].dtype) << "*)p" << g.ptr_arg[li] << ")[" << g.offset(li, coords) << "];\n";
+  o << "      }\n    }\n    __syncthreads();\n";
+  o << "#pragma unroll\n    for (int r = 0; r < " << T << "; r += " << RS << ") {\n";
+  o << "      const " << g.idx_t << " ca = a0 + ty + r, cb = b0 + tx;\n";
+  o << "      if (ca < " << sp.dims[a] << " && cb < " << sp.dims[b] << ") {\n";
+  std::vector<std::string> lv(f.leaves.size()), lr(f.leaves.size());
+  for (size_t li = 0; li < f.leaves.size(); ++li) {
+    const std::string raw = "s" + std::to_string(li) + "[tx][ty + r]";
+    lv[li] = staged[li] ? dec(f.leaves[li].dtype, raw) : g.leaf_value(li, coords);
+    lr[li] = !is_lowf(f.leaves[li].dtype) ? std::string() : staged[li] ? raw : g.leaf_raw(li, coords);
+  }
+  o << g.body(lv, "        ", &lr);
+  std::ostringstream lin;
+  int64_t stride = 1;
+  std::vector<int64_t> ostr(nd);
+  for (size_t d = nd; d-- > 0;) { ostr[d] = stride; stride *= sp.dims[d]; }
+  for (size_t d = 0; d < nd; ++d) lin << (d ? " + " : "") << "(" << g.idx_t << ")" << coords[d] << " * (" << g.idx_t << ")" << ostr[d];
+  o << "        ((" << stype(od) << "*)out)[" << lin.str() << "] = " << g.root_store(lr) << ";\n";
+  o << "      }\n    }\n  }\n}\n";
+  Emitted e;
+  e.source = o.str();
+  e.entry = "ku_pointwise_t";
+  e.leaf_args = g.args;
+  e.block = 256;
+  e.grid = line_grid(ntiles, static_cast<int64_t>(sm_count) * 8);
+  e.family = "pointwise_tiled";
+  return e;
+}
+}  // namespace
+
 Emitted emit_pointwise(const Fused& f, int sm_count) {
   Space sp = collapse(f, -1);
   if (sp.dims.empty()) { sp.dims.push_back(1); for (auto& v : sp.ls) v.push_back(0); }
   Gen g(f, sp);
+  if (const int a = transposed_dim(f, sp); a >= 0) return emit_pointwise_transposed(f, sp, g, a, sm_count);
   const DType od = f.dtype();
   const int64_t total = static_cast<int64_t>(numel(f.shape));
   const int64_t inner = sp.dims.back();

@@ -156,6 +156,37 @@ def test_movement_bit_exact(oracle_lib, cuda_lib, cpu, gpu):
         util.assert_exact(a, b, f"movement {i}")
 
 
+def test_transposed_operands_go_through_shared_memory_tiles(oracle_lib, cuda_lib, cpu, gpu):
+    """A leaf that is contiguous along another dim than the output's innermost one (a transpose, a permuted batch) is
+    read along its own rows into shared-memory tiles and read back transposed; every other operand is read in place.
+    Bit for bit the interpreter's values: ragged tile edges in both dims, leading batch dims, 1-, 2-, 4- and 8-byte
+    types (a copy of 16-bit floats keeps NaN payloads), a second transposed leaf, a row-major one, a broadcast one, a
+    padded (guarded) one, and a transposed slice that starts inside its buffer."""
+    rng = np.random.default_rng(16)
+    p = Pair(oracle_lib, cuda_lib)
+    x = p.feed((300, 500), api.F32, rng_f32(rng, (300, 500)))
+    y = p.feed((500, 300), api.F32, rng_f32(rng, (500, 300)))
+    bias = p.feed((300,), api.F32, rng_f32(rng, (300,)))
+    xb = p.feed((4, 70, 90), api.BF16, rng.integers(0, 2 ** 16, (4, 70, 90)).astype(np.uint16))       # every bit pattern, NaNs included
+    xi = p.feed((64, 3, 128), api.I64, rng.integers(-2 ** 62, 2 ** 62, (64, 3, 128)).astype(np.int64))
+    x8 = p.feed((100, 200), api.U8, rng.integers(0, 256, (100, 200)).astype(np.uint8))
+    xt = p.permute(x, [1, 0])
+    nodes = [p.add(xt, y),                                                     # transposed + row-major
+             p.mul(p.add(xt, p.broadcast_to(bias, [500, 300])), xt),          # the same transposed leaf twice + a broadcast
+             p.permute(xb, [0, 2, 1]),                                         # pure copy, 2-byte, batch dim
+             p.mul(p.permute(xi, [2, 1, 0]), p.permute(xi, [2, 1, 0])),       # 8-byte, three dims reversed
+             p.permute(x8, [1, 0]),                                            # 1-byte
+             p.add(p.permute(p.slice(x, [(7, 300), (33, 500)]), [1, 0]), p.slice(y, [(33, 500), (7, 300)])),   # offsets inside the buffers
+             p.add(p.pad(p.slice(xt, [(0, 499), (0, 300)]), [(1, 0), (0, 0)]), y),                            # a guarded transposed leaf stays on direct reads
+             p.add(xt, p.pad(p.slice(y, [(0, 500), (0, 299)]), [(0, 0), (0, 1)])),                            # a guarded row-major leaf beside a staged one
+             p.cast(xt, api.BF16)]
+    assert api.compile_check(cuda_lib, p.gc, [nodes[0]]) == ["pointwise_tiled"]
+    assert api.compile_check(cuda_lib, p.gc, [nodes[2]]) == ["pointwise_tiled"]
+    o, c, _ = p.run(cpu, gpu, nodes)
+    for i, (a, b) in enumerate(zip(o, c)):
+        util.assert_exact(a, b, f"transposed operand {i}")
+
+
 def test_empty_and_rank0(oracle_lib, cuda_lib, cpu, gpu):
     p = Pair(oracle_lib, cuda_lib)
     e = p.feed((0, 5), api.F32, np.zeros((0, 5), np.float32))

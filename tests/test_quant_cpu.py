@@ -117,7 +117,7 @@ def test_blob_round_trip_and_device_lowering(oracle_lib, cuda_lib, cpu):
     # the CUDA library reads the same blob and compiles the lowering (no GPU needed)
     cg, ce = api.deserialize(cuda_lib, blob)
     fams = api.compile_check(cuda_lib, cg, ce[0][1])
-    assert fams and all(f in ("pointwise", "gemm_simt", "gemm_tc", "quant_gemv") for f in fams)
+    assert fams and all(f in ("pointwise", "pointwise_tiled", "gemm_simt", "gemm_tc", "quant_gemv") for f in fams)
     h = api.Graph(cuda_lib)
     *_, big = operands(cuda_lib, h, 256, 512, 1024, 4, 128, True, act_dtype=api.BF16)
     assert "gemm_tc" in api.compile_check(cuda_lib, h, [big])
