@@ -43,7 +43,7 @@ from kurumi_b200 import api, build, configs  # noqa: E402
 # ncu capture per kernel at the full workload size, summarised in the named file under profiles/. An entry is used only
 # while the kernel source it was captured from is unchanged (first 16 hex digits of its SHA-256).
 NCU_TRAFFIC = {
-    ("c1_fused_reduce", "reduce_rows"): (137.3e6, "profiles/reduce_rows__c1_fused_reduce.txt", "kurumi_b200/csrc/cuda/emit.cc", "9897a798486e592a"),
+    ("c1_fused_reduce", "reduce_rows"): (137.9e6, "profiles/reduce_rows__c1_fused_reduce.txt", "kurumi_b200/csrc/cuda/emit.cc", "7e375c1b68033b2c"),
     ("c2_transposed_softmax", "softmax_groups_tma"): (478.7e6, "profiles/softmax_groups_tma__c2_transposed_softmax.txt", "kurumi_b200/csrc/cuda/kernels/softmax_groups_tma.cuh", "dd8c62b067697094"),
     ("c3_gemm_bias_gelu", "gemm_tc"): (1251e6, "profiles/gemm_tc2__c3_gemm_bias_gelu.txt", "kurumi_b200/csrc/cuda/kernels/gemm_tc2.cuh", "df0ad6236b887218"),
     ("c4_causal_attention", "attention_tc"): (1057.5e6, "profiles/attention_tc__c4_causal_attention.txt", "kurumi_b200/csrc/cuda/kernels/attention_tc.cuh", "e76ea16f0699bdc8"),

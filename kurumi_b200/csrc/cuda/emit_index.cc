@@ -37,7 +37,7 @@ Emitted emit_gather(DType d, DType idx_dt, int64_t pre, int64_t da, int64_t post
   o << "    a = a < 0 ? 0 : (a > " << (da - 1) << "ll ? " << (da - 1) << "ll : a);\n";
   o << "    ((" << stype(d) << "*)out)[e] = ((const " << stype(d) << "*)src)[(p * " << da << "ll + a) * " << post << "ll + j];\n  }\n}\n";
   Emitted e;
-  e.source = o.str(); e.entry = "ku_gather"; e.block = 256; e.grid = pick_grid(total, 256, sm_count, 8); e.family = "gather";
+  e.source = o.str(); e.entry = "ku_gather"; e.block = 256; e.grid = pick_grid(total, 256, sm_count, kStreamCtasPerSm); e.family = "gather";
   return e;
 }
 
@@ -52,7 +52,7 @@ Emitted emit_gather_along(DType d, DType idx_dt, int64_t outer, int64_t da, int6
   o << "    a = a < 0 ? 0 : (a > " << (da - 1) << "ll ? " << (da - 1) << "ll : a);\n";
   o << "    ((" << stype(d) << "*)out)[e] = ((const " << stype(d) << "*)src)[(po * " << da << "ll + a) * " << inner << "ll + pi];\n  }\n}\n";
   Emitted e;
-  e.source = o.str(); e.entry = "ku_gather_along"; e.block = 256; e.grid = pick_grid(total, 256, sm_count, 8); e.family = "gather_along";
+  e.source = o.str(); e.entry = "ku_gather_along"; e.block = 256; e.grid = pick_grid(total, 256, sm_count, kStreamCtasPerSm); e.family = "gather_along";
   return e;
 }
 
