@@ -47,7 +47,7 @@ NCU_TRAFFIC = {
     ("c2_transposed_softmax", "softmax_groups_tma"): (478.7e6, "profiles/softmax_groups_tma__c2_transposed_softmax.txt", "kurumi_b200/csrc/cuda/kernels/softmax_groups_tma.cuh", "dd8c62b067697094"),
     ("c3_gemm_bias_gelu", "gemm_tc"): (1251e6, "profiles/gemm_tc2__c3_gemm_bias_gelu.txt", "kurumi_b200/csrc/cuda/kernels/gemm_tc2.cuh", "df0ad6236b887218"),
     ("c4_causal_attention", "attention_tc"): (1057.5e6, "profiles/attention_tc__c4_causal_attention.txt", "kurumi_b200/csrc/cuda/kernels/attention_tc.cuh", "e76ea16f0699bdc8"),
-    ("n3_quant_gemv", "quant_gemv"): (128.5e6, "profiles/quant_gemv_mma__n3_quant_gemv.txt", "kurumi_b200/csrc/cuda/kernels/quant_gemv_mma.cuh", "34c98aeb544694c7"),
+    ("n3_quant_gemv", "quant_gemv"): (128.2e6, "profiles/quant_gemv_mma__n3_quant_gemv.txt", "kurumi_b200/csrc/cuda/kernels/quant_gemv_mma.cuh", "b61c2994e45d6d5a"),
     ("c5_fp8_weight_gemm", "gemm_tc_f8"): (4236e6, "profiles/gemm_tc2_f8__c5_fp8_weight_gemm.txt", "kurumi_b200/csrc/cuda/kernels/gemm_tc2.cuh", "df0ad6236b887218"),
 }
 

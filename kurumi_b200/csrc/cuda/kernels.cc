@@ -153,11 +153,13 @@ bool build_quant_gemv(const KernelLoader& load, DType act, int64_t m, int64_t n,
   // mma.sync with the raw field values as one operand (kernels/quant_gemv_mma.cuh)
   if (act != DType::F32 && (bits == 2 || bits == 4) && group % (4 * piece) == 0 && k % (4 * piece) == 0 && n * (k / group) < (int64_t(1) << 31)) {
     const int64_t run = 4 * piece, depth = 3, res = 4;
-    // a CTA is 8 warps: 8 / ks tiles of 16 rows, ks warps per tile. The largest split whose CTAs still fit one wave keeps
-    // the most loads in flight; past that the CTAs loop over blocks of rows.
+    // a CTA is 8 warps: 8 / ks tiles of 16 rows, ks warps per tile. The largest split whose CTAs make up at most two waves:
+    // CTAs that start as others finish overlap their staging and final sums with the others' weight stream (28672 x 8192,
+    // 4 bits: 896 CTAs of 32 rows 49.6 us, 448 of 64 rows in exactly one wave 55.7 us, 1792 of 16 rows 51.3 us); past
+    // that the CTAs of one wave loop over blocks of rows.
     const int64_t tiles = (n + 15) / 16, wave = static_cast<int64_t>(sm_count) * res;
     int64_t ks = 8;
-    while (ks > 1 && ((tiles + 8 / ks - 1) / (8 / ks) > wave || k / run < ks * depth)) ks /= 2;
+    while (ks > 1 && ((tiles + 8 / ks - 1) / (8 / ks) > 2 * wave || k / run < ks * depth)) ks /= 2;
     // all K columns of the activations staged once when that leaves room for res CTAs per SM, else in chunks that the
     // ring's slots line up with
     const int64_t budget = (200 * 1024) / res - 4096, unit = run * ks * depth;
@@ -170,7 +172,8 @@ bool build_quant_gemv(const KernelLoader& load, DType act, int64_t m, int64_t n,
     out->name = "quant_gemv";
     out->kernel = load(src, "ku_quant_gemv_mma", true);
     const int64_t rows_per_cta = (8 / ks) * 16;
-    out->grid[0] = static_cast<unsigned>(std::min<int64_t>((n + rows_per_cta - 1) / rows_per_cta, wave));
+    const int64_t row_blocks = (n + rows_per_cta - 1) / rows_per_cta;
+    out->grid[0] = static_cast<unsigned>(row_blocks <= 2 * wave ? row_blocks : wave);
     out->block[0] = 256;
     out->smem = static_cast<unsigned>(m * (kc + 16) * 2 + m * ((kc + run - 1) / run) * 4);
     for (int sidx = 1; sidx <= 5; ++sidx) { Arg a; a.kind = Arg::SlotPtr; a.slot = -sidx; out->args.push_back(a); }

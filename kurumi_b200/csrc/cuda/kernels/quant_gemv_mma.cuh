@@ -26,7 +26,7 @@
 // the B operand is one 8-byte read per instruction. A run of four pieces must lie in one group: GROUP % (4 * PIECE) == 0.
 //
 // A CTA is 8 warps: RT tiles of 16 rows, each split over KS warps that take every KS-th run of a row and add their
-// partial sums at the end (the host picks KS so that one wave of CTAs covers all rows). A lane keeps D runs of its two
+// partial sums at the end (the host picks the largest KS whose CTAs make up at most two waves). A lane keeps D runs of its two
 // rows in flight (a register ring), requested before the activations are staged, so the weight stream never waits for
 // the staging. The activations of all K columns are staged once per CTA when they fit (KC == K); otherwise in chunks
 // of KC columns, KC a multiple of RUN * KS * D so that the ring's slots line up with the chunk boundaries.
