@@ -72,3 +72,29 @@ def test_decode_step_kernels_compile_for_every_field_width_and_activation_type(c
     for act, bits, kw in ((api.BF16, 4, {}), (api.F16, 2, dict(n=28672, k=8192, group=256)), (api.BF16, 4, dict(n=28672, k=8192, mins=False)),
                           (api.F16, 4, dict(n=100000, k=2048)), (api.F32, 4, {}), (api.BF16, 8, {}), (api.F16, 4, dict(group=32))):
         assert families(cuda_lib, lambda g: step(g, act, bits, **kw)) == ["quant_gemv"]
+
+
+def test_the_named_configurations_compile_to_their_kernels_at_full_size(cuda_lib):
+    """Every configuration the benchmark times, recorded at its full size, lowers to the kernel it is measured with and
+    that kernel compiles for sm_100a (tcgen05 GEMM in CTA pairs, fused attention, the group softmax, the row reduction,
+    the fp8 path behind an activation quantise, the decode-step gemv); so do their row shards for 2, 4 and 8 ranks."""
+    from kurumi_b200 import configs
+    want = {
+        configs.fused_reduce: ["reduce_rows"],
+        configs.transposed_softmax: ["softmax_groups_tma"],
+        configs.gemm_bias_gelu: ["gemm_tc"],
+        configs.causal_attention: ["attention_tc"],
+        configs.fp8_weight_gemm: ["pointwise", "gemm_tc_f8"],
+        configs.quant_gemv: ["quant_gemv"],
+    }
+    for build, fams in want.items():
+        g = api.Graph(cuda_lib)
+        root, _ = build(g)
+        assert api.compile_check(cuda_lib, g, [root]) == fams, build.__name__
+    for parts in (2, 4, 8):
+        g = api.Graph(cuda_lib)
+        root, _ = configs.transposed_softmax(g, n=8192, lines=8192 // parts)
+        assert api.compile_check(cuda_lib, g, [root]) == ["softmax_groups_tma"]
+        g = api.Graph(cuda_lib)
+        root, _ = configs.fused_reduce(g, rows=4096 // parts)
+        assert api.compile_check(cuda_lib, g, [root]) == ["reduce_rows"]
